@@ -1,0 +1,78 @@
+// Shared host-side declarations of the library: the context object behind the
+// opaque dc_ctx handle, error latching, and small device helpers.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <tuple>
+
+#include "../../include/decide_cuda.h"
+
+typedef CUresult (*dc_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                       CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                       CUtensorMapFloatOOBfill);
+
+// (base pointer, rows, cols, row stride in elements, box rows)
+typedef std::tuple<const void*, uint32_t, uint32_t, uint32_t, uint32_t> dc_tmap_key;
+
+struct dc_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    int* status_dev = nullptr;       // device status word, 0 = healthy; set by a kernel whose bounded wait ran out
+    int* status_host = nullptr;      // pinned staging for dc_check_status
+    std::string last_error;          // latched message, cleared when read
+    dc_encode_tiled_fn encode_tiled = nullptr;
+    std::map<dc_tmap_key, CUtensorMap> tmaps;   // tensor-map cache, filled on first use of an operand
+    uint64_t launches = 0;           // kernels enqueued through this context
+    uint32_t gemm_impl = DC_IMPL_FAST;
+    uint32_t attn_impl = DC_IMPL_FAST;
+    uint32_t delta_impl = DC_IMPL_FAST;
+    void* workspace = nullptr;       // scratch for the chunked delta rule and other multi-pass ops
+    size_t workspace_bytes = 0;
+};
+
+int dc_fail(dc_ctx* ctx, int code, const char* fmt, ...);
+int dc_check_launch(dc_ctx* ctx, const char* what);
+// Returns a workspace of at least `bytes` (growing it is an allocation: callers that
+// must not allocate during a timed forward reserve it up front with dc_reserve_workspace).
+void* dc_workspace(dc_ctx* ctx, size_t bytes);
+
+#define DC_REQUIRE(ctx, cond, ...)                                            \
+    do {                                                                      \
+        if (!(cond)) return dc_fail((ctx), DC_INVALID_ARG, __VA_ARGS__);      \
+    } while (0)
+
+namespace dc {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// Precise: feeds the recurrence's decay gate, whose error compounds over tokens.
+__device__ __forceinline__ float softplus_precise(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+}  // namespace dc

@@ -1,0 +1,174 @@
+// Context lifetime, error latch, status word and workspace of libdecide_cuda.so.
+// Plays the part of the reference's DecideDevice (crates/decide-metal/src/device.rs:55-130):
+// device handle, "pipeline" state that must exist before a timed request, and nothing else.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+int dc_fail(dc_ctx* ctx, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx && ctx->last_error.empty()) ctx->last_error = buf;  // first error wins, as Run::fail (forward.rs:322-329)
+    return code;
+}
+
+int dc_check_launch(dc_ctx* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return DC_OK;
+}
+
+void* dc_workspace(dc_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->workspace_bytes) return ctx->workspace;
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    ctx->workspace = p;
+    ctx->workspace_bytes = bytes;
+    return p;
+}
+
+static uint32_t impl_from_env(const char* name, bool* bad) {
+    const char* v = getenv(name);
+    if (!v || !*v || strcmp(v, "fast") == 0) return DC_IMPL_FAST;
+    if (strcmp(v, "baseline") == 0) return DC_IMPL_BASELINE;
+    *bad = true;
+    return DC_IMPL_FAST;
+}
+
+extern "C" {
+
+dc_ctx* dc_open(int device, char* err, size_t err_len) {
+    auto say = [&](const char* msg, const char* detail) {
+        if (err && err_len) snprintf(err, err_len, "%s%s%s", msg, detail ? ": " : "", detail ? detail : "");
+    };
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        say("dc_open: no CUDA device (this library has no CPU path)", e != cudaSuccess ? cudaGetErrorString(e) : nullptr);
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (device < 0 || device >= count) {
+        say("dc_open: device index out of range", nullptr);
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    if ((e = cudaSetDevice(device)) != cudaSuccess || (e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
+        say("dc_open: cannot select device", cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        say("dc_open: the kernels are built for sm_100a (B200) only", prop.name);
+        return nullptr;
+    }
+    dc_ctx* ctx = new dc_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    bool bad = false;
+    ctx->gemm_impl = impl_from_env("DECIDE_GEMM", &bad);
+    ctx->attn_impl = impl_from_env("DECIDE_ATTN", &bad);
+    ctx->delta_impl = impl_from_env("DECIDE_DELTA", &bad);
+    if (bad) {
+        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`", nullptr);
+        delete ctx;
+        return nullptr;
+    }
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+        say("dc_open: cuTensorMapEncodeTiled not available", e != cudaSuccess ? cudaGetErrorString(e) : nullptr);
+        delete ctx;
+        return nullptr;
+    }
+    ctx->encode_tiled = reinterpret_cast<dc_encode_tiled_fn>(fn);
+    if ((e = cudaMalloc(&ctx->status_dev, sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ctx->status_dev, 0, sizeof(int))) != cudaSuccess ||
+        (e = cudaMallocHost(&ctx->status_host, sizeof(int))) != cudaSuccess) {
+        say("dc_open: cannot allocate the status word", cudaGetErrorString(e));
+        dc_close(ctx);
+        return nullptr;
+    }
+    *ctx->status_host = 0;
+    return ctx;
+}
+
+void dc_close(dc_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    delete ctx;
+}
+
+size_t dc_last_error(dc_ctx* ctx, char* buf, size_t len) {
+    if (!ctx) return 0;
+    size_t n = ctx->last_error.size();
+    if (buf && len) {
+        snprintf(buf, len, "%s", ctx->last_error.c_str());
+    }
+    ctx->last_error.clear();
+    return n;
+}
+
+int dc_set_impl(dc_ctx* ctx, uint32_t family, uint32_t impl) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, impl == DC_IMPL_FAST || impl == DC_IMPL_BASELINE, "dc_set_impl: impl %u is neither fast nor baseline", impl);
+    switch (family) {
+        case DC_FAMILY_GEMM: ctx->gemm_impl = impl; break;
+        case DC_FAMILY_ATTN: ctx->attn_impl = impl; break;
+        case DC_FAMILY_DELTA: ctx->delta_impl = impl; break;
+        default: return dc_fail(ctx, DC_INVALID_ARG, "dc_set_impl: unknown family %u", family);
+    }
+    return DC_OK;
+}
+
+uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family) {
+    if (!ctx) return DC_IMPL_FAST;
+    switch (family) {
+        case DC_FAMILY_GEMM: return ctx->gemm_impl;
+        case DC_FAMILY_ATTN: return ctx->attn_impl;
+        case DC_FAMILY_DELTA: return ctx->delta_impl;
+        default: return DC_IMPL_FAST;
+    }
+}
+
+int dc_check_status(dc_ctx* ctx, void* stream) {
+    if (!ctx) return DC_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "dc_check_status: %s", cudaGetErrorString(e));
+    int code = *ctx->status_host;
+    if (code != 0) {
+        cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), s);
+        cudaStreamSynchronize(s);
+        return dc_fail(ctx, DC_TIMEOUT, "a bounded device-side wait ran out (wait id %d); the results of this run are invalid", code);
+    }
+    return DC_OK;
+}
+
+uint64_t dc_launch_count(dc_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int dc_reserve_workspace(dc_ctx* ctx, size_t bytes) {
+    if (!ctx) return DC_INVALID_ARG;
+    if (!dc_workspace(ctx, bytes)) return dc_fail(ctx, DC_CUDA_ERROR, "dc_reserve_workspace: cannot allocate %zu bytes", bytes);
+    return DC_OK;
+}
+
+int dc_sm_count(dc_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+}  // extern "C"

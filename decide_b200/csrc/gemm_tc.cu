@@ -1,0 +1,363 @@
+// Y = X * W^T with fused epilogues on the 5th-generation tensor cores (tcgen05), bf16 operands,
+// fp32 accumulation in tensor memory (TMEM).
+//
+// Replaces the reference's tiled GEMM `gemm_nt_fast*` (kernels/gemm_fast.metal:289-351) and its
+// four epilogues (kernels/gemm.rs:16-26). Structure of one CTA (192 threads, one CTA per SM,
+// persistent over output tiles of 128 x BN):
+//   warp 0      TMA producer: X tile [128 x 64] and W tile [BN x 64] per k-block into a ring of
+//               128-byte-swizzled shared-memory stages (plain per-CTA loads, no multicast);
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) over each stage and
+//               commits the stage back to the producer; owns the TMEM allocation;
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread, 32 columns at
+//               a time), apply the epilogue, store to global.
+// Two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the main loop of
+// tile i+1. M, N and K tails come from TMA's out-of-bounds zero fill plus masked stores.
+// Every mbarrier wait is bounded; on expiry the CTA sets the status word, drains its own
+// copies in flight, frees its TMEM and returns.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+using namespace dc;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmArgs {
+    uint32_t m, n, k, ldy;
+    uint32_t m_tiles, n_tiles, k_blocks, group_m;
+};
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr uint32_t kABytes = BM * BK * 2;
+    static constexpr uint32_t kBBytes = BN * BK * 2;
+    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+    static constexpr uint32_t kBarBytes = 256;
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+};
+
+// Output tiles are walked in groups of `group_m` row tiles: inside a group the row tile moves
+// fastest, so the CTAs running at one time share a few W stripes and one X group in L2, and W is
+// streamed from HBM once per group.
+__device__ __forceinline__ void tile_coords(uint32_t t, const GemmArgs& a, uint32_t& tm, uint32_t& tn) {
+    const uint32_t per_group = a.group_m * a.n_tiles;
+    const uint32_t g = t / per_group;
+    const uint32_t local = t - g * per_group;
+    const uint32_t m0 = g * a.group_m;
+    const uint32_t gsz = min(a.group_m, a.m_tiles - m0);
+    tn = local / gsz;
+    tm = m0 + (local - tn * gsz);
+}
+
+__device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+    return true;
+}
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_store(void* __restrict__ y, size_t row, uint32_t col0, uint32_t ldy,
+                                               const uint32_t (&r)[32]) {
+    if constexpr (EPI == DC_EPI_STORE_F32) {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(y) + row * ldy + col0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            p[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                               __uint_as_float(r[4 * j + 3]));
+    } else if constexpr (EPI == DC_EPI_ADD_F32) {
+        float4* p = reinterpret_cast<float4*>(static_cast<float*>(y) + row * ldy + col0);
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = p[j];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j].x += __uint_as_float(r[4 * j]);
+            v[j].y += __uint_as_float(r[4 * j + 1]);
+            v[j].z += __uint_as_float(r[4 * j + 2]);
+            v[j].w += __uint_as_float(r[4 * j + 3]);
+            p[j] = v[j];
+        }
+    } else if constexpr (EPI == DC_EPI_STORE_BF16) {
+        uint4* p = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(y) + row * ldy + col0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            p[j] = v;
+        }
+    } else {
+        // SwiGLU over interleaved blocks of 16: columns [0,16) of this 32-column chunk are the gate,
+        // [16,32) the up projection of the same 16 output columns (cpu_ref.rs:39-50).
+        uint4* p = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(y) + row * ldy + (col0 >> 1));
+        float o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = silu_f(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(o[8 * j], o[8 * j + 1]);
+            v.y = pack_bf16x2(o[8 * j + 2], o[8 * j + 3]);
+            v.z = pack_bf16x2(o[8 * j + 4], o[8 * j + 5]);
+            v.w = pack_bf16x2(o[8 * j + 6], o[8 * j + 7]);
+            p[j] = v;
+        }
+    }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+               void* __restrict__ y, const GemmArgs a, int* __restrict__ status) {
+    using C = Cfg<BN>;
+    constexpr int S = C::kStages;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + S * C::kABytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * C::kStageBytes);
+    uint64_t* full = bars;                 // [S]   producer -> MMA: stage filled
+    uint64_t* empty = bars + S;            // [S]   MMA -> producer: stage consumed
+    uint64_t* acc_full = bars + 2 * S;     // [2]   MMA -> epilogue: accumulator complete
+    uint64_t* acc_empty = bars + 2 * S + 2;  // [2] epilogue -> MMA: accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t num_tiles = a.m_tiles * a.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        *abort_flag = 0u;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(&tm_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, issued = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                uint32_t tm, tn;
+                tile_coords(t, a, tm, tn);
+                for (uint32_t kb = 0; kb < a.k_blocks; ++kb) {
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], C::kStageBytes);
+                    tma_load_2d(smem_a + s * C::kABytes, &tm_x, &full[s], static_cast<int32_t>(kb * BK),
+                                static_cast<int32_t>(tm * BM));
+                    tma_load_2d(smem_b + s * C::kBBytes, &tm_w, &full[s], static_cast<int32_t>(kb * BK),
+                                static_cast<int32_t>(tn * BN));
+                    ++issued;
+                    if (++s == S) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+            if (!ok) {
+                // Leave only after this CTA's copies in flight have landed (or their own limit ran out):
+                // the last min(issued, S) stages, newest first.
+                uint32_t n_back = issued < static_cast<uint32_t>(S) ? issued : static_cast<uint32_t>(S);
+                uint32_t bs = s, bph = ph;
+                for (uint32_t j = 0; j < n_back; ++j) {
+                    if (bs == 0) {
+                        bs = S - 1;
+                        bph ^= 1u;
+                    } else {
+                        --bs;
+                    }
+                    if (!wait_quiet(&full[bs], bph)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            uint32_t s = 0, ph = 0, lt = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++lt) {
+                const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, abort_flag, status, 2)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < a.k_blocks; ++kb) {
+                    if (!mbar_wait(&full[s], ph, abort_flag, status, 3)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t ad = umma_desc_k128(smem_u32(smem_a + s * C::kABytes));
+                    const uint64_t bd = umma_desc_k128(smem_u32(smem_b + s * C::kBBytes));
+#pragma unroll
+                    for (uint32_t kk = 0; kk < BK / 16; ++kk) {
+                        // 16 elements along K = 32 bytes = 2 units of the descriptor's 16-byte address field
+                        umma_bf16_ss(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) != 0u ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                    if (++s == S) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const uint32_t q = static_cast<uint32_t>(warp) & 3u;  // TMEM lane quadrant this warp may read
+        uint32_t lt = 0;
+        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++lt) {
+            uint32_t tm, tn;
+            tile_coords(t, a, tm, tn);
+            const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+            bool ok = mbar_wait(&acc_full[acc], acc_ph, abort_flag, status, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const size_t row = static_cast<size_t>(tm) * BM + q * 32u + lane;
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = tn * BN + c * 32u;
+                if (col0 >= a.n) break;
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c * 32u, r);
+                tmem_ld_wait();
+                if (row < a.m) epilogue_store<EPI>(y, row, col0, a.ldy, r);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows,
+              CUtensorMap* out) {
+    const dc_tmap_key key(base, rows, cols, ld, box_rows);
+    auto it = ctx->tmaps.find(key);
+    if (it != ctx->tmaps.end()) {
+        *out = it->second;
+        return DC_OK;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = ctx->encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cuTensorMapEncodeTiled failed (%d) for [%u x %u] ld %u", static_cast<int>(r),
+                       rows, cols, ld);
+    if (ctx->tmaps.size() >= 8192) ctx->tmaps.clear();
+    ctx->tmaps.emplace(key, m);
+    *out = m;
+    return DC_OK;
+}
+
+template <int BN, int EPI>
+int launch(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtensorMap& tw, void* y, const GemmArgs& a) {
+    using C = Cfg<BN>;
+    static bool attr_set[16] = {};
+    auto kern = gemm_tc_kernel<BN, EPI>;
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cannot opt in to %u bytes of shared memory: %s", C::kSmemBytes, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    const uint32_t tiles = a.m_tiles * a.n_tiles;
+    const uint32_t grid = tiles < static_cast<uint32_t>(ctx->sm_count) ? tiles : static_cast<uint32_t>(ctx->sm_count);
+    kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tx, tw, y, a, ctx->status_dev);
+    return dc_check_launch(ctx, "gemm (tcgen05)");
+}
+
+template <int BN>
+int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtensorMap& tw, void* y, const GemmArgs& a,
+               uint32_t epi) {
+    switch (epi) {
+        case DC_EPI_STORE_F32: return launch<BN, DC_EPI_STORE_F32>(ctx, stream, tx, tw, y, a);
+        case DC_EPI_STORE_BF16: return launch<BN, DC_EPI_STORE_BF16>(ctx, stream, tx, tw, y, a);
+        case DC_EPI_ADD_F32: return launch<BN, DC_EPI_ADD_F32>(ctx, stream, tx, tw, y, a);
+        default: return launch<BN, DC_EPI_SWIGLU_BF16>(ctx, stream, tx, tw, y, a);
+    }
+}
+
+}  // namespace
+
+// Tile plan: the analogue of gemm_configs::plan (crates/decide-metal/src/gemm_configs.rs:312).
+// 128 x 256 tiles unless the narrower 128 x 128 tile fills the SMs in clearly fewer waves.
+uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, int sm_count) {
+    const uint32_t m_tiles = (m + BM - 1) / BM;
+    auto waves = [&](uint32_t bn) {
+        const uint32_t tiles = m_tiles * ((n + bn - 1) / bn);
+        return (tiles + sm_count - 1) / sm_count;
+    };
+    // relative time: waves x tile width, with a 12% penalty for the narrow tile's lower operand reuse
+    const double t256 = waves(256) * 256.0;
+    const double t128 = waves(128) * 128.0 * 1.12;
+    return t128 < t256 ? 128u : 256u;
+}
+
+int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
+               uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override) {
+    const uint32_t bn = bn_override ? bn_override : dc_gemm_plan_bn(m, n, ctx->sm_count);
+    GemmArgs a;
+    a.m = m;
+    a.n = n;
+    a.k = k;
+    a.ldy = ldy;
+    a.m_tiles = (m + BM - 1) / BM;
+    a.n_tiles = (n + bn - 1) / bn;
+    a.k_blocks = (k + BK - 1) / BK;
+    a.group_m = a.m_tiles < 16 ? a.m_tiles : 16;
+    CUtensorMap tx, tw;
+    int rc = make_tmap(ctx, x, m, k, ldx, BM, &tx);
+    if (rc != DC_OK) return rc;
+    rc = make_tmap(ctx, w, n, k, ldw, bn, &tw);
+    if (rc != DC_OK) return rc;
+    if (bn == 256) return launch_epi<256>(ctx, stream, tx, tw, y, a, epi);
+    return launch_epi<128>(ctx, stream, tx, tw, y, a, epi);
+}

@@ -1,0 +1,203 @@
+// HBM-bound row kernels: RMSNorm, embedding gather, row gathers, the candidate-row logit head and
+// the gated RMSNorm. One warp per row (or per (row, head)), 128-bit loads and stores, shuffle
+// reductions. They replace kernels/rmsnorm.metal, embed.metal, head.metal and gnorm.metal.
+#include "common.cuh"
+
+namespace {
+
+using namespace dc;
+
+constexpr int kWarpsPerBlock = 8;
+
+// y[r] = x[rowmap[r]] * rsqrt(mean(x^2) + eps) * (w or 1 + w); spec cpu_ref.rs:11-22.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+               const uint32_t* __restrict__ rowmap, uint32_t rows, uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps,
+               uint32_t add_one) {
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t src = rowmap ? rowmap[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(src) * ld_in);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const uint32_t nv = h >> 2;
+    float ss = 0.0f;
+    for (uint32_t i = lane; i < nv; i += 32) {
+        const float4 v = xr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(h) + eps);
+    const float one = add_one ? 1.0f : 0.0f;
+    uint2* yr = reinterpret_cast<uint2*>(y + static_cast<size_t>(r) * ld_out);
+    for (uint32_t i = lane; i < nv; i += 32) {
+        const float4 v = xr[i];
+        const float4 g = wr[i];
+        uint2 o;
+        o.x = pack_bf16x2(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
+        o.y = pack_bf16x2(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
+        yr[i] = o;
+    }
+}
+
+// out[t] = float(table[ids[t]]); embed.metal:4-13.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+embed_kernel(const uint32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ out, uint32_t t,
+             uint32_t h) {
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= t) return;
+    const int lane = threadIdx.x & 31;
+    const uint2* src = reinterpret_cast<const uint2*>(table + static_cast<size_t>(ids[r]) * h);
+    float4* dst = reinterpret_cast<float4*>(out + static_cast<size_t>(r) * h);
+    for (uint32_t i = lane; i < (h >> 2); i += 32) {
+        const uint2 v = src[i];
+        dst[i] = make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+    }
+}
+
+// out[i] = x[rowmap[i]], rows of `row_bytes` bytes (a multiple of 16); head.metal:9-28.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+gather_rows_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ rowmap, uint4* __restrict__ out, uint32_t rows,
+                   uint32_t vec_per_row) {
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint4* src = x + static_cast<size_t>(rowmap[r]) * vec_per_row;
+    uint4* dst = out + static_cast<size_t>(r) * vec_per_row;
+    for (uint32_t i = lane; i < vec_per_row; i += 32) dst[i] = src[i];
+}
+
+// One warp per (row, candidate): final zero-centred RMSNorm of the row, then the dot product with the
+// candidate's bf16 embedding row, all in fp32 (head.metal:32-59; spec cpu_ref.rs:192-198). The table
+// rows are read from the device-resident table by id.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+final_head_kernel(const float* __restrict__ x, const float* __restrict__ w, const __nv_bfloat16* __restrict__ table,
+                  const uint32_t* __restrict__ cand, const uint32_t* __restrict__ ncand, float* __restrict__ logits,
+                  uint32_t h, uint32_t max_cand, float eps) {
+    const uint32_t r = blockIdx.x;
+    const uint32_t c = blockIdx.y * kWarpsPerBlock + (threadIdx.x >> 5);
+    const uint32_t nc = min(ncand[r], max_cand);
+    if (c >= nc) return;
+    const int lane = threadIdx.x & 31;
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * h);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const uint32_t nv = h >> 2;
+    float ss = 0.0f;
+    for (uint32_t i = lane; i < nv; i += 32) {
+        const float4 v = xr[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(h) + eps);
+    const uint2* er = reinterpret_cast<const uint2*>(table + static_cast<size_t>(cand[static_cast<size_t>(r) * max_cand + c]) * h);
+    float dot = 0.0f;
+    for (uint32_t i = lane; i < nv; i += 32) {
+        const float4 v = xr[i];
+        const float4 g = wr[i];
+        const uint2 e = er[i];
+        dot = fmaf(v.x * inv * (1.0f + g.x), bf16_lo(e.x), dot);
+        dot = fmaf(v.y * inv * (1.0f + g.y), bf16_hi(e.x), dot);
+        dot = fmaf(v.z * inv * (1.0f + g.z), bf16_lo(e.y), dot);
+        dot = fmaf(v.w * inv * (1.0f + g.w), bf16_hi(e.y), dot);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) logits[static_cast<size_t>(r) * max_cand + c] = dot;
+}
+
+// Per (row, value head): RMSNorm over dv = 128 with fp32 weight (no +1), times silu(z);
+// gnorm.metal:6-25, spec cpu_ref.rs:132-145. One warp per (row, head), one float4 per lane.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+gated_rmsnorm_silu_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ w,
+                          __nv_bfloat16* __restrict__ y, uint32_t t, uint32_t nv_heads, uint32_t ldz, float eps) {
+    const uint32_t idx = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (idx >= t * nv_heads) return;
+    const uint32_t s = idx / nv_heads, hd = idx - s * nv_heads;
+    const int lane = threadIdx.x & 31;
+    const float4 v = reinterpret_cast<const float4*>(o + static_cast<size_t>(idx) * 128)[lane];
+    const float4 zz = reinterpret_cast<const float4*>(z + static_cast<size_t>(s) * ldz + hd * 128)[lane];
+    const float4 g = reinterpret_cast<const float4*>(w)[lane];
+    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+    uint2 out;
+    out.x = pack_bf16x2(v.x * inv * g.x * silu_f(zz.x), v.y * inv * g.y * silu_f(zz.y));
+    out.y = pack_bf16x2(v.z * inv * g.z * silu_f(zz.z), v.w * inv * g.w * silu_f(zz.w));
+    reinterpret_cast<uint2*>(y + static_cast<size_t>(idx) * 128)[lane] = out;
+}
+
+inline uint32_t blocks_for(uint32_t warps) { return (warps + kWarpsPerBlock - 1) / kWarpsPerBlock; }
+inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* y, const uint32_t* rowmap, uint32_t rows,
+               uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps, uint32_t add_one) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, x && w && y, "rmsnorm: null operand");
+    DC_REQUIRE(ctx, h <= ld_in && h <= ld_out, "rmsnorm: H = %u exceeds a row stride (ld_in = %u, ld_out = %u)", h, ld_in, ld_out);
+    DC_REQUIRE(ctx, h % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && h > 0, "rmsnorm: H and the row strides must be multiples of 4");
+    DC_REQUIRE(ctx, aligned16(x) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "rmsnorm: misaligned operand");
+    if (rows == 0) return DC_OK;
+    rmsnorm_kernel<<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, w, static_cast<__nv_bfloat16*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
+    return dc_check_launch(ctx, "rmsnorm");
+}
+
+int dc_embed(dc_ctx* ctx, void* stream, const uint32_t* ids, const void* table, float* out, uint32_t t, uint32_t h) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, ids && table && out, "embed: null operand");
+    DC_REQUIRE(ctx, h % 4 == 0 && h > 0, "embed: H = %u must be a multiple of 4", h);
+    DC_REQUIRE(ctx, reinterpret_cast<uintptr_t>(table) % 8 == 0 && aligned16(out), "embed: misaligned operand");
+    if (t == 0) return DC_OK;
+    embed_kernel<<<blocks_for(t), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        ids, static_cast<const __nv_bfloat16*>(table), out, t, h);
+    return dc_check_launch(ctx, "embed");
+}
+
+static int gather_rows(dc_ctx* ctx, void* stream, const void* x, const uint32_t* rowmap, void* out, uint32_t rows,
+                       size_t row_bytes, const char* what) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, x && rowmap && out, "%s: null operand", what);
+    DC_REQUIRE(ctx, row_bytes % 16 == 0 && row_bytes > 0 && aligned16(x) && aligned16(out), "%s: rows must be whole 16-byte vectors", what);
+    if (rows == 0) return DC_OK;
+    gather_rows_kernel<<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4*>(x), rowmap, static_cast<uint4*>(out), rows, static_cast<uint32_t>(row_bytes / 16));
+    return dc_check_launch(ctx, what);
+}
+
+int dc_gather_rows_f32(dc_ctx* ctx, void* stream, const float* x, const uint32_t* rowmap, float* out, uint32_t rows, uint32_t h) {
+    return gather_rows(ctx, stream, x, rowmap, out, rows, static_cast<size_t>(h) * 4, "gather_rows_f32");
+}
+
+int dc_gather_rows_bf16(dc_ctx* ctx, void* stream, const void* x, const uint32_t* rowmap, void* out, uint32_t rows, uint32_t h) {
+    return gather_rows(ctx, stream, x, rowmap, out, rows, static_cast<size_t>(h) * 2, "gather_rows_bf16");
+}
+
+int dc_final_head(dc_ctx* ctx, void* stream, const float* x, const float* w, const void* table, const uint32_t* cand,
+                  const uint32_t* ncand, float* logits, uint32_t rows, uint32_t h, uint32_t max_cand, float eps) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, x && w && table && cand && ncand && logits, "final_head: null operand");
+    DC_REQUIRE(ctx, h % 4 == 0 && h > 0 && max_cand >= 1, "final_head: H = %u must be a multiple of 4 and max_cand >= 1", h);
+    DC_REQUIRE(ctx, aligned16(x) && aligned16(w) && reinterpret_cast<uintptr_t>(table) % 8 == 0, "final_head: misaligned operand");
+    if (rows == 0) return DC_OK;
+    dim3 grid(rows, (max_cand + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    final_head_kernel<<<grid, kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, w, static_cast<const __nv_bfloat16*>(table), cand, ncand, logits, h, max_cand, eps);
+    return dc_check_launch(ctx, "final_head");
+}
+
+int dc_gated_rmsnorm_silu(dc_ctx* ctx, void* stream, const float* o, const float* z, const float* w, void* y, uint32_t t,
+                          uint32_t nv, uint32_t dv, uint32_t ldz, float eps) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, o && z && w && y, "gated_rmsnorm_silu: null operand");
+    if (dv != 128) return dc_fail(ctx, DC_UNSUPPORTED, "gated_rmsnorm_silu: value head dim %u (built for 128)", dv);
+    DC_REQUIRE(ctx, ldz >= nv * dv && ldz % 4 == 0, "gated_rmsnorm_silu: ldz = %u must cover %u columns and be a multiple of 4", ldz, nv * dv);
+    DC_REQUIRE(ctx, aligned16(o) && aligned16(z) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "gated_rmsnorm_silu: misaligned operand");
+    if (t == 0) return DC_OK;
+    gated_rmsnorm_silu_kernel<<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        o, z, w, static_cast<__nv_bfloat16*>(y), t, nv, ldz, eps);
+    return dc_check_launch(ctx, "gated_rmsnorm_silu");
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+"""The operator interface of decide's engine, over the CUDA library.
+
+Mirrors crates/decide-engine/src/kernels/mod.rs:40-67 of the reference: a `Kernels` object holding
+one object per kernel family (`k.gemm`, `k.norm`, `k.rope`, ...), one method per kernel, the same
+argument order and meaning. Where the reference passes a Metal compute encoder, these take a CUDA
+stream (`None` = torch's current stream); where it passes `(buffer, byte offset)` pairs, these take
+`(tensor, byte offset)` pairs or plain tensors. Methods only enqueue; nothing synchronises.
+Contract violations raise `KernelError` (the reference panics via `assert!`).
+
+torch is used for device memory and streams only; every operation runs in libdecide_cuda.so.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+
+import torch
+
+from . import _lib
+
+EPS = 1e-6  # crates/decide-engine/src/config.rs:33
+
+
+class KernelError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[dc error {code}] {message}")
+        self.code = code
+
+
+class Epilogue(enum.IntEnum):
+    """kernels/gemm.rs:16-26, with bf16 in place of fp16."""
+    StoreF32 = 0
+    StoreBF16 = 1
+    AddF32 = 2
+    SwigluBF16 = 3
+
+
+class Impl(enum.IntEnum):
+    """GemmImpl / AttnImpl / DeltaImpl of the reference."""
+    Fast = 0
+    Baseline = 1
+
+
+class Family(enum.IntEnum):
+    Gemm = 0
+    Attn = 1
+    Delta = 2
+
+
+def _ptr(arg) -> int:
+    """Device address of a tensor, or of (tensor, byte offset); None -> NULL."""
+    if arg is None:
+        return 0
+    if isinstance(arg, tuple):
+        t, off = arg
+        return t.data_ptr() + int(off)
+    return arg.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+class Device:
+    """One context per GPU: the analogue of DecideDevice::shared (crates/decide-metal/src/device.rs:125-130)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("decide_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+        torch.cuda.set_device(device)
+        torch.cuda.init()
+        err = ctypes.create_string_buffer(512)
+        self.handle = self.lib.dc_open(device, err, len(err))
+        if not self.handle:
+            raise RuntimeError(err.value.decode() or "dc_open failed")
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.dc_close(self.handle)
+            self.handle = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def last_error(self) -> str:
+        buf = ctypes.create_string_buffer(1024)
+        self.lib.dc_last_error(self.handle, buf, len(buf))
+        return buf.value.decode()
+
+    def call(self, name: str, *args):
+        rc = getattr(self.lib, name)(self.handle, *args)
+        if rc != 0:
+            raise KernelError(rc, self.last_error())
+
+    def check_status(self, stream=None):
+        """Synchronises the stream and raises if a kernel's bounded wait ran out."""
+        self.call("dc_check_status", _stream(stream))
+
+    def set_impl(self, family: Family, impl: Impl):
+        self.call("dc_set_impl", int(family), int(impl))
+
+    def get_impl(self, family: Family) -> Impl:
+        return Impl(self.lib.dc_get_impl(self.handle, int(family)))
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.dc_launch_count(self.handle))
+
+    @property
+    def sm_count(self) -> int:
+        return int(self.lib.dc_sm_count(self.handle))
+
+    def reserve_workspace(self, nbytes: int):
+        self.call("dc_reserve_workspace", nbytes)
+
+
+class _Family:
+    def __init__(self, dev: Device):
+        self.dev = dev
+
+
+class Gemm(_Family):
+    def implementation(self) -> Impl:
+        return self.dev.get_impl(Family.Gemm)
+
+    def gemm(self, stream, x, w, y, m, n, k, ldx, ldw, ldy, epi: Epilogue, swiglu_block: int = 16):
+        """Y = X·Wᵀ then `epi` (kernels/gemm.rs:138-175)."""
+        self.dev.call("dc_gemm", _stream(stream), _ptr(x), _ptr(w), _ptr(y), m, n, k, ldx, ldw, ldy, int(epi), swiglu_block)
+
+    def gemm_tile(self, stream, x, w, y, m, n, k, ldx, ldw, ldy, epi: Epilogue, bn: int):
+        """The fast kernel with a forced tile width (test hook)."""
+        self.dev.call("dc_gemm_tile", _stream(stream), _ptr(x), _ptr(w), _ptr(y), m, n, k, ldx, ldw, ldy, int(epi), bn)
+
+    def plan(self, m: int, n: int) -> int:
+        return int(self.dev.lib.dc_gemm_plan(self.dev.handle, m, n))
+
+
+class Norm(_Family):
+    def rmsnorm(self, stream, x, w, y, rowmap, rows, h, ld_in, ld_out, add_one: bool, eps: float = EPS):
+        """y[r] = rmsnorm(x[rowmap[r]])·(w or 1+w) as bf16 (kernels/norm.rs:23-33). rowmap None = identity."""
+        self.dev.call("dc_rmsnorm", _stream(stream), _ptr(x), _ptr(w), _ptr(y), _ptr(rowmap), rows, h, ld_in, ld_out, eps, int(add_one))
+
+
+class Embed(_Family):
+    def embed(self, stream, ids, table, out, t, h):
+        """out[t] = table[ids[t]] (bf16 → fp32) (kernels/embed.rs:16-22)."""
+        self.dev.call("dc_embed", _stream(stream), _ptr(ids), _ptr(table), _ptr(out), t, h)
+
+
+class GNorm(_Family):
+    def gated_rmsnorm_silu(self, stream, o, z, w, y, t, ldz, nv: int, dv: int = 128, eps: float = EPS):
+        """Per (row, value head) RMSNorm × SiLU(z) (kernels/gnorm.rs:19-31)."""
+        self.dev.call("dc_gated_rmsnorm_silu", _stream(stream), _ptr(o), _ptr(z), _ptr(w), _ptr(y), t, nv, dv, ldz, eps)
+
+
+class Head(_Family):
+    def gather_rows_f32(self, stream, x, rowmap, out, rows, h):
+        self.dev.call("dc_gather_rows_f32", _stream(stream), _ptr(x), _ptr(rowmap), _ptr(out), rows, h)
+
+    def gather_rows_bf16(self, stream, x, rowmap, out, rows, h):
+        self.dev.call("dc_gather_rows_bf16", _stream(stream), _ptr(x), _ptr(rowmap), _ptr(out), rows, h)
+
+    def final_head(self, stream, x, w, table, cand, ncand, logits, rows, h, max_cand, eps: float = EPS):
+        """Final norm + candidate-row logits (kernels/head.rs:47-60)."""
+        self.dev.call("dc_final_head", _stream(stream), _ptr(x), _ptr(w), _ptr(table), _ptr(cand), _ptr(ncand), _ptr(logits), rows, h, max_cand, eps)
+
+
+class Kernels:
+    """Every kernel family, as `Kernels::new(dev)` of the reference (kernels/mod.rs:54-66)."""
+
+    def __init__(self, dev: Device):
+        self.dev = dev
+        self.embed = Embed(dev)
+        self.norm = Norm(dev)
+        self.gemm = Gemm(dev)
+        self.gnorm = GNorm(dev)
+        self.head = Head(dev)

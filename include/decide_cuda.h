@@ -1,0 +1,125 @@
+/* decide_cuda.h — C ABI of libdecide_cuda.so, the sm_100a (B200) backend behind decide's
+ * operator interface.
+ *
+ * It replaces the reference's `decide-metal` device layer and `kernels/*.metal` behind the
+ * `decide-engine` dispatch wrappers (crates/decide-engine/src/kernels/mod.rs:40-67): one
+ * entry point per wrapper method, same argument meaning.
+ *
+ * Conventions (they mirror the reference's, kernels/mod.rs:1-5 and 31-38):
+ *  - Every dc_<op> only ENQUEUES work on `stream` (a cudaStream_t passed as void*) and
+ *    returns; it never synchronises. Stream order is the only ordering, as the serial
+ *    compute encoder is in the reference (forward.rs:31-38).
+ *  - Pointers are device pointers already offset to the first element (the reference passes
+ *    (buffer, byte offset) pairs). Dims and strides are in ELEMENTS, enums are uint32_t.
+ *  - The caller owns every buffer. The context owns only its tensor-map cache, a status
+ *    word and a bounded scratch workspace.
+ *  - Return value 0 = DC_OK. Contract violations that the reference `assert!`s return
+ *    DC_INVALID_ARG with a message readable through dc_last_error (latched, cleared on
+ *    read), in the style of the reference's own C ABI (crates/decide-ane/src/lib.rs:22-35).
+ *  - There is no CPU fallback: without a CUDA device dc_open fails.
+ *  - A context is not thread-safe (the reference's Forward::logits takes &mut self,
+ *    forward.rs:704); distinct contexts are independent.
+ */
+#ifndef DECIDE_CUDA_H
+#define DECIDE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct dc_ctx dc_ctx;
+
+enum {
+    DC_OK = 0,
+    DC_INVALID_ARG = 1,   /* what the reference asserts on */
+    DC_CUDA_ERROR = 2,    /* a CUDA call failed */
+    DC_UNSUPPORTED = 3,   /* shape/feature outside what the kernels are built for */
+    DC_TIMEOUT = 4        /* a bounded device-side wait ran out (see dc_check_status) */
+};
+
+/* Epilogue of dc_gemm: kernels/gemm.rs:16-26 (fp16 there, bf16 here). */
+enum {
+    DC_EPI_STORE_F32 = 0,   /* Y fp32 [M,N] = acc */
+    DC_EPI_STORE_BF16 = 1,  /* Y bf16 [M,N] = acc */
+    DC_EPI_ADD_F32 = 2,     /* Y fp32 [M,N] += acc (the residual add) */
+    DC_EPI_SWIGLU_BF16 = 3  /* Y bf16 [M,N/2] = silu(gate)*up over interleaved gate|up blocks */
+};
+
+/* Kernel choice per family, the reference's DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA = fast|baseline
+ * (kernels/gemm.rs:56-63, attn.rs:49-56, delta.rs:34-41). */
+enum { DC_IMPL_FAST = 0, DC_IMPL_BASELINE = 1 };
+enum { DC_FAMILY_GEMM = 0, DC_FAMILY_ATTN = 1, DC_FAMILY_DELTA = 2 };
+
+/* ---- context: replaces DecideDevice::shared + Kernels::new (device.rs:125-130, mod.rs:54-66) ---- */
+dc_ctx* dc_open(int device, char* err, size_t err_len);
+void dc_close(dc_ctx* ctx);
+/* Copies the latched error message (empty when none) and clears it; returns its length. */
+size_t dc_last_error(dc_ctx* ctx, char* buf, size_t len);
+/* Picks fast or baseline kernels for a family; at open the DECIDE_GEMM / DECIDE_ATTN /
+ * DECIDE_DELTA environment variables are read once, as Gemm::new etc. do. */
+int dc_set_impl(dc_ctx* ctx, uint32_t family, uint32_t impl);
+uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family);
+/* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
+ * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
+int dc_check_status(dc_ctx* ctx, void* stream);
+/* Kernels enqueued through this context so far. */
+uint64_t dc_launch_count(dc_ctx* ctx);
+/* Grows the context's scratch workspace to at least `bytes` now, so that later calls do not
+ * allocate (Gemm::warm_up's role for pipelines, gemm.rs:89-107). */
+int dc_reserve_workspace(dc_ctx* ctx, size_t bytes);
+/* Number of SMs of the context's device. */
+int dc_sm_count(dc_ctx* ctx);
+
+/* ---- Gemm::gemm (kernels/gemm.rs:138-175; spec cpu_ref.rs:25-50) ----
+ * Y = X * W^T then `epilogue`. X bf16 [M,K] row stride ldx; W bf16 [N,K] row stride ldw;
+ * ldy in elements of Y's type. fp32 accumulation. Requires N%32==0, K%32==0, M>=1,
+ * ldx,ldw >= K, ldy >= output columns. The fast (tcgen05) kernels also need ldx%8==0, ldw%8==0,
+ * x,w 16-byte aligned, ldy%8==0 (bf16 outputs) or ldy%4==0 (fp32 outputs), y 16-byte aligned, and
+ * swiglu_block == 16 for DC_EPI_SWIGLU_BF16 (as gemm_fast.metal hard-codes). */
+int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
+            uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t swiglu_block);
+
+/* Test hooks for the fast GEMM: dc_gemm_tile forces the output tile width (128 or 256) that
+ * dc_gemm_plan would otherwise choose per shape (the role of gemm_configs::plan,
+ * crates/decide-metal/src/gemm_configs.rs:312, and of the reference's per-config test sweep). */
+int dc_gemm_tile(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
+                 uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t bn);
+uint32_t dc_gemm_plan(dc_ctx* ctx, uint32_t m, uint32_t n);
+
+/* ---- Norm::rmsnorm (kernels/norm.rs:23-33; spec cpu_ref.rs:11-22) ----
+ * y[r] = x[rowmap[r]] * rsqrt(mean(x^2)+eps) * (add_one ? 1+w : w); x fp32, w fp32 [h], y bf16.
+ * rowmap u32 [rows] or NULL for the identity. h%4==0. */
+int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* y, const uint32_t* rowmap,
+               uint32_t rows, uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps, uint32_t add_one);
+
+/* ---- Embed::embed (kernels/embed.rs:16-22) ---- out[t] = float(table[ids[t]]), table bf16 [vocab,h]. */
+int dc_embed(dc_ctx* ctx, void* stream, const uint32_t* ids, const void* table, float* out, uint32_t t, uint32_t h);
+
+/* ---- Head::gather_rows_f32 / gather_rows_f16 (kernels/head.rs:28-45) ---- out[i] = x[rowmap[i]]. */
+int dc_gather_rows_f32(dc_ctx* ctx, void* stream, const float* x, const uint32_t* rowmap, float* out, uint32_t rows,
+                       uint32_t h);
+int dc_gather_rows_bf16(dc_ctx* ctx, void* stream, const void* x, const uint32_t* rowmap, void* out, uint32_t rows,
+                        uint32_t h);
+
+/* ---- Head::final_head (kernels/head.rs:47-60; spec cpu_ref.rs:192-198) ----
+ * Final zero-centred RMSNorm (weight w fp32 [h]) of each of `rows` fp32 rows of x [rows,h], then
+ * logits against the bf16 rows of `table` named by cand (u32 [rows,max_cand], row r uses the first
+ * ncand[r]). Writes fp32 logits [rows,max_cand]; entries past ncand[r] are not written. */
+int dc_final_head(dc_ctx* ctx, void* stream, const float* x, const float* w, const void* table,
+                  const uint32_t* cand, const uint32_t* ncand, float* logits, uint32_t rows, uint32_t h,
+                  uint32_t max_cand, float eps);
+
+/* ---- GNorm::gated_rmsnorm_silu (kernels/gnorm.rs:19-31; spec cpu_ref.rs:132-145) ----
+ * Per (row, value head): RMSNorm of o (fp32 [t,nv,dv]) over dv with weight w (fp32 [dv], no +1),
+ * times silu(z); z is read from rows of stride ldz (head h at columns h*dv..). Writes bf16 y [t,nv*dv].
+ * dv must be 128. */
+int dc_gated_rmsnorm_silu(dc_ctx* ctx, void* stream, const float* o, const float* z, const float* w, void* y,
+                          uint32_t t, uint32_t nv, uint32_t dv, uint32_t ldz, float eps);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECIDE_CUDA_H */

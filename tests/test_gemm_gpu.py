@@ -1,0 +1,162 @@
+"""GEMM parity on the GPU, through the C ABI, against the restated cpu_ref::gemm_nt +
+swiglu_interleaved (oracle/cpu_ref.py). Inputs are seeded, rounded to bf16 once, and shared
+bit-for-bit by both sides. Tolerances: fp32 outputs atol 2e-4 + rtol 2e-5 (fp32 accumulation of
+up to 9728 bf16 products of magnitude ~0.02); bf16 outputs add bf16's half-ulp, rtol 2^-8."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_ref
+from tests.util import assert_close, bf16, np32, randn
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = dict(atol=2e-4, rtol=2e-5)
+BF16_TOL = dict(atol=2e-3, rtol=2 ** -8)
+
+
+def _operands(seed, m, n, k, ldx=None, ldw=None):
+    ldx, ldw = ldx or k, ldw or k
+    x = torch.zeros(m, ldx, dtype=torch.bfloat16)
+    w = torch.zeros(n, ldw, dtype=torch.bfloat16)
+    x[:, :k] = bf16(randn(seed, m, k))
+    w[:, :k] = bf16(randn(seed + 1, n, k, std=0.02))
+    return x, w
+
+
+def _want(x, w, m, n, k, epi, y0=None, block=16):
+    acc = cpu_ref.gemm_nt(np32(x[:, :k]), np32(w[:, :k]), m, n, k)
+    if epi == 3:
+        return cpu_ref.swiglu_interleaved(acc, m, n, block)
+    if epi == 2:
+        return acc + y0
+    return acc
+
+
+def _run(k, x, w, m, n, kk, epi, ldy=None, y0=None, bn=None, block=16):
+    from decide_b200.kernels import Epilogue
+
+    n_out = n // 2 if epi == 3 else n
+    ldy = ldy or n_out
+    dt = torch.float32 if epi in (0, 2) else torch.bfloat16
+    if y0 is not None:
+        y = torch.zeros(m, ldy, dtype=dt)
+        y[:, :n_out] = torch.from_numpy(y0)
+        y = y.cuda()
+    else:
+        y = torch.full((m, ldy), 7.0, dtype=dt, device="cuda")  # canary: columns past n_out must stay 7
+    xd, wd = x.cuda(), w.cuda()
+    if bn is None:
+        k.gemm.gemm(None, xd, wd, y, m, n, kk, x.shape[1], w.shape[1], ldy, Epilogue(epi), block)
+    else:
+        k.gemm.gemm_tile(None, xd, wd, y, m, n, kk, x.shape[1], w.shape[1], ldy, Epilogue(epi), bn)
+    k.dev.check_status()
+    out = np32(y)
+    if ldy > n_out and y0 is None:
+        assert (out[:, n_out:] == 7.0).all(), "the kernel wrote past the output columns"
+    return out[:, :n_out]
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("m,n,kk", [(128, 256, 64), (128, 256, 256), (1, 32, 32), (37, 96, 160), (276, 512, 2560),
+                                    (300, 8224, 512), (603, 2560, 1024)])
+def test_fast_store_f32_shapes(k, m, n, kk, bn):
+    """One tile / one k-block up to ragged M, N and K tails (TMA zero fill + masked stores)."""
+    x, w = _operands(10 + m, m, n, kk)
+    got = _run(k, x, w, m, n, kk, 0, bn=bn)
+    assert_close(got, _want(x, w, m, n, kk, 0), what=f"StoreF32 {m}x{n}x{kk} bn{bn}", **F32_TOL)
+
+
+@pytest.mark.parametrize("epi", [0, 1, 2, 3])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_fast_epilogues(k, epi, bn):
+    m, n, kk = 276, 1024, 2560
+    x, w = _operands(3, m, n, kk)
+    y0 = np32(randn(5, m, n)) if epi == 2 else None
+    got = _run(k, x, w, m, n, kk, epi, y0=y0, bn=bn)
+    tol = F32_TOL if epi in (0, 2) else BF16_TOL
+    assert_close(got, _want(x, w, m, n, kk, epi, y0), what=f"epilogue {epi} bn{bn}", **tol)
+
+
+def test_fast_strides_and_slices(k):
+    """Row strides wider than K / N, and a row slice of W by offset (gemm.rs:126-130)."""
+    from decide_b200.kernels import Epilogue
+
+    m, n, kk = 200, 640, 320
+    x, w = _operands(21, m, n, kk, ldx=kk + 64, ldw=kk + 8)
+    got = _run(k, x, w, m, n, kk, 0, ldy=n + 12)
+    assert_close(got, _want(x, w, m, n, kk, 0), what="strided", **F32_TOL)
+    # rows 128..384 of W as a slice
+    xd, wd = x.cuda(), w.cuda()
+    y = torch.zeros(m, 256, dtype=torch.float32, device="cuda")
+    k.gemm.gemm(None, xd, (wd, 128 * w.shape[1] * 2), y, m, 256, kk, x.shape[1], w.shape[1], 256, Epilogue.StoreF32)
+    k.dev.check_status()
+    want = cpu_ref.gemm_nt(np32(x[:, :kk]), np32(w[128:384, :kk]), m, 256, kk)
+    assert_close(np32(y), want, what="W row slice", **F32_TOL)
+
+
+def test_config0_gate_up_swiglu(k):
+    """BASELINE config 0: X[276x2560] ~N(0,1), W_gate_up[19456x2560] ~N(0,0.02) -> SiLU(gate)*up [276x9728]."""
+    m, n, kk = 276, 19456, 2560
+    x, w = _operands(0, m, n, kk)
+    got = _run(k, x, w, m, n, kk, 3)
+    assert_close(got, _want(x, w, m, n, kk, 3), what="config 0", **BF16_TOL)
+
+
+@pytest.mark.parametrize("epi", [0, 1, 2, 3])
+@pytest.mark.parametrize("block", [16, 32])
+def test_baseline_kernel(k, epi, block):
+    """The bisecting kernel (DECIDE_GEMM=baseline) against the same oracle, incl. other SwiGLU blocks."""
+    from decide_b200.kernels import Family, Impl
+
+    if epi != 3 and block != 16:
+        pytest.skip("block only matters for SwiGLU")
+    m, n, kk = 70, 192, 96
+    x, w = _operands(40, m, n, kk)
+    y0 = np32(randn(41, m, n)) if epi == 2 else None
+    k.dev.set_impl(Family.Gemm, Impl.Baseline)
+    try:
+        got = _run(k, x, w, m, n, kk, epi, y0=y0, block=block)
+    finally:
+        k.dev.set_impl(Family.Gemm, Impl.Fast)
+    tol = F32_TOL if epi in (0, 2) else BF16_TOL
+    assert_close(got, _want(x, w, m, n, kk, epi, y0, block), what=f"baseline epilogue {epi}", **tol)
+
+
+def test_fast_equals_baseline_bitwise_when_exact(k):
+    """Small integers: every product and partial sum is exact in fp32, so fast and baseline must agree bit for bit."""
+    from decide_b200.kernels import Epilogue, Family, Impl
+
+    m, n, kk = 130, 288, 192
+    g = torch.Generator().manual_seed(9)
+    x = torch.randint(-4, 5, (m, kk), generator=g).to(torch.bfloat16).cuda()
+    w = torch.randint(-4, 5, (n, kk), generator=g).to(torch.bfloat16).cuda()
+    outs = []
+    for impl in (Impl.Fast, Impl.Baseline):
+        k.dev.set_impl(Family.Gemm, impl)
+        y = torch.zeros(m, n, dtype=torch.float32, device="cuda")
+        k.gemm.gemm(None, x, w, y, m, n, kk, kk, kk, n, Epilogue.StoreF32)
+        k.dev.check_status()
+        outs.append(y.cpu())
+    k.dev.set_impl(Family.Gemm, Impl.Fast)
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], (x.float().cpu() @ w.float().cpu().T))
+
+
+def test_contract_violations_are_errors(k):
+    """What the reference asserts (gemm.rs:140-144, 159-163) comes back as DC_INVALID_ARG, nothing is launched."""
+    from decide_b200.kernels import Epilogue, KernelError
+
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(4, 64, dtype=torch.float32, device="cuda")
+    before = k.dev.launches
+    for args in [(4, 48, 64, 64, 64, 64), (4, 64, 48, 64, 64, 64), (0, 64, 64, 64, 64, 64), (4, 64, 64, 32, 64, 64),
+                 (4, 64, 64, 64, 64, 32), (4, 64, 64, 68, 64, 64)]:
+        with pytest.raises(KernelError) as e:
+            k.gemm.gemm(None, x, w, y, *args, Epilogue.StoreF32)
+        assert e.value.code == 1
+    with pytest.raises(KernelError) as e:
+        k.gemm.gemm(None, x, w, y, 4, 64, 64, 64, 64, 32, Epilogue.SwigluBF16, 32)
+    assert e.value.code in (1, 3)
+    assert k.dev.launches == before
