@@ -172,6 +172,55 @@ class Head(_Family):
         self.dev.call("dc_final_head", _stream(stream), _ptr(x), _ptr(w), _ptr(table), _ptr(cand), _ptr(ncand), _ptr(logits), rows, h, max_cand, eps)
 
 
+class Rope(_Family):
+    def q_norm_rope(self, stream, pq, qw, inv_freq, qpos, qo, rows, ldq, nq: int, hd: int, rot: int, eps: float = EPS):
+        """Head norm + RoPE of the q heads (kernels/rope.rs:26-37)."""
+        self.dev.call("dc_q_norm_rope", _stream(stream), _ptr(pq), _ptr(qw), _ptr(inv_freq), _ptr(qpos), _ptr(qo), rows, ldq, nq, hd, rot, eps)
+
+    def kv_norm_rope(self, stream, pkv, kw, inv_freq, kc, vc, rows, ldkv, kcol, vcol, pos0, cache_rows: int, nkv: int,
+                     hd: int, rot: int, pos=None, eps: float = EPS):
+        """Head norm + RoPE of the k heads into the K cache, v heads copied to the V cache (kernels/rope.rs:39-51).
+        `pos` (u32 per row) switches to packed sequences: rotate for pos[r], write cache row r."""
+        self.dev.call("dc_kv_norm_rope", _stream(stream), _ptr(pkv), _ptr(kw), _ptr(inv_freq), _ptr(kc), _ptr(vc), rows, ldkv,
+                      kcol, vcol, pos0, _ptr(pos), cache_rows, nkv, hd, rot, eps)
+
+
+class Attn(_Family):
+    def implementation(self) -> Impl:
+        return self.dev.get_impl(Family.Attn)
+
+    def attention(self, stream, q, kc, vc, gate, qpos, y, rows, ldg, nq: int, nkv: int, hd: int = 128, seq_start=None,
+                  n_seq: int = 1, max_len: int = 0):
+        """Causal GQA attention with the optional sigmoid gate (kernels/attn.rs:81-118). The reference passes
+        the fused projection `pq` and reads the gate at a fixed column; here `gate` is that column's address
+        (`(p, col * 4)`), or None for no gate."""
+        self.dev.call("dc_attention", _stream(stream), _ptr(q), _ptr(kc), _ptr(vc), _ptr(gate), _ptr(qpos), _ptr(y), rows, ldg, nq,
+                      nkv, hd, _ptr(seq_start), n_seq, max_len)
+
+
+class Conv(_Family):
+    def conv_silu_l2(self, stream, p, prev, w, q, k, v, t, ldp, nk: int, nv: int, dk: int = 128, dv: int = 128,
+                     seq_start=None, n_seq: int = 1, max_len: int = 0):
+        """Depthwise causal conv + SiLU + per-head L2 norm (kernels/conv.rs:21-36)."""
+        self.dev.call("dc_conv_silu_l2", _stream(stream), _ptr(p), _ptr(prev), _ptr(w), _ptr(q), _ptr(k), _ptr(v), t, ldp, nk, nv, dk, dv,
+                      _ptr(seq_start), n_seq, max_len)
+
+    def conv_state_update(self, stream, p, prev_in, prev_out, t, ldp, conv_dim: int):
+        """The 3 raw rows that end the chunk (kernels/conv.rs:38-46)."""
+        self.dev.call("dc_conv_state_update", _stream(stream), _ptr(p), _ptr(prev_in), _ptr(prev_out), t, ldp, conv_dim)
+
+
+class Delta(_Family):
+    def implementation(self) -> Impl:
+        return self.dev.get_impl(Family.Delta)
+
+    def gated_delta(self, stream, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, write_state: bool,
+                    nk: int, nv: int, dk: int = 128, dv: int = 128, seq_start=None, n_seq: int = 1):
+        """The gated delta rule (kernels/delta.rs:53-100)."""
+        self.dev.call("dc_gated_delta", _stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias),
+                      _ptr(state_in), _ptr(state_out), _ptr(o), t, ldab, int(write_state), nk, nv, dk, dv, _ptr(seq_start), n_seq)
+
+
 class Kernels:
     """Every kernel family, as `Kernels::new(dev)` of the reference (kernels/mod.rs:54-66)."""
 
@@ -182,3 +231,7 @@ class Kernels:
         self.gemm = Gemm(dev)
         self.gnorm = GNorm(dev)
         self.head = Head(dev)
+        self.rope = Rope(dev)
+        self.attn = Attn(dev)
+        self.conv = Conv(dev)
+        self.delta = Delta(dev)

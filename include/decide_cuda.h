@@ -119,6 +119,61 @@ int dc_final_head(dc_ctx* ctx, void* stream, const float* x, const float* w, con
 int dc_gated_rmsnorm_silu(dc_ctx* ctx, void* stream, const float* o, const float* z, const float* w, void* y,
                           uint32_t t, uint32_t nv, uint32_t dv, uint32_t ldz, float eps);
 
+/* ---- Rope::q_norm_rope (kernels/rope.rs:26-37; spec cpu_ref.rs:149-162) ----
+ * Zero-centred per-head RMSNorm (weight qw fp32 [hd]) + RoPE on the first `rot` dims (pairs i, i+rot/2,
+ * fp32 angle = qpos[r] * inv_freq[i], precise sin/cos) of the nq q heads of `rows` rows of pq (fp32,
+ * q at column 0, row stride ldq). Writes bf16 qo [rows,nq,hd]. hd 128 or 256; rot%8==0, rot<=128. */
+int dc_q_norm_rope(dc_ctx* ctx, void* stream, const float* pq, const float* qw, const float* inv_freq,
+                   const uint32_t* qpos, void* qo, uint32_t rows, uint32_t ldq, uint32_t nq, uint32_t hd,
+                   uint32_t rot, float eps);
+
+/* ---- Rope::kv_norm_rope (kernels/rope.rs:39-51) ----
+ * For `rows` rows of pkv (fp32, row stride ldkv): norm+RoPE of the nkv k heads (at column kcol) into the K
+ * cache kc and a copy of the nkv v heads (at column vcol) into the V cache vc, both bf16 [cache_rows,nkv,hd].
+ * With pos == NULL row r is at position pos0 + r and is written to cache row pos0 + r (the reference's
+ * form). With pos (u32 [rows], packed sequences) row r is rotated for position pos[r] and written to
+ * cache row r. Rows past cache_rows are refused (rope.rs:45). */
+int dc_kv_norm_rope(dc_ctx* ctx, void* stream, const float* pkv, const float* kw, const float* inv_freq, void* kc,
+                    void* vc, uint32_t rows, uint32_t ldkv, uint32_t kcol, uint32_t vcol, uint32_t pos0,
+                    const uint32_t* pos, uint32_t cache_rows, uint32_t nkv, uint32_t hd, uint32_t rot, float eps);
+
+/* ---- Attn::attention (kernels/attn.rs:81-118; spec cpu_ref.rs:167-188) ----
+ * Causal GQA attention: query row r (bf16 q [rows,nq,hd]) at position qpos[r] attends cache rows
+ * 0..=qpos[r] of the bf16 K/V caches [..,nkv,hd]; scale hd^-1/2; fp32 online softmax. `gate` (fp32,
+ * row stride ldg, already offset to the gate's first column; NULL = no gate) multiplies the output by
+ * sigmoid(gate). Writes bf16 y [rows, nq*hd]. hd must be 128.
+ * seq_start == NULL: one sequence. Otherwise seq_start is u32 [n_seq+1] row offsets of packed
+ * sequences (q rows and cache rows packed alike, qpos relative to the sequence) and max_len the
+ * longest sequence. */
+int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void* kc, const void* vc, const float* gate,
+                 const uint32_t* qpos, void* y, uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, uint32_t hd,
+                 const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
+
+/* ---- Conv::conv_silu_l2 (kernels/conv.rs:21-36; spec cpu_ref.rs:55-81) ----
+ * Depthwise causal conv (kernel 4) + SiLU over the qkv columns 0..(2nk+nv)*128 of `t` rows of p (fp32,
+ * row stride ldp); prev = the 3 raw rows before them (fp32 [3,conv_dim], oldest first; NULL = zeros);
+ * w fp32 [conv_dim,4]. Writes fp32 q,k [t,nk,dk] (L2-normed, q also scaled by dk^-1/2) and v [t,nv,dv].
+ * dk = dv = 128. Packed sequences: seq_start u32 [n_seq+1], prev [n_seq,3,conv_dim], max_len. */
+int dc_conv_silu_l2(dc_ctx* ctx, void* stream, const float* p, const float* prev, const float* w, float* q, float* k,
+                    float* v, uint32_t t, uint32_t ldp, uint32_t nk, uint32_t nv, uint32_t dk, uint32_t dv,
+                    const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
+
+/* ---- Conv::conv_state_update (kernels/conv.rs:38-46; spec cpu_ref.rs:86-95) ----
+ * prev_out = the 3 raw rows that end this chunk of t rows, drawing on prev_in (NULL = zeros) when t < 3.
+ * prev_out may be prev_in. */
+int dc_conv_state_update(dc_ctx* ctx, void* stream, const float* p, const float* prev_in, float* prev_out,
+                         uint32_t t, uint32_t ldp, uint32_t conv_dim);
+
+/* ---- Delta::gated_delta (kernels/delta.rs:53-100; spec cpu_ref.rs:101-129) ----
+ * The gated delta rule over t rows, fp32: q,k [t,nk,dk], v and o [t,nv,dv]; a,b read from rows of stride
+ * ldab (value head h at column h); a_log, dt_bias fp32 [nv]; state fp32 [nv][dv][dk]; state_in may be
+ * state_out (NULL state_in = zero state); state_out is written only with write_state. dk = dv = 128.
+ * Packed sequences: seq_start u32 [n_seq+1] and states [n_seq][nv][dv][dk]. */
+int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, const float* v, const float* a,
+                   const float* b, const float* a_log, const float* dt_bias, const float* state_in, float* state_out,
+                   float* o, uint32_t t, uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk,
+                   uint32_t dv, const uint32_t* seq_start, uint32_t n_seq);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,298 @@
+"""The attention-side and Gated-DeltaNet-side kernels on the GPU against the restated cpu_ref
+functions: head norm + RoPE, K/V cache write, causal GQA attention (fast and baseline, gated and
+un-gated, packed sequences), conv + SiLU + L2 norm, conv state update, the gated delta rule (state
+carry across chunks, packed sequences, the reference's by-hand known answer)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_ref
+from tests.util import assert_close, bf16, np32, randn, uniform
+
+pytestmark = pytest.mark.gpu
+
+
+def _u32(x):
+    return torch.as_tensor(np.asarray(x, dtype=np.int32)).cuda()
+
+
+# ------------------------------------------------------------------ rope
+@pytest.mark.parametrize("hd,rot,theta,nq", [(128, 128, 1e6, 32), (256, 64, 1e7, 16), (128, 32, 1e6, 4)])
+def test_q_norm_rope(k, hd, rot, theta, nq):
+    rows, ldq = 50, nq * hd + 64
+    pq = randn(1, rows, ldq)
+    w = randn(2, hd, std=0.02)
+    qpos = np.random.RandomState(3).randint(0, 8192, rows)
+    qpos[0], qpos[1] = 0, 8191
+    inv_freq = torch.from_numpy(cpu_ref.inv_freq(rot, theta))
+    qo = torch.empty(rows, nq, hd, dtype=torch.bfloat16, device="cuda")
+    k.rope.q_norm_rope(None, pq.cuda(), w.cuda(), inv_freq.cuda(), _u32(qpos), qo, rows, ldq, nq, hd, rot)
+    seg = np32(pq)[:, :nq * hd].reshape(rows, nq, hd)
+    want = cpu_ref.head_norm_rope(seg, np32(w), qpos[:, None].repeat(nq, 1), rot, theta)
+    # fp32 angles up to 8191 rad: sin/cos of the same fp32 angle, so only bf16 rounding remains
+    assert_close(np32(qo), want, atol=2e-3, rtol=2 ** -8, what="q_norm_rope")
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_kv_norm_rope(k, packed):
+    hd, rot, theta, nkv = 128, 128, 1e6, 8
+    rows, ld, kcol, vcol, pos0, cache_rows = 37, 6144, 4096, 5120, 11, 64
+    p = randn(4, rows, ld)
+    w = randn(5, hd, std=0.02)
+    inv_freq = torch.from_numpy(cpu_ref.inv_freq(rot, theta))
+    kc = torch.full((cache_rows, nkv, hd), 9.0, dtype=torch.bfloat16, device="cuda")
+    vc = torch.full((cache_rows, nkv, hd), 9.0, dtype=torch.bfloat16, device="cuda")
+    if packed:
+        pos = np.concatenate([np.arange(20), np.arange(17)])
+        k.rope.kv_norm_rope(None, p.cuda(), w.cuda(), inv_freq.cuda(), kc, vc, rows, ld, kcol, vcol, 0, cache_rows, nkv, hd, rot,
+                            pos=_u32(pos))
+        dst = np.arange(rows)
+    else:
+        pos = pos0 + np.arange(rows)
+        k.rope.kv_norm_rope(None, p.cuda(), w.cuda(), inv_freq.cuda(), kc, vc, rows, ld, kcol, vcol, pos0, cache_rows, nkv, hd, rot)
+        dst = pos
+    kseg = np32(p)[:, kcol:kcol + nkv * hd].reshape(rows, nkv, hd)
+    want_k = cpu_ref.head_norm_rope(kseg, np32(w), pos[:, None].repeat(nkv, 1), rot, theta)
+    assert_close(np32(kc)[dst], want_k, atol=2e-3, rtol=2 ** -8, what="k cache")
+    want_v = np32(bf16(p[:, vcol:vcol + nkv * hd])).reshape(rows, nkv, hd)
+    assert np.array_equal(np32(vc)[dst], want_v)
+    untouched = np.setdiff1d(np.arange(cache_rows), dst)
+    assert (np32(kc)[untouched] == 9.0).all() and (np32(vc)[untouched] == 9.0).all()
+
+
+def test_kv_cache_overrun_is_refused(k):
+    from decide_b200.kernels import KernelError
+
+    z = torch.zeros(8, 2048, device="cuda")
+    c = torch.zeros(8, 8, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(KernelError):
+        k.rope.kv_norm_rope(None, z, z, z, c, c, 8, 2048, 0, 1024, 1, 8, 8, 128, 128)
+
+
+# ------------------------------------------------------------- attention
+def _attn_case(seed, rows, nq, nkv, hd, gated, qpos=None, npos=None):
+    npos = npos or rows
+    q = bf16(randn(seed, rows, nq, hd))
+    kc = bf16(randn(seed + 1, npos, nkv, hd))
+    vc = bf16(randn(seed + 2, npos, nkv, hd))
+    gate = randn(seed + 3, rows, nq * hd + 32) if gated else None
+    qpos = np.arange(rows) if qpos is None else qpos
+    want = cpu_ref.attention(np32(q), qpos, np32(kc), np32(vc), np32(gate)[:, :nq * hd] if gated else None, nq, nkv, hd)
+    return q, kc, vc, gate, qpos, want
+
+
+@pytest.mark.parametrize("impl", ["fast", "baseline"])
+@pytest.mark.parametrize("rows,gated", [(1, True), (64, False), (65, True), (300, True), (603, False)])
+def test_attention_single_sequence(k, impl, rows, gated):
+    from decide_b200.kernels import Family, Impl
+
+    nq, nkv, hd = 8, 2, 128
+    q, kc, vc, gate, qpos, want = _attn_case(10 + rows, rows, nq, nkv, hd, gated)
+    y = torch.empty(rows, nq * hd, dtype=torch.bfloat16, device="cuda")
+    k.dev.set_impl(Family.Attn, Impl.Baseline if impl == "baseline" else Impl.Fast)
+    try:
+        k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda() if gated else None, _u32(qpos), y, rows,
+                         gate.shape[1] if gated else 0, nq, nkv, hd)
+        k.dev.check_status()
+    finally:
+        k.dev.set_impl(Family.Attn, Impl.Fast)
+    # P is rounded to bf16 before PV in the fast kernel (as the reference rounds to fp16): atol covers it
+    assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what=f"attention {impl} rows={rows}")
+
+
+def test_attention_scattered_query_positions(k):
+    """Query rows at arbitrary positions of a longer cache (the pruned-last-layer form, forward.rs:1176-1178)."""
+    nq, nkv, hd, npos = 4, 1, 128, 500
+    qpos = np.array([499, 3, 250, 0, 77, 77, 128, 64, 63])
+    q, kc, vc, gate, qpos, want = _attn_case(40, len(qpos), nq, nkv, hd, True, qpos=qpos, npos=npos)
+    y = torch.empty(len(qpos), nq * hd, dtype=torch.bfloat16, device="cuda")
+    k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda(), _u32(qpos), y, len(qpos), gate.shape[1], nq, nkv, hd)
+    assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
+
+
+@pytest.mark.parametrize("impl", ["fast", "baseline"])
+def test_attention_packed_sequences(k, impl):
+    from decide_b200.kernels import Family, Impl
+
+    nq, nkv, hd = 8, 2, 128
+    lens = [70, 1, 130, 64]
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total = int(starts[-1])
+    q = bf16(randn(50, total, nq, hd))
+    kc = bf16(randn(51, total, nkv, hd))
+    vc = bf16(randn(52, total, nkv, hd))
+    gate = randn(53, total, nq * hd)
+    qpos = np.concatenate([np.arange(n) for n in lens])
+    y = torch.empty(total, nq * hd, dtype=torch.bfloat16, device="cuda")
+    k.dev.set_impl(Family.Attn, Impl.Baseline if impl == "baseline" else Impl.Fast)
+    try:
+        k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda(), _u32(qpos), y, total, nq * hd, nq, nkv, hd,
+                         seq_start=_u32(starts), n_seq=len(lens), max_len=max(lens))
+    finally:
+        k.dev.set_impl(Family.Attn, Impl.Fast)
+    got = np32(y)
+    for s, n in enumerate(lens):
+        a, b = starts[s], starts[s + 1]
+        want = cpu_ref.attention(np32(q)[a:b], np.arange(n), np32(kc)[a:b], np32(vc)[a:b], np32(gate)[a:b], nq, nkv, hd)
+        assert_close(got[a:b], want, atol=6e-3, rtol=2 ** -7, what=f"packed attention seq {s}")
+
+
+# ------------------------------------------------------------------ conv
+@pytest.mark.parametrize("t,nk,nv,with_prev", [(1, 16, 16, True), (2, 16, 16, False), (100, 16, 16, True), (35, 16, 32, True)])
+def test_conv_silu_l2(k, t, nk, nv, with_prev):
+    conv_dim = (2 * nk + nv) * 128
+    ldp = conv_dim + 2080
+    p = randn(60, t, ldp)
+    prev = randn(61, 3, conv_dim) if with_prev else None
+    w = randn(62, conv_dim, 4, std=0.3)
+    q = torch.empty(t, nk, 128, device="cuda")
+    kk = torch.empty(t, nk, 128, device="cuda")
+    v = torch.empty(t, nv, 128, device="cuda")
+    k.conv.conv_silu_l2(None, p.cuda(), prev.cuda() if with_prev else None, w.cuda(), q, kk, v, t, ldp, nk, nv)
+    wq, wk, wv = cpu_ref.conv_silu_l2(np32(p), ldp, t, np32(prev) if with_prev else np.zeros((3, conv_dim), np.float32),
+                                     np32(w), nk, nv, 128, 128)
+    assert_close(np32(q), wq, atol=2e-6, rtol=2e-5, what="conv q")
+    assert_close(np32(kk), wk, atol=2e-6, rtol=2e-5, what="conv k")
+    assert_close(np32(v), wv, atol=2e-6, rtol=2e-5, what="conv v")
+
+
+def test_conv_packed_sequences_equal_separate_calls(k):
+    nk = nv = 16
+    conv_dim = 48 * 128
+    lens = [5, 40, 1, 17]
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total = int(starts[-1])
+    p = randn(63, total, conv_dim).cuda()
+    w = randn(64, conv_dim, 4, std=0.3).cuda()
+    outs = [torch.empty(total, 16, 128, device="cuda") for _ in range(3)]
+    k.conv.conv_silu_l2(None, p, None, w, *outs, total, conv_dim, nk, nv, seq_start=_u32(starts), n_seq=len(lens), max_len=max(lens))
+    for s, n in enumerate(lens):
+        a = int(starts[s])
+        ref = [torch.empty(n, 16, 128, device="cuda") for _ in range(3)]
+        k.conv.conv_silu_l2(None, p[a:a + n], None, w, *ref, n, conv_dim, nk, nv)
+        for got, want in zip(outs, ref):
+            assert torch.equal(got[a:a + n], want)
+
+
+@pytest.mark.parametrize("t", [1, 2, 3, 50])
+def test_conv_state_update(k, t):
+    conv_dim, ldp = 6144, 8224
+    p = randn(65, t, ldp)
+    prev = randn(66, 3, conv_dim)
+    buf = prev.clone().cuda()
+    k.conv.conv_state_update(None, p.cuda(), buf, buf, t, ldp, conv_dim)  # in place, as the engine does
+    want = cpu_ref.conv_state_update(np32(p), ldp, t, np32(prev), conv_dim)
+    assert np.array_equal(np32(buf), want)
+
+
+# ----------------------------------------------------------------- delta
+def _delta_inputs(seed, t, nk, nv):
+    q = randn(seed, t, nk, 128)
+    kk = randn(seed + 1, t, nk, 128)
+    q = q / q.norm(dim=-1, keepdim=True) * 128 ** -0.5
+    kk = kk / kk.norm(dim=-1, keepdim=True)
+    v = randn(seed + 2, t, nv, 128)
+    ldab = nv + 8
+    a = randn(seed + 3, t, ldab)
+    b = randn(seed + 4, t, ldab)
+    a_log = uniform(seed + 5, nv, lo=0.0, hi=math.log(16.0))
+    dt_bias = randn(seed + 6, nv, std=0.02, mean=1.0)
+    return q, kk, v, a, b, ldab, a_log, dt_bias
+
+
+def _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, state, t, nk, nv, write=True, **kw):
+    o = torch.empty(q.shape[0], nv, 128, device="cuda")
+    k.delta.gated_delta(None, q.cuda(), kk.cuda(), v.cuda(), a.cuda(), b.cuda(), a_log.cuda(), dt_bias.cuda(), state, state, o, t,
+                        ldab, write, nk, nv, **kw)
+    return o
+
+
+@pytest.mark.parametrize("t,nk,nv", [(1, 16, 16), (17, 16, 16), (130, 16, 16), (40, 16, 32)])
+def test_gated_delta_vs_sequential_reference(k, t, nk, nv):
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(70 + t, t, nk, nv)
+    s0 = randn(80, nv, 128, 128, std=0.1)
+    state = s0.clone().cuda()
+    o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, state, t, nk, nv)
+    ref_state = np32(s0).copy()
+    want = cpu_ref.gated_delta(np32(q), np32(kk), np32(v), np32(a), np32(b), ldab, np32(a_log), np32(dt_bias), ref_state, t, nk, nv, 128, 128)
+    assert_close(np32(o), want, atol=2e-5, rtol=2e-4, what="delta o")
+    assert_close(np32(state), ref_state, atol=2e-5, rtol=2e-4, what="delta state")
+
+
+def test_gated_delta_by_hand(k):
+    """The reference's known answer (cpu_ref.rs:222-236): one step, beta = 1, g = 1 -> o = v, S = k delta^T."""
+    nk = nv = 16
+    kk = torch.zeros(1, nk, 128)
+    kk[0, :, 0] = 1.0
+    v = torch.zeros(1, nv, 128)
+    v[0, 0, 5] = 3.0
+    a, b = torch.zeros(1, nv), torch.full((1, nv), 50.0)
+    a_log = torch.full((nv,), -float("inf"))
+    state = torch.zeros(nv, 128, 128, device="cuda")
+    o = _delta_gpu(k, kk.clone(), kk, v, a, b, nv, a_log, torch.zeros(nv), state, 1, nk, nv)
+    assert abs(o[0, 0, 5].item() - 3.0) < 1e-5
+    assert abs(state[0, 5, 0].item() - 3.0) < 1e-5
+    assert o.abs().sum().item() == pytest.approx(3.0, abs=1e-4)
+
+
+def test_gated_delta_chunk_continuation_is_exact(k):
+    """Whole sequence vs the same rows in two calls carrying the state (the engine's chunk continuation,
+    forward.rs:1214-1234): fp32 through memory, so bit-identical."""
+    t, nk, nv = 90, 16, 16
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(90, t, nk, nv)
+    s_whole = torch.zeros(nv, 128, 128, device="cuda")
+    o_whole = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, s_whole, t, nk, nv)
+    s_split = torch.zeros(nv, 128, 128, device="cuda")
+    cut = 33
+    o1 = _delta_gpu(k, q[:cut], kk[:cut], v[:cut], a[:cut], b[:cut], ldab, a_log, dt_bias, s_split, cut, nk, nv)
+    o2 = _delta_gpu(k, q[cut:], kk[cut:], v[cut:], a[cut:], b[cut:], ldab, a_log, dt_bias, s_split, t - cut, nk, nv)
+    assert torch.equal(torch.cat([o1, o2]), o_whole)
+    assert torch.equal(s_split, s_whole)
+
+
+def test_gated_delta_write_state_false_leaves_state(k):
+    t, nk, nv = 10, 16, 16
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(95, t, nk, nv)
+    state = torch.full((nv, 128, 128), 0.25, device="cuda")
+    _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, state, t, nk, nv, write=False)
+    assert (state == 0.25).all()
+
+
+def test_gated_delta_packed_sequences(k):
+    nk = nv = 16
+    lens = [20, 1, 45]
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total = int(starts[-1])
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(97, total, nk, nv)
+    states = torch.zeros(len(lens), nv, 128, 128, device="cuda")
+    o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, states, total, nk, nv, seq_start=_u32(starts), n_seq=len(lens))
+    for s, n in enumerate(lens):
+        lo, hi = int(starts[s]), int(starts[s + 1])
+        st = np.zeros((nv, 128, 128), np.float32)
+        want = cpu_ref.gated_delta(np32(q)[lo:hi], np32(kk)[lo:hi], np32(v)[lo:hi], np32(a)[lo:hi], np32(b)[lo:hi], ldab,
+                                   np32(a_log), np32(dt_bias), st, n, nk, nv, 128, 128)
+        assert_close(np32(o)[lo:hi], want, atol=2e-5, rtol=2e-4, what=f"packed delta seq {s}")
+        assert_close(np32(states[s]), st, atol=2e-5, rtol=2e-4, what=f"packed delta state {s}")
+
+
+@pytest.mark.parametrize("n_seq", [10, 40])
+def test_gated_delta_many_sequences_use_wider_lanes(k, n_seq):
+    """With many sequences the kernel gives each value column fewer lanes (4, then 1) than for a single
+    sequence (8); every variant must match the sequential reference."""
+    nk = nv = 16
+    rs = np.random.RandomState(n_seq)
+    lens = rs.randint(1, 24, n_seq).tolist()
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total = int(starts[-1])
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(120 + n_seq, total, nk, nv)
+    states = torch.zeros(n_seq, nv, 128, 128, device="cuda")
+    o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, states, total, nk, nv, seq_start=_u32(starts), n_seq=n_seq)
+    for s in (0, n_seq // 2, n_seq - 1):
+        lo, hi = int(starts[s]), int(starts[s + 1])
+        st = np.zeros((nv, 128, 128), np.float32)
+        want = cpu_ref.gated_delta(np32(q)[lo:hi], np32(kk)[lo:hi], np32(v)[lo:hi], np32(a)[lo:hi], np32(b)[lo:hi], ldab,
+                                   np32(a_log), np32(dt_bias), st, hi - lo, nk, nv, 128, 128)
+        assert_close(np32(o)[lo:hi], want, atol=2e-5, rtol=2e-4, what=f"delta seq {s} of {n_seq}")
+        assert_close(np32(states[s]), st, atol=2e-5, rtol=2e-4, what=f"delta state {s} of {n_seq}")
