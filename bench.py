@@ -1,0 +1,289 @@
+"""Prefill throughput of the B200 engine on the benchmark's full-model config, and the CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one batched prefill of 64 requests x 603 seeded token ids through the full synthetic
+36-layer hybrid model (3 Gated DeltaNet : 1 attention layer, hidden 2560, vocab 151936, tied bf16
+embedding, random-init weights) ending in the candidate-row head over 6 answer rows x 16 candidate
+ids per request. With N GPUs every rank runs its own 64 requests (requests share nothing: no
+collective on the data path), so per-GPU work is fixed ("weak" scaling); `value` is the tokens all
+ranks prefilled divided by the slowest rank's device time.
+
+`value` is timed with the batch resident in HBM; `e2e` is the same batch through the public
+host-buffer call (`Engine.logits`: ids, offsets, answer rows and candidates copied in from host
+memory, logits copied out, every step). `roofline` is the dominant kernel, the fused gate_up
+projection GEMM (tensor-bound): 2*M*N*K per launch divided by its average CUDA-event duration inside
+the timed steps, against the measured sustained bf16 peak. `cpu_baseline` times the reference's fp32
+CPU forward (oracle/gold_synth.py) on one request with all host cores.
+
+`--impl reference` times that CPU forward alone, one request per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+REQUESTS, TOKENS, ANSWERS, CANDS = 64, 603, 6, 16
+METRIC, UNIT = "prefill_tokens_per_s", "tokens/s"
+WORKLOAD = "configs[4]: full 36-layer hybrid model, 64 requests x 603 tokens, 6 answer rows x 16 candidates"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return {"bf16_tflops": j["bf16_tflops"], "bf16_tflops_sustained": j["bf16_tflops_sustained"], "hbm_gbs": j["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu: int):
+        self.gpu = gpu
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        rows = [l.split(", ") for l in Path(self.file.name).read_text().splitlines() if l.count(",") >= 8]
+        os.unlink(self.file.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(r[5 + i].strip().lower() == "active" for r in rows)]
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "power_w_max": max(float(r[3]) for r in rows),
+                "samples": len(rows), "reasons": reasons}
+
+
+def cpu_gold_setup(dims, seed):
+    import torch
+
+    from decide_b200.synth import synth_state_dict
+    from oracle import gold_synth
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    sd = synth_state_dict(dims, seed)
+    return sd, gold_synth.build_model(dims, sd)
+
+
+def run_reference(args):
+    """The reference arm: the fp32 CPU forward the reference's gold generator runs, one request per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    from decide_b200.synth import synth_batch
+    from decide_b200.weights import BASELINE_DIMS as dims
+    from oracle import gold_synth
+
+    sd, model = cpu_gold_setup(dims, seed=1)
+    cores = torch.get_num_threads()
+    batch = synth_batch(dims, args.steps + args.warmup, TOKENS, seed=2, n_answers=ANSWERS, n_cand=CANDS, max_cand=CANDS)
+    times = []
+    for s in range(args.steps + args.warmup):
+        one = type(batch)(batch.ids[s * TOKENS:(s + 1) * TOKENS], np.array([0, TOKENS], np.uint32),
+                          batch.ans_rows[s * ANSWERS:(s + 1) * ANSWERS] - np.uint32(s * TOKENS), batch.cand[s * ANSWERS:(s + 1) * ANSWERS],
+                          batch.ncand[s * ANSWERS:(s + 1) * ANSWERS])
+        _, sec = gold_synth.gold_batch_logits(model, one, CANDS)
+        if s >= args.warmup:
+            times.append(sec)
+    total = sum(times)
+    value = TOKENS * len(times) / total
+    sample = f"{len(times)} request(s) of {TOKENS} tokens, all 36 layers, fp32, torch {torch.__version__} CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "step": "one 603-token request on the host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_engine(args):
+    import torch
+    import torch.distributed as dist
+
+    from decide_b200 import head
+    from decide_b200.engine import Engine
+    from decide_b200.kernels import Device
+    from decide_b200.synth import synth_batch, synth_fused_on_device
+    from decide_b200.weights import BASELINE_DIMS as dims, fuse_layer
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = Device(local)
+    cuda = torch.device("cuda", local)
+
+    with_cpu = (world == 1 and rank == 0 and not args.no_cpu_baseline)
+    cpu = None
+    if with_cpu:
+        t0 = time.perf_counter()
+        sd, gold = cpu_gold_setup(dims, seed=1)
+        fused = [{k: v.to(cuda) for k, v in fuse_layer(sd, l, dims).items()} for l in range(dims.n_layers)]
+        embed, final_norm = sd["embed_tokens.weight"].to(cuda), sd["norm.weight"].to(cuda)
+        cpu = {"setup_s": time.perf_counter() - t0}
+    else:
+        fused, embed, final_norm = synth_fused_on_device(dims, 1 + rank, cuda)
+    rows = REQUESTS * TOKENS
+    eng = Engine(dims, dev=dev, max_rows=rows, max_seqs=REQUESTS, max_answers=REQUESTS * ANSWERS, max_cand=CANDS,
+                 fused_layers=fused, embed=embed, final_norm=final_norm)
+    batch = synth_batch(dims, REQUESTS, TOKENS, seed=100 + rank, n_answers=ANSWERS, n_cand=CANDS, max_cand=CANDS)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=cuda)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    stream = torch.cuda.current_stream()
+    # ---- warm-up (also fills the tensor-map cache and leaves the batch resident on the device)
+    logits = None
+    for _ in range(max(args.warmup, 3)):
+        logits = eng.logits(batch)
+    eng.profile()
+
+    # ---- device-resident timing: the headline `value`
+    sampler = ClockSampler(local)
+    eng.set_profiling(True)
+    barrier()
+    sampler.start()
+    launches0 = dev.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        eng.forward_resident(batch)
+    e1.record(stream)
+    barrier()
+    launches = dev.launches - launches0
+    ms_value = max_over_ranks(e0.elapsed_time(e1))
+    prof = {name: (ms, calls) for name, ms, calls in eng.profile()}
+    eng.set_profiling(False)
+
+    # ---- end to end through the host-buffer call
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        logits = eng.logits(batch)
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    dev.check_status()
+
+    tokens = world * rows * args.steps
+    value = tokens / (ms_value / 1e3)
+    e2e = tokens / (ms_e2e / 1e3)
+    h2d = rows * 4 * 2 + (REQUESTS + 1) * 4 + REQUESTS * ANSWERS * 4 * 2 + REQUESTS * ANSWERS * CANDS * 4
+    d2h = REQUESTS * ANSWERS * CANDS * 4
+
+    peaks = measured_peaks()
+    gu_ms, gu_calls = prof.get("gemm_gate_up", (0.0, 0))
+    flops_per_launch = 2.0 * rows * (2 * dims.inter) * dims.hidden
+    achieved = flops_per_launch / (gu_ms / gu_calls * 1e-3) / 1e12 if gu_calls else None
+    gemm_ms = sum(ms for n, (ms, _) in prof.items() if n.startswith("gemm_"))
+    gemm_tflops = dims.gemm_flops_per_row() * rows * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+    traffic = None
+    tf = ROOT / "profiles" / "gemm_gate_up_traffic.json"
+    if tf.exists():
+        traffic = json.loads(tf.read_text()).get("dram_bytes_per_launch_at_bench_size")
+
+    cpu_baseline = None
+    if with_cpu and rank == 0:
+        from oracle import gold_synth
+
+        one = type(batch)(batch.ids[:TOKENS], np.array([0, TOKENS], np.uint32), batch.ans_rows[:ANSWERS], batch.cand[:ANSWERS], batch.ncand[:ANSWERS])
+        want, sec = gold_synth.gold_batch_logits(gold, one, CANDS)
+        got = logits[:ANSWERS]
+        pg, dg = head.decide(got, one.ncand)
+        pw, dw = head.decide(want, one.ncand)
+        cpu_baseline = {"value": TOKENS / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": f"1 request of {TOKENS} tokens (request 0 of the batch), all 36 layers, fp32 CPU forward: {sec:.1f} s",
+                        "parity_on_sample": {"max_abs_dlogit": float(np.abs(got - want).max()), "max_abs_dp": float(np.abs(pg - pw).max()),
+                                             "decisions_equal": bool((dg == dw).all())}}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests_per_gpu": REQUESTS, "tokens_per_request": TOKENS,
+                       "l2": "inputs larger than L2: 8.2 GB of weights stream through every step", "sharding": "by request, no collectives"},
+            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"kernel": "gemm_tc_kernel<256, SwiGLU> (gate_up projection)", "bound": "tensor", "achieved": achieved,
+                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"] if achieved else None,
+                         "peak_source": f"{peaks['source']} (sustained cuBLAS bf16)", "traffic": traffic,
+                         "flops_per_launch": flops_per_launch, "launches_timed": gu_calls},
+            "gemm_tflops_all_projections": gemm_tflops,
+            "gemm_frac_of_peak": gemm_tflops / peaks["bf16_tflops_sustained"] if gemm_tflops else None,
+            "per_op_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(prof.items(), key=lambda kv: -kv[1][0])},
+            "cpu_baseline": cpu_baseline,
+        }))
+    eng.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU forward (weights are then drawn on the GPU)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_engine(args)
+
+
+if __name__ == "__main__":
+    main()

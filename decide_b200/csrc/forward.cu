@@ -1,0 +1,418 @@
+// The prefill driver: the op sequence of the reference's Forward (crates/decide-engine/src/
+// forward.rs:1129-1142 encode_chunk, 1191-1254 encode_layer, 1266-1276 encode_mlp, 1312-1328 head)
+// over the dc_* kernels, for a batch of packed requests on one stream.
+//
+// The model object owns the activation buffers (forward.rs:124-180 does the same) and borrows the
+// weights. Requests are concatenated row-wise into one M for every GEMM and row kernel; conv, delta
+// rule and attention take the per-request row offsets. Nothing is allocated, JIT-compiled or
+// tensor-map-encoded by a forward after the first one of a given shape.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+struct dc_model {
+    dc_ctx* ctx = nullptr;
+    dc_dims d{};
+    std::vector<dc_layer_weights> layers;
+    const void* embed = nullptr;
+    const float* final_norm = nullptr;
+    uint32_t max_rows = 0, max_seqs = 0, max_answers = 0, max_cand = 0;
+    // derived
+    uint32_t key_dim = 0, value_dim = 0, conv_dim = 0, lin_in_n = 0, q_dim = 0, kv_dim = 0, att_in_n = 0, p_ld = 0;
+    // device buffers
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    float *x = nullptr, *p = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *xs = nullptr, *logits = nullptr,
+          *inv_freq = nullptr;
+    void *h = nullptr, *g = nullptr, *mlp = nullptr, *qo = nullptr, *kc = nullptr, *vc = nullptr;
+    uint32_t *ids = nullptr, *pos = nullptr, *seq_start = nullptr, *ans_rows = nullptr, *cand = nullptr, *ncand = nullptr;
+    // pinned host staging for the host-buffer entry point
+    char* host = nullptr;
+    size_t host_bytes = 0;
+    // per-op profiler (the reference's DECIDE_PROFILE_PERKERNEL table, crates/decide-metal/src/profile.rs:29-101)
+    uint32_t layer_limit = 0;  // 0 = all layers
+    bool profiling = false;
+    struct Span {
+        const char* name;
+        cudaEvent_t a, b;
+    };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> event_pool;
+    std::vector<std::pair<std::string, std::pair<double, uint64_t>>> totals;
+};
+
+namespace {
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool is_attention_layer(const dc_dims& d, uint32_t l) { return (l + 1) % d.full_attn_interval == 0; }
+
+struct Prof {
+    dc_model* m;
+    cudaStream_t s;
+    const char* name;
+    size_t idx = 0;
+    Prof(dc_model* m_, cudaStream_t s_, const char* n) : m(m_), s(s_), name(n) {
+        if (!m->profiling) return;
+        auto get = [&]() {
+            if (m->event_pool.empty()) {
+                cudaEvent_t e;
+                cudaEventCreate(&e);
+                return e;
+            }
+            cudaEvent_t e = m->event_pool.back();
+            m->event_pool.pop_back();
+            return e;
+        };
+        dc_model::Span sp{name, get(), get()};
+        cudaEventRecord(sp.a, s);
+        idx = m->spans.size();
+        m->spans.push_back(sp);
+    }
+    ~Prof() {
+        if (m->profiling) cudaEventRecord(m->spans[idx].b, s);
+    }
+};
+
+#define RUN(name, call)                  \
+    do {                                 \
+        Prof _p(m, s, name);             \
+        int _rc = (call);                \
+        if (_rc != DC_OK) return _rc;    \
+    } while (0)
+
+int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, uint32_t max_len, uint32_t n_ans) {
+    dc_ctx* c = m->ctx;
+    const dc_dims& d = m->d;
+    const uint32_t H = d.hidden;
+    void* st = s;
+    RUN("embed", dc_embed(c, st, m->ids, m->embed, m->x, rows, H));
+    const uint32_t n_run = m->layer_limit ? std::min(m->layer_limit, d.n_layers) : d.n_layers;
+    for (uint32_t l = 0; l < n_run; ++l) {
+        const dc_layer_weights& w = m->layers[l];
+        RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.in_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
+        uint32_t out_k;
+        if (!is_attention_layer(d, l)) {
+            const uint32_t ld = m->lin_in_n;
+            RUN("gemm_gdn_in", dc_gemm(c, st, m->h, w.w_in, m->p, rows, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
+            RUN("conv_silu_l2", dc_conv_silu_l2(c, st, m->p, nullptr, w.conv_w, m->q, m->k, m->v, rows, ld, d.gdn_nk, d.gdn_nv,
+                                                d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
+            const float* b = m->p + m->conv_dim + m->value_dim;  // fused order qkv|z|b|a (config.rs:14-17)
+            const float* a = b + d.gdn_nv;
+            RUN("gated_delta", dc_gated_delta(c, st, m->q, m->k, m->v, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
+                                              d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq));
+            RUN("gated_rmsnorm_silu", dc_gated_rmsnorm_silu(c, st, m->o, m->p + m->conv_dim, w.gnorm, m->g, rows, d.gdn_nv, d.gdn_dv, ld, d.eps));
+            out_k = m->value_dim;
+        } else {
+            const uint32_t ld = m->att_in_n;
+            const uint32_t kcol = d.attn_gate ? 2 * m->q_dim : m->q_dim;  // q|gate|k|v or q|k|v (config.rs:25-29)
+            const uint32_t vcol = kcol + m->kv_dim;
+            RUN("gemm_attn_in", dc_gemm(c, st, m->h, w.w_in, m->p, rows, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
+            RUN("q_norm_rope", dc_q_norm_rope(c, st, m->p, w.q_norm, m->inv_freq, m->pos, m->qo, rows, ld, d.nq, d.head_dim, d.rot_dim, d.eps));
+            RUN("kv_norm_rope", dc_kv_norm_rope(c, st, m->p, w.k_norm, m->inv_freq, m->kc, m->vc, rows, ld, kcol, vcol, 0, m->pos,
+                                                m->max_rows, d.nkv, d.head_dim, d.rot_dim, d.eps));
+            RUN("attention", dc_attention(c, st, m->qo, m->kc, m->vc, d.attn_gate ? m->p + m->q_dim : nullptr, m->pos, m->g, rows, ld, d.nq,
+                                          d.nkv, d.head_dim, m->seq_start, n_seq, max_len));
+            out_k = m->q_dim;
+        }
+        RUN("gemm_out", dc_gemm(c, st, m->g, w.w_out, m->x, rows, H, out_k, out_k, out_k, H, DC_EPI_ADD_F32, d.swiglu_block));
+        RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.post_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
+        RUN("gemm_gate_up", dc_gemm(c, st, m->h, w.w_gu, m->mlp, rows, 2 * d.inter, H, H, H, d.inter, DC_EPI_SWIGLU_BF16, d.swiglu_block));
+        RUN("gemm_down", dc_gemm(c, st, m->mlp, w.w_down, m->x, rows, H, d.inter, d.inter, d.inter, H, DC_EPI_ADD_F32, d.swiglu_block));
+    }
+    if (n_ans && n_run == d.n_layers) {
+        RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows, m->xs, n_ans, H));
+        RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
+    }
+    return DC_OK;
+}
+
+void collect_profile(dc_model* m) {
+    for (auto& sp : m->spans) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, sp.a, sp.b);
+        auto it = std::find_if(m->totals.begin(), m->totals.end(), [&](auto& e) { return e.first == sp.name; });
+        if (it == m->totals.end()) m->totals.push_back({sp.name, {ms, 1}});
+        else {
+            it->second.first += ms;
+            it->second.second += 1;
+        }
+        m->event_pool.push_back(sp.a);
+        m->event_pool.push_back(sp.b);
+    }
+    m->spans.clear();
+}
+
+}  // namespace
+
+extern "C" {
+
+dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weights* layers, const void* embed,
+                          const float* final_norm, uint32_t max_rows, uint32_t max_seqs, uint32_t max_answers,
+                          uint32_t max_cand) {
+    if (!ctx) return nullptr;
+    auto fail = [&](const char* msg) -> dc_model* {
+        dc_fail(ctx, DC_INVALID_ARG, "dc_model_create: %s", msg);
+        return nullptr;
+    };
+    if (!dims || !layers || !embed || !final_norm) return fail("null argument");
+    const dc_dims& d = *dims;
+    if (d.hidden % 32 || d.inter % 32 || d.hidden == 0 || d.n_layers == 0) return fail("hidden and intermediate sizes must be multiples of 32");
+    if (d.head_dim != 128) return fail("attention head_dim must be 128");
+    if (d.gdn_dk != 128 || d.gdn_dv != 128) return fail("Gated DeltaNet head dims must be 128");
+    if (d.nkv == 0 || d.nq % d.nkv || d.gdn_nk == 0 || d.gdn_nv % d.gdn_nk) return fail("head counts do not divide");
+    if (d.full_attn_interval == 0 || d.swiglu_block != 16) return fail("full_attn_interval must be positive and swiglu_block 16");
+    if (d.rot_dim % 8 || d.rot_dim > d.head_dim || d.rot_dim == 0) return fail("rotary dims must be a multiple of 8 within head_dim");
+    if (max_rows == 0 || max_seqs == 0 || max_cand == 0) return fail("capacities must be positive");
+    if (d.gdn_nv % 4) return fail("the number of value heads must be a multiple of 4 (row alignment of the fused projection)");
+
+    dc_model* m = new dc_model();
+    m->ctx = ctx;
+    m->d = d;
+    m->layers.assign(layers, layers + d.n_layers);
+    m->embed = embed;
+    m->final_norm = final_norm;
+    m->max_rows = max_rows;
+    m->max_seqs = max_seqs;
+    m->max_answers = max_answers ? max_answers : 1;
+    m->max_cand = max_cand;
+    m->key_dim = d.gdn_nk * d.gdn_dk;
+    m->value_dim = d.gdn_nv * d.gdn_dv;
+    m->conv_dim = 2 * m->key_dim + m->value_dim;
+    m->lin_in_n = m->conv_dim + m->value_dim + 2 * d.gdn_nv;
+    m->q_dim = d.nq * d.head_dim;
+    m->kv_dim = d.nkv * d.head_dim;
+    m->att_in_n = (d.attn_gate ? 2 : 1) * m->q_dim + 2 * m->kv_dim;
+    m->p_ld = std::max(m->lin_in_n, m->att_in_n);
+    if (m->lin_in_n % 32) {
+        delete m;
+        return fail("the fused Gated DeltaNet projection width must be a multiple of 32");
+    }
+
+    const size_t R = max_rows, A = m->max_answers;
+    struct Want {
+        void** ptr;
+        size_t bytes;
+    };
+    std::vector<Want> wants = {
+        {reinterpret_cast<void**>(&m->x), R * d.hidden * 4},
+        {&m->h, R * d.hidden * 2},
+        {reinterpret_cast<void**>(&m->p), R * m->p_ld * 4},
+        {reinterpret_cast<void**>(&m->q), R * m->key_dim * 4},
+        {reinterpret_cast<void**>(&m->k), R * m->key_dim * 4},
+        {reinterpret_cast<void**>(&m->v), R * m->value_dim * 4},
+        {reinterpret_cast<void**>(&m->o), R * m->value_dim * 4},
+        {&m->g, R * std::max(m->value_dim, m->q_dim) * 2},
+        {&m->mlp, R * d.inter * 2},
+        {&m->qo, R * m->q_dim * 2},
+        {&m->kc, R * m->kv_dim * 2},
+        {&m->vc, R * m->kv_dim * 2},
+        {reinterpret_cast<void**>(&m->xs), A * d.hidden * 4},
+        {reinterpret_cast<void**>(&m->logits), A * max_cand * 4},
+        {reinterpret_cast<void**>(&m->inv_freq), (d.rot_dim / 2) * 4},
+        {reinterpret_cast<void**>(&m->ids), R * 4},
+        {reinterpret_cast<void**>(&m->pos), R * 4},
+        {reinterpret_cast<void**>(&m->seq_start), (static_cast<size_t>(max_seqs) + 1) * 4},
+        {reinterpret_cast<void**>(&m->ans_rows), A * 4},
+        {reinterpret_cast<void**>(&m->cand), A * max_cand * 4},
+        {reinterpret_cast<void**>(&m->ncand), A * 4},
+    };
+    size_t total = 0;
+    for (auto& wnt : wants) total += align_up(wnt.bytes, 1024);
+    cudaSetDevice(ctx->device);
+    if (cudaMalloc(&m->arena, total) != cudaSuccess) {
+        cudaGetLastError();
+        delete m;
+        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate %zu bytes of activations", total);
+        return nullptr;
+    }
+    m->arena_bytes = total;
+    size_t off = 0;
+    for (auto& wnt : wants) {
+        *wnt.ptr = m->arena + off;
+        off += align_up(wnt.bytes, 1024);
+    }
+    // RoPE inverse frequencies in fp32, as the reference and HF compute them (config.rs:44-46)
+    std::vector<float> f(d.rot_dim / 2);
+    for (uint32_t i = 0; i < d.rot_dim / 2; ++i)
+        f[i] = 1.0f / powf(d.rope_theta, static_cast<float>(2 * i) / static_cast<float>(d.rot_dim));
+    cudaMemcpy(m->inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice);
+    m->host_bytes = align_up(R * 4, 64) * 2 + align_up((max_seqs + 1) * 4, 64) + align_up(A * 4, 64) * 2 + align_up(A * max_cand * 4, 64) * 2;
+    if (cudaMallocHost(&m->host, m->host_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(m->arena);
+        delete m;
+        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate pinned staging");
+        return nullptr;
+    }
+    return m;
+}
+
+void dc_model_destroy(dc_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    collect_profile(m);
+    for (auto e : m->event_pool) cudaEventDestroy(e);
+    if (m->arena) cudaFree(m->arena);
+    if (m->host) cudaFreeHost(m->host);
+    delete m;
+}
+
+size_t dc_model_activation_bytes(dc_model* m) { return m ? m->arena_bytes : 0; }
+
+int dc_model_set_layer_limit(dc_model* m, uint32_t n) {
+    if (!m) return DC_INVALID_ARG;
+    m->layer_limit = n;
+    return DC_OK;
+}
+
+int dc_model_set_profiling(dc_model* m, uint32_t on) {
+    if (!m) return DC_INVALID_ARG;
+    m->profiling = on != 0;
+    return DC_OK;
+}
+
+// Writes "name total_ms calls" lines, largest first; returns the length needed.
+size_t dc_model_profile(dc_model* m, char* buf, size_t len) {
+    if (!m) return 0;
+    cudaDeviceSynchronize();
+    collect_profile(m);
+    auto rows = m->totals;
+    std::sort(rows.begin(), rows.end(), [](auto& a, auto& b) { return a.second.first > b.second.first; });
+    std::string out;
+    char line[160];
+    for (auto& r : rows) {
+        snprintf(line, sizeof line, "%s %.4f %llu\n", r.first.c_str(), r.second.first, static_cast<unsigned long long>(r.second.second));
+        out += line;
+    }
+    if (buf && len) snprintf(buf, len, "%s", out.c_str());
+    m->totals.clear();
+    return out.size();
+}
+
+static int check_batch(dc_model* m, uint32_t n_seq, const uint32_t* seq_start, uint32_t n_ans, uint32_t* rows, uint32_t* max_len) {
+    dc_ctx* ctx = m->ctx;
+    DC_REQUIRE(ctx, n_seq >= 1 && n_seq <= m->max_seqs, "forward: %u requests (capacity %u)", n_seq, m->max_seqs);
+    DC_REQUIRE(ctx, seq_start[0] == 0, "forward: seq_start[0] must be 0");
+    uint32_t ml = 0;
+    for (uint32_t i = 0; i < n_seq; ++i) {
+        DC_REQUIRE(ctx, seq_start[i + 1] > seq_start[i], "forward: request %u is empty", i);
+        ml = std::max(ml, seq_start[i + 1] - seq_start[i]);
+    }
+    *rows = seq_start[n_seq];
+    *max_len = ml;
+    DC_REQUIRE(ctx, *rows <= m->max_rows, "forward: %u rows (capacity %u)", *rows, m->max_rows);
+    DC_REQUIRE(ctx, n_ans <= m->max_answers, "forward: %u answer rows (capacity %u)", n_ans, m->max_answers);
+    return DC_OK;
+}
+
+// Whole prefill with HOST buffers: copies ids / offsets / answers in, runs every layer, copies the
+// candidate logits out and waits. The analogue of Forward::logits (forward.rs:704-731) for a batch.
+int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint32_t* seq_start, uint32_t n_seq,
+                     const uint32_t* ans_rows, const uint32_t* cand, const uint32_t* ncand, uint32_t n_ans, float* logits) {
+    if (!m) return DC_INVALID_ARG;
+    dc_ctx* ctx = m->ctx;
+    DC_REQUIRE(ctx, ids && seq_start && (n_ans == 0 || (ans_rows && cand && ncand && logits)), "prefill: null argument");
+    uint32_t rows = 0, max_len = 0;
+    int rc = check_batch(m, n_seq, seq_start, n_ans, &rows, &max_len);
+    if (rc != DC_OK) return rc;
+    for (uint32_t i = 0; i < n_ans; ++i) {
+        DC_REQUIRE(ctx, ans_rows[i] < rows, "prefill: answer row %u is past the %u rows", ans_rows[i], rows);
+        DC_REQUIRE(ctx, ncand[i] >= 1 && ncand[i] <= m->max_cand, "prefill: answer %u has %u candidates (1..%u)", i, ncand[i], m->max_cand);
+        for (uint32_t j = 0; j < ncand[i]; ++j)
+            DC_REQUIRE(ctx, cand[static_cast<size_t>(i) * m->max_cand + j] < m->d.vocab, "prefill: candidate id out of the vocabulary");
+    }
+    for (uint32_t i = 0; i < rows; ++i) DC_REQUIRE(ctx, ids[i] < m->d.vocab, "prefill: token id %u out of the vocabulary", ids[i]);
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // stage through pinned memory: ids, positions, offsets, answers
+    char* hp = m->host;
+    auto take = [&](size_t bytes) {
+        char* r = hp;
+        hp += align_up(bytes, 64);
+        return r;
+    };
+    uint32_t* h_ids = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_rows) * 4));
+    uint32_t* h_pos = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_rows) * 4));
+    uint32_t* h_seq = reinterpret_cast<uint32_t*>(take((static_cast<size_t>(m->max_seqs) + 1) * 4));
+    uint32_t* h_ans = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
+    uint32_t* h_ncand = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
+    uint32_t* h_cand = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * m->max_cand * 4));
+    float* h_logits = reinterpret_cast<float*>(take(static_cast<size_t>(m->max_answers) * m->max_cand * 4));
+    memcpy(h_ids, ids, static_cast<size_t>(rows) * 4);
+    memcpy(h_seq, seq_start, (static_cast<size_t>(n_seq) + 1) * 4);
+    for (uint32_t i = 0; i < n_seq; ++i)
+        for (uint32_t r = seq_start[i]; r < seq_start[i + 1]; ++r) h_pos[r] = r - seq_start[i];
+    if (n_ans) {
+        memcpy(h_ans, ans_rows, static_cast<size_t>(n_ans) * 4);
+        memcpy(h_ncand, ncand, static_cast<size_t>(n_ans) * 4);
+        memcpy(h_cand, cand, static_cast<size_t>(n_ans) * m->max_cand * 4);
+    }
+    cudaError_t e = cudaMemcpyAsync(m->ids, h_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->pos, h_pos, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->seq_start, h_seq, (static_cast<size_t>(n_seq) + 1) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ans_rows, h_ans, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ncand, h_ncand, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->cand, h_cand, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: host-to-device copy failed: %s", cudaGetErrorString(e));
+
+    rc = forward_device(m, s, rows, n_seq, max_len, n_ans);
+    if (rc != DC_OK) return rc;
+    if (n_ans) {
+        e = cudaMemcpyAsync(h_logits, m->logits, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyDeviceToHost, s);
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: device-to-host copy failed: %s", cudaGetErrorString(e));
+    }
+    rc = dc_check_status(ctx, s);  // synchronises
+    if (rc != DC_OK) return rc;
+    if (n_ans) {
+        memcpy(logits, h_logits, static_cast<size_t>(n_ans) * m->max_cand * 4);
+        // non-finite logits are an error, as forward.rs:906-913
+        for (uint32_t i = 0; i < n_ans; ++i)
+            for (uint32_t j = 0; j < ncand[i]; ++j)
+                if (!std::isfinite(logits[static_cast<size_t>(i) * m->max_cand + j]))
+                    return dc_fail(ctx, DC_CUDA_ERROR, "prefill: non-finite logit for answer %u candidate %u", i, j);
+    }
+    return DC_OK;
+}
+
+// The same pass with inputs already resident in the model's device buffers (set by a previous
+// dc_model_prefill of the same batch): enqueues only, no copies, no synchronisation.
+int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_start, uint32_t n_seq, uint32_t n_ans) {
+    if (!m) return DC_INVALID_ARG;
+    uint32_t rows = 0, max_len = 0;
+    int rc = check_batch(m, n_seq, seq_start, n_ans, &rows, &max_len);
+    if (rc != DC_OK) return rc;
+    return forward_device(m, static_cast<cudaStream_t>(stream), rows, n_seq, max_len, n_ans);
+}
+
+// Device address of a named activation buffer, for per-layer parity checks
+// (the reference's debug_layers, forward.rs:778-797).
+void* dc_model_buffer(dc_model* m, const char* name) {
+    if (!m || !name) return nullptr;
+    const std::string n(name);
+    if (n == "x") return m->x;
+    if (n == "h") return m->h;
+    if (n == "p") return m->p;
+    if (n == "g") return m->g;
+    if (n == "mlp") return m->mlp;
+    if (n == "logits") return m->logits;
+    if (n == "xs") return m->xs;
+    return nullptr;
+}
+
+// Synchronous copy of the first `bytes` bytes of a named activation buffer to host memory.
+int dc_model_read_buffer(dc_model* m, const char* name, void* dst, size_t bytes) {
+    if (!m) return DC_INVALID_ARG;
+    void* src = dc_model_buffer(m, name);
+    if (!src || !dst) return dc_fail(m->ctx, DC_INVALID_ARG, "dc_model_read_buffer: unknown buffer or null destination");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return dc_fail(m->ctx, DC_CUDA_ERROR, "dc_model_read_buffer: %s", cudaGetErrorString(e));
+    return DC_OK;
+}
+
+}  // extern "C"

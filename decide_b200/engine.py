@@ -1,0 +1,101 @@
+"""The public entry: a prefill engine for one GPU.
+
+`Engine(dims, state_dict)` converts checkpoint-layout tensors to the fused layouts, uploads them and
+creates the C++ model (libdecide_cuda.so `dc_model_*`); `engine.logits(batch)` runs one batched
+prefill from host buffers and returns the candidate logits. This is the slice of the reference's
+`Engine`/`Forward` (crates/decide-engine/src/engine.rs:226-230, forward.rs:704-731) that the hot path
+needs: token ids in, candidate-row logits out. torch holds the device memory of the weights; every
+computation happens in the library.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from .kernels import Device, KernelError, _stream
+from .synth import Batch
+from .weights import LAYER_FIELDS, CDims, CLayerWeights, Dims, fuse_layer
+
+
+def _u32p(a: np.ndarray):
+    assert a.dtype == np.uint32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+class Engine:
+    def __init__(self, dims: Dims, state_dict: dict | None = None, dev: Device | None = None, max_rows: int = 4096,
+                 max_seqs: int = 64, max_answers: int = 1024, max_cand: int = 16, fused_layers: list | None = None,
+                 embed: torch.Tensor | None = None, final_norm: torch.Tensor | None = None):
+        """Either `state_dict` (checkpoint names, CPU tensors) or already fused device tensors
+        (`fused_layers`, `embed`, `final_norm`) must be given."""
+        self.dims = dims
+        self.dev = dev or Device(0)
+        self.lib = self.dev.lib
+        self.max_cand = max_cand
+        cuda = torch.device("cuda", self.dev.device)
+        if fused_layers is None:
+            fused_layers = []
+            for l in range(dims.n_layers):
+                fused_layers.append({k: v.to(cuda) for k, v in fuse_layer(state_dict, l, dims).items()})
+            embed = state_dict["embed_tokens.weight"].to(torch.bfloat16).to(cuda)
+            final_norm = state_dict["norm.weight"].to(torch.float32).to(cuda)
+        self.layers, self.embed, self.final_norm = fused_layers, embed, final_norm  # keep the device tensors alive
+        arr = (CLayerWeights * dims.n_layers)()
+        for l, lw in enumerate(fused_layers):
+            for name in LAYER_FIELDS:
+                setattr(arr[l], name, lw[name].data_ptr() if name in lw else None)
+        cd = CDims.of(dims)
+        self.handle = self.lib.dc_model_create(self.dev.handle, ctypes.byref(cd), arr, embed.data_ptr(), final_norm.data_ptr(),
+                                               max_rows, max_seqs, max_answers, max_cand)
+        if not self.handle:
+            raise KernelError(1, self.dev.last_error())
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.dc_model_destroy(self.handle)
+            self.handle = None
+
+    def _call(self, name, *args):
+        rc = getattr(self.lib, name)(self.handle, *args)
+        if rc != 0:
+            raise KernelError(rc, self.dev.last_error())
+
+    def logits(self, batch: Batch, stream=None) -> np.ndarray:
+        """One batched prefill from host buffers: returns fp32 logits [n_ans, max_cand] (synchronous)."""
+        n_ans = len(batch.ans_rows)
+        out = np.zeros((n_ans, self.max_cand), dtype=np.float32)
+        assert batch.cand.shape == (n_ans, self.max_cand)
+        self._call("dc_model_prefill", _stream(stream), _u32p(batch.ids), _u32p(batch.seq_start), batch.n_seq, _u32p(batch.ans_rows),
+                   _u32p(batch.cand), _u32p(batch.ncand), n_ans, out.ctypes.data_as(ctypes.c_void_p))
+        return out
+
+    def forward_resident(self, batch: Batch, stream=None):
+        """Enqueues the same pass over the inputs the last `logits(batch)` left on the device."""
+        self._call("dc_model_forward_resident", _stream(stream), _u32p(batch.seq_start), batch.n_seq, len(batch.ans_rows))
+
+    def set_layer_limit(self, n: int):
+        self._call("dc_model_set_layer_limit", n)
+
+    def buffer(self, name: str, shape, dtype=np.float32) -> np.ndarray:
+        """A host copy of a named activation buffer's leading elements (per-layer parity checks)."""
+        out = np.empty(shape, dtype=dtype)
+        self._call("dc_model_read_buffer", name.encode(), out.ctypes.data_as(ctypes.c_void_p), out.nbytes)
+        return out
+
+    def set_profiling(self, on: bool):
+        self._call("dc_model_set_profiling", int(on))
+
+    def profile(self) -> list[tuple[str, float, int]]:
+        buf = ctypes.create_string_buffer(8192)
+        self.lib.dc_model_profile(self.handle, buf, len(buf))
+        rows = []
+        for line in buf.value.decode().splitlines():
+            name, ms, calls = line.split()
+            rows.append((name, float(ms), int(calls)))
+        return rows
+
+    @property
+    def activation_bytes(self) -> int:
+        return int(self.lib.dc_model_activation_bytes(self.handle))

@@ -1,0 +1,139 @@
+"""Model dims and the fused weight layouts the kernels read.
+
+The reference compiles its dims in (crates/decide-engine/src/config.rs:4-41) and fuses the
+checkpoint's tensors at conversion time (crates/decide-engine/src/convert.rs:35-62, 204-245):
+  linear layer   w_in = in_proj_qkv | in_proj_z | in_proj_b | in_proj_a      (rows)
+  attention      w_in = q rows | gate rows | k_proj | v_proj, the checkpoint's q_proj being
+                 per head [head_dim query rows, head_dim gate rows]
+  MLP            w_gu = gate_proj and up_proj rows interleaved in blocks of 16
+Here the dims are a value (`Dims`) and the same fusions are applied to a state dict with the
+checkpoint's (Hugging Face Qwen3.5 text model) tensor names. Matrices are bf16 (the reference
+converts to fp16), small tensors fp32.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass(frozen=True)
+class Dims:
+    hidden: int = 2560
+    n_layers: int = 36
+    nq: int = 32
+    nkv: int = 8
+    head_dim: int = 128
+    rot_dim: int = 128
+    gdn_nk: int = 16
+    gdn_nv: int = 16
+    gdn_dk: int = 128
+    gdn_dv: int = 128
+    inter: int = 9728
+    vocab: int = 151936
+    full_attn_interval: int = 4
+    attn_gate: bool = True
+    swiglu_block: int = 16
+    eps: float = 1e-6
+    rope_theta: float = 1e6
+
+    # derived sizes, named as in config.rs
+    @property
+    def key_dim(self): return self.gdn_nk * self.gdn_dk
+    @property
+    def value_dim(self): return self.gdn_nv * self.gdn_dv
+    @property
+    def conv_dim(self): return 2 * self.key_dim + self.value_dim
+    @property
+    def lin_in_n(self): return self.conv_dim + self.value_dim + 2 * self.gdn_nv
+    @property
+    def q_dim(self): return self.nq * self.head_dim
+    @property
+    def kv_dim(self): return self.nkv * self.head_dim
+    @property
+    def att_in_n(self): return (2 if self.attn_gate else 1) * self.q_dim + 2 * self.kv_dim
+
+    def is_full_attention(self, layer: int) -> bool:  # config.rs:39-41
+        return (layer + 1) % self.full_attn_interval == 0
+
+    def gemm_flops_per_row(self) -> float:
+        """2*N*K summed over the projection GEMMs of all layers, per token row."""
+        total = 0.0
+        for l in range(self.n_layers):
+            if self.is_full_attention(l):
+                total += 2.0 * self.hidden * self.att_in_n + 2.0 * self.q_dim * self.hidden
+            else:
+                total += 2.0 * self.hidden * self.lin_in_n + 2.0 * self.value_dim * self.hidden
+            total += 2.0 * self.hidden * 2 * self.inter + 2.0 * self.inter * self.hidden
+        return total
+
+
+# The dims the benchmark configs use, and the reference checkpoint's own dims cut to what the kernels
+# support (head_dim 128 only), for a second tested instantiation.
+BASELINE_DIMS = Dims()
+
+
+class CDims(ctypes.Structure):
+    """dc_dims of include/decide_cuda.h."""
+    _fields_ = [(n, ctypes.c_uint32) for n in (
+        "hidden", "n_layers", "nq", "nkv", "head_dim", "rot_dim", "gdn_nk", "gdn_nv", "gdn_dk", "gdn_dv", "inter", "vocab",
+        "full_attn_interval", "attn_gate", "swiglu_block")] + [("eps", ctypes.c_float), ("rope_theta", ctypes.c_float)]
+
+    @classmethod
+    def of(cls, d: Dims) -> "CDims":
+        return cls(d.hidden, d.n_layers, d.nq, d.nkv, d.head_dim, d.rot_dim, d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, d.inter,
+                   d.vocab, d.full_attn_interval, int(d.attn_gate), d.swiglu_block, d.eps, d.rope_theta)
+
+
+LAYER_FIELDS = ("in_norm", "w_in", "w_out", "post_norm", "w_gu", "w_down", "conv_w", "a_log", "dt_bias", "gnorm", "q_norm", "k_norm")
+
+
+class CLayerWeights(ctypes.Structure):
+    """dc_layer_weights of include/decide_cuda.h."""
+    _fields_ = [(n, ctypes.c_void_p) for n in LAYER_FIELDS]
+
+
+def deinterleave_q_gate(q_proj: torch.Tensor, heads: int, head_dim: int) -> torch.Tensor:
+    """Per-head [query rows, gate rows] -> [all query rows | all gate rows] (convert.rs:35-47)."""
+    k = q_proj.shape[1]
+    v = q_proj.reshape(heads, 2, head_dim, k)
+    return torch.cat([v[:, 0].reshape(heads * head_dim, k), v[:, 1].reshape(heads * head_dim, k)], dim=0)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int) -> torch.Tensor:
+    """gate_proj and up_proj rows interleaved in blocks of `block` rows (convert.rs:49-62)."""
+    n, k = gate.shape
+    assert up.shape == gate.shape and n % block == 0, f"gate/up must be equal [n, k] matrices with n a multiple of {block}"
+    return torch.stack([gate.reshape(n // block, block, k), up.reshape(n // block, block, k)], dim=1).reshape(2 * n, k)
+
+
+def fuse_layer(sd: dict, i: int, d: Dims) -> dict:
+    """One layer's tensors in the engine's layouts, from checkpoint names (convert.rs:204-245)."""
+    bf = lambda t: t.to(torch.bfloat16).contiguous()
+    f32 = lambda t: t.to(torch.float32).contiguous()
+    p = f"layers.{i}."
+    out = {"in_norm": f32(sd[p + "input_layernorm.weight"]), "post_norm": f32(sd[p + "post_attention_layernorm.weight"])}
+    if d.is_full_attention(i):
+        q = sd[p + "self_attn.q_proj.weight"]
+        if d.attn_gate:
+            assert q.shape == (2 * d.q_dim, d.hidden)
+            q = deinterleave_q_gate(q, d.nq, d.head_dim)
+        out["w_in"] = bf(torch.cat([q, sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"]], dim=0))
+        out["q_norm"] = f32(sd[p + "self_attn.q_norm.weight"])
+        out["k_norm"] = f32(sd[p + "self_attn.k_norm.weight"])
+        out["w_out"] = bf(sd[p + "self_attn.o_proj.weight"])
+        assert out["w_in"].shape == (d.att_in_n, d.hidden)
+    else:
+        la = p + "linear_attn."
+        out["w_in"] = bf(torch.cat([sd[la + "in_proj_qkv.weight"], sd[la + "in_proj_z.weight"], sd[la + "in_proj_b.weight"],
+                                    sd[la + "in_proj_a.weight"]], dim=0))
+        out["conv_w"] = f32(sd[la + "conv1d.weight"].reshape(d.conv_dim, 4))
+        out["a_log"] = f32(sd[la + "A_log"])
+        out["dt_bias"] = f32(sd[la + "dt_bias"])
+        out["gnorm"] = f32(sd[la + "norm.weight"])
+        out["w_out"] = bf(sd[la + "out_proj.weight"])
+        assert out["w_in"].shape == (d.lin_in_n, d.hidden)
+    out["w_gu"] = bf(interleave_gate_up(sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"], d.swiglu_block))
+    out["w_down"] = bf(sd[p + "mlp.down_proj.weight"])
+    return out

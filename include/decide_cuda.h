@@ -174,6 +174,82 @@ int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, co
                    float* o, uint32_t t, uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk,
                    uint32_t dv, const uint32_t* seq_start, uint32_t n_seq);
 
+/* ======================================================================================
+ * Whole-model prefill: the host loop of Forward (crates/decide-engine/src/forward.rs:1129-1328)
+ * in C++ over the entry points above, for a batch of packed requests.
+ * ====================================================================================== */
+
+/* Model dims: the reference compiles these in (crates/decide-engine/src/config.rs:4-37); here they
+ * are given at creation. Layer l is full attention iff (l+1) % full_attn_interval == 0 (config.rs:39-41). */
+typedef struct dc_dims {
+    uint32_t hidden, n_layers;
+    uint32_t nq, nkv, head_dim, rot_dim;          /* attention: q heads, kv heads, head dim, rotary dims */
+    uint32_t gdn_nk, gdn_nv, gdn_dk, gdn_dv;      /* Gated DeltaNet: key heads, value heads, dims */
+    uint32_t inter, vocab;
+    uint32_t full_attn_interval;                  /* 4 */
+    uint32_t attn_gate;                           /* 1: fused in-proj is q|gate|k|v with a sigmoid output gate; 0: q|k|v */
+    uint32_t swiglu_block;                        /* gate|up interleave of w_gu, 16 (config.rs:31) */
+    float eps;                                    /* 1e-6 */
+    float rope_theta;
+} dc_dims;
+
+/* One layer's tensors in the reference's fused layouts (crates/decide-engine/src/convert.rs:204-245).
+ * bf16 matrices are [out, in] row-major; small tensors are fp32. Unused members are NULL. */
+typedef struct dc_layer_weights {
+    const float* in_norm;    /* [hidden] zero-centred */
+    const void* w_in;        /* linear layer: [conv_dim + value_dim + 2 nv, hidden] = qkv|z|b|a;
+                                attention layer: [q|gate|k|v or q|k|v, hidden] */
+    const void* w_out;       /* [hidden, value_dim] or [hidden, nq*head_dim] */
+    const float* post_norm;  /* [hidden] zero-centred */
+    const void* w_gu;        /* [2 inter, hidden], gate|up interleaved in blocks of swiglu_block rows */
+    const void* w_down;      /* [hidden, inter] */
+    const float* conv_w;     /* linear: [conv_dim, 4] */
+    const float* a_log;      /* linear: [nv] */
+    const float* dt_bias;    /* linear: [nv] */
+    const float* gnorm;      /* linear: [dv] */
+    const float* q_norm;     /* attention: [head_dim] zero-centred */
+    const float* k_norm;     /* attention: [head_dim] zero-centred */
+} dc_layer_weights;
+
+typedef struct dc_model dc_model;
+
+/* Borrows the weights (device pointers, which must outlive the model), allocates every activation
+ * buffer for up to max_rows packed rows, max_seqs requests and max_answers answer rows of up to
+ * max_cand candidates each (Forward::new, forward.rs:1336-1379). NULL on failure (see dc_last_error). */
+dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weights* layers, const void* embed,
+                          const float* final_norm, uint32_t max_rows, uint32_t max_seqs, uint32_t max_answers,
+                          uint32_t max_cand);
+void dc_model_destroy(dc_model* m);
+size_t dc_model_activation_bytes(dc_model* m);
+
+/* One batched prefill from HOST buffers (the analogue of Forward::logits, forward.rs:704-731):
+ * ids u32 [rows] packed by request, seq_start u32 [n_seq+1] (seq_start[0] = 0), ans_rows u32 [n_ans]
+ * packed row index of each answer row, cand u32 [n_ans,max_cand], ncand u32 [n_ans]. Copies in, runs
+ * all layers and the candidate-row head on `stream`, copies fp32 logits [n_ans,max_cand] out and waits.
+ * Non-finite logits are an error (forward.rs:906-913). */
+int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint32_t* seq_start, uint32_t n_seq,
+                     const uint32_t* ans_rows, const uint32_t* cand, const uint32_t* ncand, uint32_t n_ans,
+                     float* logits);
+
+/* The same pass over the inputs left on the device by the last dc_model_prefill of this batch:
+ * only enqueues (no copies, no wait); the logits stay in the model's device buffer. */
+int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_start, uint32_t n_seq, uint32_t n_ans);
+
+/* Runs only the first `n` layers and skips the head when n < n_layers (0 restores all layers): the
+ * residual stream after layer n-1 is then in buffer "x" (debug_layers, forward.rs:778-797). */
+int dc_model_set_layer_limit(dc_model* m, uint32_t n);
+/* Device address of a named activation buffer: "x" (fp32 residual [rows,hidden]), "h", "p", "g",
+ * "mlp", "xs", "logits". */
+void* dc_model_buffer(dc_model* m, const char* name);
+/* Waits for the device, then copies the first `bytes` bytes of that buffer to host memory `dst`. */
+int dc_model_read_buffer(dc_model* m, const char* name, void* dst, size_t bytes);
+
+/* Per-op timing table (the reference's DECIDE_PROFILE_PERKERNEL, crates/decide-metal/src/profile.rs:29-101):
+ * when on, every op of a forward is bracketed by CUDA events; dc_model_profile synchronises, writes
+ * "name total_ms calls" lines (largest first) into buf, clears the table and returns the text length. */
+int dc_model_set_profiling(dc_model* m, uint32_t on);
+size_t dc_model_profile(dc_model* m, char* buf, size_t len);
+
 #ifdef __cplusplus
 }
 #endif
