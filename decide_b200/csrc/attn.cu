@@ -26,24 +26,31 @@ __device__ __forceinline__ uint32_t tile_off(int row, int col) {
     return static_cast<uint32_t>(row * HD + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)));
 }
 
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const uint16_t* p) {
     const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const uint16_t* p) {
     const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+template <typename Act>
+__device__ __forceinline__ void mma_16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (Act::kUmmaFormat == 1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
 }
 
 // Copies `nrows` x 128 bf16 (rows beyond `valid` zero-filled) from global (row stride `ld`) into a swizzled tile.
-__device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat16* src, size_t ld, int valid) {
+__device__ __forceinline__ void load_tile(uint16_t* tile, const uint16_t* src, size_t ld, int valid) {
     for (int e = threadIdx.x; e < BKV * (HD / 8); e += kThreads) {
         const int r = e >> 4, c = e & 15;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -52,14 +59,15 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
     }
 }
 
+template <typename Act>
 __global__ void __launch_bounds__(kThreads)
-attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
-                 const float* __restrict__ gate, const uint32_t* __restrict__ qpos, __nv_bfloat16* __restrict__ y, uint32_t rows,
+attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
+                 const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t rows,
                  uint32_t ldg, uint32_t nq, uint32_t nkv, float scale_log2, const uint32_t* __restrict__ seq_start) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* ks = qs + BQ * HD;
-    __nv_bfloat16* vs = ks + BKV * HD;
+    uint16_t* qs = reinterpret_cast<uint16_t*>(smem_raw);
+    uint16_t* ks = qs + BQ * HD;
+    uint16_t* vs = ks + BKV * HD;
     int* qp = reinterpret_cast<int*>(vs + BKV * HD);  // [BQ] position of each query row, -1 = no row
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, kvh = h / (nq / nkv);
@@ -88,8 +96,8 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
-    const __nv_bfloat16* kbase = kc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
-    const __nv_bfloat16* vbase = vc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
+    const uint16_t* kbase = kc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
+    const uint16_t* vbase = vc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
     const size_t ldkv = static_cast<size_t>(nkv) * HD;
 
     for (int j0 = 0; j0 < kv_end; j0 += BKV) {
@@ -108,8 +116,8 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
             for (int np = 0; np < BKV / 16; ++np) {
                 uint32_t bfr[4];
                 ldsm_x4(bfr, ks + tile_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
-                mma_bf16(sacc[2 * np], qf[kk], bfr[0], bfr[1]);
-                mma_bf16(sacc[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+                mma_16<Act>(sacc[2 * np], qf[kk], bfr[0], bfr[1]);
+                mma_16<Act>(sacc[2 * np + 1], qf[kk], bfr[2], bfr[3]);
             }
         }
         // scale, causal mask, running max
@@ -141,9 +149,9 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
             const float p1 = sacc[i][1] > 0.5f * kMasked ? exp2f(sacc[i][1] - mn0) : 0.f;
             const float p2 = sacc[i][2] > 0.5f * kMasked ? exp2f(sacc[i][2] - mn1) : 0.f;
             const float p3 = sacc[i][3] > 0.5f * kMasked ? exp2f(sacc[i][3] - mn1) : 0.f;
-            const uint32_t lo = pack_bf16x2(p0, p1), hi = pack_bf16x2(p2, p3);
-            rs0 += bf16_lo(lo) + bf16_hi(lo);
-            rs1 += bf16_lo(hi) + bf16_hi(hi);
+            const uint32_t lo = Act::pack(p0, p1), hi = Act::pack(p2, p3);
+            rs0 += Act::lo(lo) + Act::hi(lo);
+            rs1 += Act::lo(hi) + Act::hi(hi);
             pf[i >> 1][(i & 1) * 2] = lo;
             pf[i >> 1][(i & 1) * 2 + 1] = hi;
         }
@@ -162,8 +170,8 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
             for (int dp = 0; dp < HD / 16; ++dp) {
                 uint32_t bfr[4];
                 ldsm_x4_trans(bfr, vs + tile_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 16 + (lane >> 4) * 8));
-                mma_bf16(oacc[2 * dp], pf[kk], bfr[0], bfr[1]);
-                mma_bf16(oacc[2 * dp + 1], pf[kk], bfr[2], bfr[3]);
+                mma_16<Act>(oacc[2 * dp], pf[kk], bfr[0], bfr[1]);
+                mma_16<Act>(oacc[2 * dp + 1], pf[kk], bfr[2], bfr[3]);
             }
         }
     }
@@ -185,7 +193,7 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
                 a *= sigmoid_f(g.x);
                 b *= sigmoid_f(g.y);
             }
-            *reinterpret_cast<uint32_t*>(y + (row * nq + h) * HD + d) = pack_bf16x2(a, b);
+            *reinterpret_cast<uint32_t*>(y + (row * nq + h) * HD + d) = Act::pack(a, b);
         }
         if (lr1 < valid_q) {
             const size_t row = row_lo + r0 + lr1;
@@ -195,15 +203,16 @@ attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __res
                 a *= sigmoid_f(g.x);
                 b *= sigmoid_f(g.y);
             }
-            *reinterpret_cast<uint32_t*>(y + (row * nq + h) * HD + d) = pack_bf16x2(a, b);
+            *reinterpret_cast<uint32_t*>(y + (row * nq + h) * HD + d) = Act::pack(a, b);
         }
     }
 }
 
 // One warp per (row, head): online softmax over cache rows 0..=qpos, fp32 (attn.metal:6-39).
+template <typename Act>
 __global__ void __launch_bounds__(256)
-attn_baseline_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
-                     const float* __restrict__ gate, const uint32_t* __restrict__ qpos, __nv_bfloat16* __restrict__ y, uint32_t rows,
+attn_baseline_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
+                     const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t rows,
                      uint32_t ldg, uint32_t nq, uint32_t nkv, float scale, const uint32_t* __restrict__ seq_start, uint32_t n_seq) {
     const uint32_t idx = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (idx >= rows * nq) return;
@@ -215,22 +224,22 @@ attn_baseline_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             if (r >= seq_start[s]) row_lo = seq_start[s];
     }
     const uint2 qv = reinterpret_cast<const uint2*>(q + static_cast<size_t>(idx) * HD)[lane];
-    const float q0 = bf16_lo(qv.x), q1 = bf16_hi(qv.x), q2 = bf16_lo(qv.y), q3 = bf16_hi(qv.y);
+    const float q0 = Act::lo(qv.x), q1 = Act::hi(qv.x), q2 = Act::lo(qv.y), q3 = Act::hi(qv.y);
     float m = kMasked, l = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
     const uint32_t n = qpos[r] + 1;
     for (uint32_t j = 0; j < n; ++j) {
         const size_t off = (static_cast<size_t>(row_lo + j) * nkv + kvh) * HD;
         const uint2 kvv = reinterpret_cast<const uint2*>(kc + off)[lane];
-        float s = q0 * bf16_lo(kvv.x) + q1 * bf16_hi(kvv.x) + q2 * bf16_lo(kvv.y) + q3 * bf16_hi(kvv.y);
+        float s = q0 * Act::lo(kvv.x) + q1 * Act::hi(kvv.x) + q2 * Act::lo(kvv.y) + q3 * Act::hi(kvv.y);
         s = warp_sum(s) * scale;
         const float mn = fmaxf(m, s);
         const float corr = expf(m - mn), p = expf(s - mn);
         const uint2 vv = reinterpret_cast<const uint2*>(vc + off)[lane];
         l = l * corr + p;
-        a0 = a0 * corr + p * bf16_lo(vv.x);
-        a1 = a1 * corr + p * bf16_hi(vv.x);
-        a2 = a2 * corr + p * bf16_lo(vv.y);
-        a3 = a3 * corr + p * bf16_hi(vv.y);
+        a0 = a0 * corr + p * Act::lo(vv.x);
+        a1 = a1 * corr + p * Act::hi(vv.x);
+        a2 = a2 * corr + p * Act::lo(vv.y);
+        a3 = a3 * corr + p * Act::hi(vv.y);
         m = mn;
     }
     const float inv = 1.0f / l;
@@ -243,8 +252,8 @@ attn_baseline_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         o3 *= 1.0f / (1.0f + expf(-g.w));
     }
     uint2 out;
-    out.x = pack_bf16x2(o0, o1);
-    out.y = pack_bf16x2(o2, o3);
+    out.x = Act::pack(o0, o1);
+    out.y = Act::pack(o2, o3);
     reinterpret_cast<uint2*>(y + static_cast<size_t>(idx) * HD)[lane] = out;
 }
 
@@ -270,21 +279,23 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const float scale = 1.0f / sqrtf(static_cast<float>(hd));
     if (ctx->attn_impl == DC_IMPL_BASELINE) {
-        attn_baseline_kernel<<<(rows * nq + 7) / 8, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
-                                                              static_cast<const __nv_bfloat16*>(vc), gate, qpos, static_cast<__nv_bfloat16*>(y),
-                                                              rows, ldg, nq, nkv, scale, seq_start, n_seq);
+        auto kern = ctx->act_dtype == DC_ACT_F16 ? attn_baseline_kernel<ActF16> : attn_baseline_kernel<ActBF16>;
+        kern<<<(rows * nq + 7) / 8, 256, 0, s>>>(static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc), static_cast<const uint16_t*>(vc),
+                                                 gate, qpos, static_cast<uint16_t*>(y), rows, ldg, nq, nkv, scale, seq_start, n_seq);
         return dc_check_launch(ctx, "attention (baseline)");
     }
     constexpr size_t smem = (BQ + 2 * BKV) * HD * 2 + BQ * sizeof(int);
     static bool attr_set[16] = {};
+    auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;
     if (!attr_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(attn_fast_kernel<ActF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fast_kernel<ActBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot opt in to %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         attr_set[ctx->device & 15] = true;
     }
     dim3 grid((max_len + BQ - 1) / BQ, nq, n_seq);
-    attn_fast_kernel<<<grid, kThreads, smem, s>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
-                                                  static_cast<const __nv_bfloat16*>(vc), gate, qpos, static_cast<__nv_bfloat16*>(y), rows, ldg,
+    fast<<<grid, kThreads, smem, s>>>(static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc),
+                                                  static_cast<const uint16_t*>(vc), gate, qpos, static_cast<uint16_t*>(y), rows, ldg,
                                                   nq, nkv, scale * 1.4426950408889634f, seq_start);
     return dc_check_launch(ctx, "attention");
 }

@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -35,6 +36,7 @@ struct dc_ctx {
     uint32_t gemm_impl = DC_IMPL_FAST;
     uint32_t attn_impl = DC_IMPL_FAST;
     uint32_t delta_impl = DC_IMPL_FAST;
+    uint32_t act_dtype = DC_ACT_F16;  // storage type of 16-bit activations (weights are always bf16)
     void* workspace = nullptr;       // scratch for the chunked delta rule and other multi-pass ops
     size_t workspace_bytes = 0;
 };
@@ -67,6 +69,31 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+
+// The two 16-bit activation formats. Weights are always bf16; 16-bit ACTIVATIONS (normed rows, gated
+// outputs, the MLP intermediate, attention q/k/v) are stored in the context's activation type.
+struct ActBF16 {
+    static constexpr uint32_t kUmmaFormat = 1;  // tcgen05 instruction-descriptor code for bf16
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    static __device__ __forceinline__ float lo(uint32_t v) { return __uint_as_float(v << 16); }
+    static __device__ __forceinline__ float hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+    static __device__ __forceinline__ float one(uint16_t v) { return __uint_as_float(static_cast<uint32_t>(v) << 16); }
+    static __device__ __forceinline__ uint16_t to16(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+};
+struct ActF16 {
+    static constexpr uint32_t kUmmaFormat = 0;  // fp16
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    static __device__ __forceinline__ float lo(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu))); }
+    static __device__ __forceinline__ float hi(uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v >> 16))); }
+    static __device__ __forceinline__ float one(uint16_t v) { return __half2float(__ushort_as_half(v)); }
+    static __device__ __forceinline__ uint16_t to16(float f) { return __half_as_ushort(__float2half_rn(f)); }
+};
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

@@ -80,8 +80,13 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
     ctx->gemm_impl = impl_from_env("DECIDE_GEMM", &bad);
     ctx->attn_impl = impl_from_env("DECIDE_ATTN", &bad);
     ctx->delta_impl = impl_from_env("DECIDE_DELTA", &bad);
+    if (const char* a = getenv("DECIDE_ACT")) {
+        if (strcmp(a, "bf16") == 0) ctx->act_dtype = DC_ACT_BF16;
+        else if (strcmp(a, "f16") == 0 || !*a) ctx->act_dtype = DC_ACT_F16;
+        else bad = true;
+    }
     if (bad) {
-        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`", nullptr);
+        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`, DECIDE_ACT `f16` or `bf16`", nullptr);
         delete ctx;
         return nullptr;
     }
@@ -145,6 +150,15 @@ uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family) {
         default: return DC_IMPL_FAST;
     }
 }
+
+int dc_set_activation_dtype(dc_ctx* ctx, uint32_t act) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, act == DC_ACT_BF16 || act == DC_ACT_F16, "dc_set_activation_dtype: unknown type %u", act);
+    ctx->act_dtype = act;
+    return DC_OK;
+}
+
+uint32_t dc_get_activation_dtype(dc_ctx* ctx) { return ctx ? ctx->act_dtype : DC_ACT_F16; }
 
 int dc_check_status(dc_ctx* ctx, void* stream) {
     if (!ctx) return DC_INVALID_ARG;

@@ -19,9 +19,9 @@ constexpr int RK = 16;   // its k step
 
 // One thread computes a 4 x 4 patch of the 64 x 64 output tile. For the SwiGLU epilogue the tile is
 // 64 OUTPUT columns: column j pairs W row gate(j) = (j / sb) * 2 sb + j % sb with row gate(j) + sb.
-template <int EPI>
+template <int EPI, typename Act>
 __global__ void __launch_bounds__(256)
-gemm_baseline_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ y,
+gemm_baseline_kernel(const uint16_t* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ y,
                      uint32_t m, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t sb) {
     constexpr bool kSwiglu = (EPI == DC_EPI_SWIGLU_BF16);
     __shared__ float xs[RK][RT + 1];
@@ -36,7 +36,7 @@ gemm_baseline_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         for (int e = threadIdx.x; e < RT * RK; e += 256) {
             const int r = e / RK, kk = e % RK;
             const uint32_t gr = row0 + r;
-            xs[kk][r] = (gr < m && k0 + kk < k) ? __bfloat162float(x[static_cast<size_t>(gr) * ldx + k0 + kk]) : 0.0f;
+            xs[kk][r] = (gr < m && k0 + kk < k) ? Act::one(x[static_cast<size_t>(gr) * ldx + k0 + kk]) : 0.0f;
             const uint32_t j = col0 + r;
             if (j < n_out && k0 + kk < k) {
                 if constexpr (kSwiglu) {
@@ -81,10 +81,10 @@ gemm_baseline_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
             const size_t o = static_cast<size_t>(r) * ldy + c;
             if constexpr (EPI == DC_EPI_STORE_F32) static_cast<float*>(y)[o] = acc[0][i][j];
             else if constexpr (EPI == DC_EPI_ADD_F32) static_cast<float*>(y)[o] += acc[0][i][j];
-            else if constexpr (EPI == DC_EPI_STORE_BF16) static_cast<__nv_bfloat16*>(y)[o] = __float2bfloat16_rn(acc[0][i][j]);
+            else if constexpr (EPI == DC_EPI_STORE_BF16) static_cast<uint16_t*>(y)[o] = Act::to16(acc[0][i][j]);
             else {
                 const float g = acc[0][i][j];
-                static_cast<__nv_bfloat16*>(y)[o] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * acc[1][i][j]);
+                static_cast<uint16_t*>(y)[o] = Act::to16(g / (1.0f + expf(-g)) * acc[1][i][j]);
             }
         }
     }
@@ -95,8 +95,10 @@ int launch_baseline(dc_ctx* ctx, cudaStream_t s, const void* x, const void* w, v
                     uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t sb) {
     const uint32_t n_out = EPI == DC_EPI_SWIGLU_BF16 ? n / 2 : n;
     dim3 grid((n_out + RT - 1) / RT, (m + RT - 1) / RT);
-    gemm_baseline_kernel<EPI><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-                                                   y, m, n, k, ldx, ldw, ldy, sb);
+    if (ctx->act_dtype == DC_ACT_F16)
+        gemm_baseline_kernel<EPI, ActF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const __nv_bfloat16*>(w), y, m, n, k, ldx, ldw, ldy, sb);
+    else
+        gemm_baseline_kernel<EPI, ActBF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const __nv_bfloat16*>(w), y, m, n, k, ldx, ldw, ldy, sb);
     return dc_check_launch(ctx, "gemm (baseline)");
 }
 

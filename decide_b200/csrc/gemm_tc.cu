@@ -29,6 +29,7 @@ constexpr uint32_t kTmemCols = 512;
 struct GemmArgs {
     uint32_t m, n, k, ldy;
     uint32_t m_tiles, n_tiles, k_blocks, group_m;
+    uint32_t idesc;  // tcgen05 instruction descriptor: A = the activation type, B = bf16, D = fp32
 };
 
 template <int BN>
@@ -63,7 +64,7 @@ __device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
     return true;
 }
 
-template <int EPI>
+template <int EPI, typename Act>
 __device__ __forceinline__ void epilogue_store(void* __restrict__ y, size_t row, uint32_t col0, uint32_t ldy,
                                                const uint32_t (&r)[32]) {
     if constexpr (EPI == DC_EPI_STORE_F32) {
@@ -86,36 +87,36 @@ __device__ __forceinline__ void epilogue_store(void* __restrict__ y, size_t row,
             p[j] = v[j];
         }
     } else if constexpr (EPI == DC_EPI_STORE_BF16) {
-        uint4* p = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(y) + row * ldy + col0);
+        uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + col0);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            v.x = Act::pack(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+            v.y = Act::pack(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = Act::pack(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = Act::pack(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
             p[j] = v;
         }
     } else {
         // SwiGLU over interleaved blocks of 16: columns [0,16) of this 32-column chunk are the gate,
         // [16,32) the up projection of the same 16 output columns (cpu_ref.rs:39-50).
-        uint4* p = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(y) + row * ldy + (col0 >> 1));
+        uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + (col0 >> 1));
         float o[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) o[j] = silu_f(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             uint4 v;
-            v.x = pack_bf16x2(o[8 * j], o[8 * j + 1]);
-            v.y = pack_bf16x2(o[8 * j + 2], o[8 * j + 3]);
-            v.z = pack_bf16x2(o[8 * j + 4], o[8 * j + 5]);
-            v.w = pack_bf16x2(o[8 * j + 6], o[8 * j + 7]);
+            v.x = Act::pack(o[8 * j], o[8 * j + 1]);
+            v.y = Act::pack(o[8 * j + 2], o[8 * j + 3]);
+            v.z = Act::pack(o[8 * j + 4], o[8 * j + 5]);
+            v.w = Act::pack(o[8 * j + 6], o[8 * j + 7]);
             p[j] = v;
         }
     }
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, typename Act>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                void* __restrict__ y, const GemmArgs a, int* __restrict__ status) {
@@ -205,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            const uint32_t idesc = a.idesc;
             uint32_t s = 0, ph = 0, lt = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++lt) {
@@ -256,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32u, r);
                 tmem_ld_wait();
-                if (row < a.m) epilogue_store<EPI>(y, row, col0, a.ldy, r);
+                if (row < a.m) epilogue_store<EPI, Act>(y, row, col0, a.ldy, r);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -273,9 +274,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     }
 }
 
-int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows,
+int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16,
               CUtensorMap* out) {
-    const dc_tmap_key key(base, rows, cols, ld, box_rows);
+    const dc_tmap_key key(base, rows, cols, ld, box_rows | (f16 ? 0x10000u : 0u));
     auto it = ctx->tmaps.find(key);
     if (it != ctx->tmaps.end()) {
         *out = it->second;
@@ -286,7 +287,7 @@ int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint3
     cuuint32_t box[2] = {BK, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUtensorMap m;
-    CUresult r = ctx->encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+    CUresult r = ctx->encode_tiled(&m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -298,11 +299,11 @@ int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint3
     return DC_OK;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, typename Act>
 int launch(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtensorMap& tw, void* y, const GemmArgs& a) {
     using C = Cfg<BN>;
     static bool attr_set[16] = {};
-    auto kern = gemm_tc_kernel<BN, EPI>;
+    auto kern = gemm_tc_kernel<BN, EPI, Act>;
     if (!attr_set[ctx->device & 15]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cannot opt in to %u bytes of shared memory: %s", C::kSmemBytes, cudaGetErrorString(e));
@@ -317,11 +318,14 @@ int launch(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtens
 template <int BN>
 int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtensorMap& tw, void* y, const GemmArgs& a,
                uint32_t epi) {
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
     switch (epi) {
-        case DC_EPI_STORE_F32: return launch<BN, DC_EPI_STORE_F32>(ctx, stream, tx, tw, y, a);
-        case DC_EPI_STORE_BF16: return launch<BN, DC_EPI_STORE_BF16>(ctx, stream, tx, tw, y, a);
-        case DC_EPI_ADD_F32: return launch<BN, DC_EPI_ADD_F32>(ctx, stream, tx, tw, y, a);
-        default: return launch<BN, DC_EPI_SWIGLU_BF16>(ctx, stream, tx, tw, y, a);
+        case DC_EPI_STORE_F32: return launch<BN, DC_EPI_STORE_F32, ActBF16>(ctx, stream, tx, tw, y, a);
+        case DC_EPI_ADD_F32: return launch<BN, DC_EPI_ADD_F32, ActBF16>(ctx, stream, tx, tw, y, a);
+        case DC_EPI_STORE_BF16:
+            return f16 ? launch<BN, DC_EPI_STORE_BF16, ActF16>(ctx, stream, tx, tw, y, a) : launch<BN, DC_EPI_STORE_BF16, ActBF16>(ctx, stream, tx, tw, y, a);
+        default:
+            return f16 ? launch<BN, DC_EPI_SWIGLU_BF16, ActF16>(ctx, stream, tx, tw, y, a) : launch<BN, DC_EPI_SWIGLU_BF16, ActBF16>(ctx, stream, tx, tw, y, a);
     }
 }
 
@@ -353,10 +357,12 @@ int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, v
     a.n_tiles = (n + bn - 1) / bn;
     a.k_blocks = (k + BK - 1) / BK;
     a.group_m = a.m_tiles < 16 ? a.m_tiles : 16;
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    a.idesc = umma_idesc(f16 ? ActF16::kUmmaFormat : ActBF16::kUmmaFormat, ActBF16::kUmmaFormat, BM, static_cast<int>(bn));
     CUtensorMap tx, tw;
-    int rc = make_tmap(ctx, x, m, k, ldx, BM, &tx);
+    int rc = make_tmap(ctx, x, m, k, ldx, BM, f16, &tx);
     if (rc != DC_OK) return rc;
-    rc = make_tmap(ctx, w, n, k, ldw, bn, &tw);
+    rc = make_tmap(ctx, w, n, k, ldw, bn, false, &tw);
     if (rc != DC_OK) return rc;
     if (bn == 256) return launch_epi<256>(ctx, stream, tx, tw, y, a, epi);
     return launch_epi<128>(ctx, stream, tx, tw, y, a, epi);

@@ -147,11 +147,12 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+// Instruction descriptor of kind::f16: 16-bit A and B (format code 0 = fp16, 1 = bf16, chosen per
+// operand), fp32 accumulator, both operands K-major, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_format, uint32_t b_format, int m, int n) {
     return (1u << 4)                                  // D format fp32
-           | (1u << 7)                                // A format bf16
-           | (1u << 10)                               // B format bf16
+           | (a_format << 7)                          // A format
+           | (b_format << 10)                         // B format
            | (static_cast<uint32_t>(n >> 3) << 17)    // N / 8
            | (static_cast<uint32_t>(m >> 4) << 24);   // M / 16
 }

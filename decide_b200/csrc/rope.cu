@@ -58,17 +58,18 @@ __device__ __forceinline__ void norm_rope(float4 (&v)[HD / 128], const float* __
     }
 }
 
-__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, const float4& v) {
+template <typename Act>
+__device__ __forceinline__ void store_16x4(uint16_t* dst, const float4& v) {
     uint2 o;
-    o.x = pack_bf16x2(v.x, v.y);
-    o.y = pack_bf16x2(v.z, v.w);
+    o.x = Act::pack(v.x, v.y);
+    o.y = Act::pack(v.z, v.w);
     *reinterpret_cast<uint2*>(dst) = o;
 }
 
-template <int HD>
+template <int HD, typename Act>
 __global__ void __launch_bounds__(kWarps * 32)
 q_norm_rope_kernel(const float* __restrict__ pq, const float* __restrict__ qw, const float* __restrict__ inv_freq,
-                   const uint32_t* __restrict__ qpos, __nv_bfloat16* __restrict__ qo, uint32_t rows, uint32_t ldq,
+                   const uint32_t* __restrict__ qpos, uint16_t* __restrict__ qo, uint32_t rows, uint32_t ldq,
                    uint32_t nq, uint32_t rot, float eps) {
     const uint32_t idx = blockIdx.x * kWarps + (threadIdx.x >> 5);
     if (idx >= rows * nq) return;
@@ -80,19 +81,19 @@ q_norm_rope_kernel(const float* __restrict__ pq, const float* __restrict__ qw, c
 #pragma unroll
     for (int c = 0; c < NC; ++c) v[c] = reinterpret_cast<const float4*>(src)[c * 32 + lane];
     norm_rope<HD>(v, qw, inv_freq, rot, static_cast<float>(qpos[r]), eps, lane);
-    __nv_bfloat16* dst = qo + static_cast<size_t>(idx) * HD;
+    uint16_t* dst = qo + static_cast<size_t>(idx) * HD;
 #pragma unroll
-    for (int c = 0; c < NC; ++c) store_bf16x4(dst + c * 128 + 4 * lane, v[c]);
+    for (int c = 0; c < NC; ++c) store_16x4<Act>(dst + c * 128 + 4 * lane, v[c]);
 }
 
 // Head slots 0..nkv-1 are the k heads (norm + rope into the K cache), nkv..2nkv-1 the v heads (copied
 // to the V cache). Without `pos`, row r is at position pos0 + r and is written to cache row pos0 + r
 // (the reference's single-sequence form). With `pos` (packed sequences), row r is rotated for
 // position pos[r] and written to cache row r.
-template <int HD>
+template <int HD, typename Act>
 __global__ void __launch_bounds__(kWarps * 32)
 kv_norm_rope_kernel(const float* __restrict__ pkv, const float* __restrict__ kw, const float* __restrict__ inv_freq,
-                    const uint32_t* __restrict__ pos, __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                    const uint32_t* __restrict__ pos, uint16_t* __restrict__ kc, uint16_t* __restrict__ vc,
                     uint32_t rows, uint32_t ldkv, uint32_t kcol, uint32_t vcol, uint32_t pos0, uint32_t nkv, uint32_t rot,
                     float eps) {
     const uint32_t idx = blockIdx.x * kWarps + (threadIdx.x >> 5);
@@ -109,9 +110,9 @@ kv_norm_rope_kernel(const float* __restrict__ pkv, const float* __restrict__ kw,
     const uint32_t p = pos ? pos[r] : pos0 + r;
     const size_t crow = pos ? r : pos0 + r;
     if (is_k) norm_rope<HD>(v, kw, inv_freq, rot, static_cast<float>(p), eps, lane);
-    __nv_bfloat16* dst = (is_k ? kc : vc) + (crow * nkv + h) * HD;
+    uint16_t* dst = (is_k ? kc : vc) + (crow * nkv + h) * HD;
 #pragma unroll
-    for (int c = 0; c < NC; ++c) store_bf16x4(dst + c * 128 + 4 * lane, v[c]);
+    for (int c = 0; c < NC; ++c) store_16x4<Act>(dst + c * 128 + 4 * lane, v[c]);
 }
 
 inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
@@ -132,10 +133,12 @@ int dc_q_norm_rope(dc_ctx* ctx, void* stream, const float* pq, const float* qw, 
     if (rows == 0) return DC_OK;
     const uint32_t blocks = (rows * nq + kWarps - 1) / kWarps;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (hd == 128)
-        q_norm_rope_kernel<128><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, static_cast<__nv_bfloat16*>(qo), rows, ldq, nq, rot, eps);
-    else
-        q_norm_rope_kernel<256><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, static_cast<__nv_bfloat16*>(qo), rows, ldq, nq, rot, eps);
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    uint16_t* out = static_cast<uint16_t*>(qo);
+    if (hd == 128 && f16) q_norm_rope_kernel<128, ActF16><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, out, rows, ldq, nq, rot, eps);
+    else if (hd == 128) q_norm_rope_kernel<128, ActBF16><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, out, rows, ldq, nq, rot, eps);
+    else if (f16) q_norm_rope_kernel<256, ActF16><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, out, rows, ldq, nq, rot, eps);
+    else q_norm_rope_kernel<256, ActBF16><<<blocks, kWarps * 32, 0, s>>>(pq, qw, inv_freq, qpos, out, rows, ldq, nq, rot, eps);
     return dc_check_launch(ctx, "q_norm_rope");
 }
 
@@ -155,10 +158,13 @@ int dc_kv_norm_rope(dc_ctx* ctx, void* stream, const float* pkv, const float* kw
     if (rows == 0) return DC_OK;
     const uint32_t blocks = (rows * 2 * nkv + kWarps - 1) / kWarps;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (hd == 128)
-        kv_norm_rope_kernel<128><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
-    else
-        kv_norm_rope_kernel<256><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    uint16_t* ko = static_cast<uint16_t*>(kc);
+    uint16_t* vo = static_cast<uint16_t*>(vc);
+    if (hd == 128 && f16) kv_norm_rope_kernel<128, ActF16><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, ko, vo, rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
+    else if (hd == 128) kv_norm_rope_kernel<128, ActBF16><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, ko, vo, rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
+    else if (f16) kv_norm_rope_kernel<256, ActF16><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, ko, vo, rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
+    else kv_norm_rope_kernel<256, ActBF16><<<blocks, kWarps * 32, 0, s>>>(pkv, kw, inv_freq, pos, ko, vo, rows, ldkv, kcol, vcol, pos0, nkv, rot, eps);
     return dc_check_launch(ctx, "kv_norm_rope");
 }
 

@@ -10,8 +10,9 @@ using namespace dc;
 constexpr int kWarpsPerBlock = 8;
 
 // y[r] = x[rowmap[r]] * rsqrt(mean(x^2) + eps) * (w or 1 + w); spec cpu_ref.rs:11-22.
+template <typename Act>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_t* __restrict__ y,
                const uint32_t* __restrict__ rowmap, uint32_t rows, uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps,
                uint32_t add_one) {
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -34,8 +35,8 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, __nv_bf
         const float4 v = xr[i];
         const float4 g = wr[i];
         uint2 o;
-        o.x = pack_bf16x2(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
-        o.y = pack_bf16x2(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
+        o.x = Act::pack(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
+        o.y = Act::pack(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
         yr[i] = o;
     }
 }
@@ -106,9 +107,10 @@ final_head_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
 
 // Per (row, value head): RMSNorm over dv = 128 with fp32 weight (no +1), times silu(z);
 // gnorm.metal:6-25, spec cpu_ref.rs:132-145. One warp per (row, head), one float4 per lane.
+template <typename Act>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 gated_rmsnorm_silu_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ w,
-                          __nv_bfloat16* __restrict__ y, uint32_t t, uint32_t nv_heads, uint32_t ldz, float eps) {
+                          uint16_t* __restrict__ y, uint32_t t, uint32_t nv_heads, uint32_t ldz, float eps) {
     const uint32_t idx = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (idx >= t * nv_heads) return;
     const uint32_t s = idx / nv_heads, hd = idx - s * nv_heads;
@@ -119,8 +121,8 @@ gated_rmsnorm_silu_kernel(const float* __restrict__ o, const float* __restrict__
     const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
     const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
     uint2 out;
-    out.x = pack_bf16x2(v.x * inv * g.x * silu_f(zz.x), v.y * inv * g.y * silu_f(zz.y));
-    out.y = pack_bf16x2(v.z * inv * g.z * silu_f(zz.z), v.w * inv * g.w * silu_f(zz.w));
+    out.x = Act::pack(v.x * inv * g.x * silu_f(zz.x), v.y * inv * g.y * silu_f(zz.y));
+    out.y = Act::pack(v.z * inv * g.z * silu_f(zz.z), v.w * inv * g.w * silu_f(zz.w));
     reinterpret_cast<uint2*>(y + static_cast<size_t>(idx) * 128)[lane] = out;
 }
 
@@ -139,8 +141,12 @@ int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* 
     DC_REQUIRE(ctx, h % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && h > 0, "rmsnorm: H and the row strides must be multiples of 4");
     DC_REQUIRE(ctx, aligned16(x) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "rmsnorm: misaligned operand");
     if (rows == 0) return DC_OK;
-    rmsnorm_kernel<<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, w, static_cast<__nv_bfloat16*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
+    if (ctx->act_dtype == DC_ACT_F16)
+        rmsnorm_kernel<ActF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            x, w, static_cast<uint16_t*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
+    else
+        rmsnorm_kernel<ActBF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            x, w, static_cast<uint16_t*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
     return dc_check_launch(ctx, "rmsnorm");
 }
 
@@ -195,8 +201,12 @@ int dc_gated_rmsnorm_silu(dc_ctx* ctx, void* stream, const float* o, const float
     DC_REQUIRE(ctx, ldz >= nv * dv && ldz % 4 == 0, "gated_rmsnorm_silu: ldz = %u must cover %u columns and be a multiple of 4", ldz, nv * dv);
     DC_REQUIRE(ctx, aligned16(o) && aligned16(z) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "gated_rmsnorm_silu: misaligned operand");
     if (t == 0) return DC_OK;
-    gated_rmsnorm_silu_kernel<<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        o, z, w, static_cast<__nv_bfloat16*>(y), t, nv, ldz, eps);
+    if (ctx->act_dtype == DC_ACT_F16)
+        gated_rmsnorm_silu_kernel<ActF16><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            o, z, w, static_cast<uint16_t*>(y), t, nv, ldz, eps);
+    else
+        gated_rmsnorm_silu_kernel<ActBF16><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            o, z, w, static_cast<uint16_t*>(y), t, nv, ldz, eps);
     return dc_check_launch(ctx, "gated_rmsnorm_silu");
 }
 

@@ -47,6 +47,12 @@ class Family(enum.IntEnum):
     Delta = 2
 
 
+class Act(enum.IntEnum):
+    """Storage type of the 16-bit activations (DC_ACT_*); weights are always bf16."""
+    BF16 = 0
+    F16 = 1
+
+
 def _ptr(arg) -> int:
     """Device address of a tensor, or of (tensor, byte offset); None -> NULL."""
     if arg is None:
@@ -108,6 +114,18 @@ class Device:
 
     def get_impl(self, family: Family) -> Impl:
         return Impl(self.lib.dc_get_impl(self.handle, int(family)))
+
+    def set_activation_dtype(self, act: Act):
+        self.call("dc_set_activation_dtype", int(act))
+
+    @property
+    def act(self) -> Act:
+        return Act(self.lib.dc_get_activation_dtype(self.handle))
+
+    @property
+    def act_torch(self) -> torch.dtype:
+        """torch dtype of the 16-bit activation buffers this context reads and writes."""
+        return torch.float16 if self.act == Act.F16 else torch.bfloat16
 
     @property
     def launches(self) -> int:

@@ -53,6 +53,14 @@ enum {
 enum { DC_IMPL_FAST = 0, DC_IMPL_BASELINE = 1 };
 enum { DC_FAMILY_GEMM = 0, DC_FAMILY_ATTN = 1, DC_FAMILY_DELTA = 2 };
 
+/* Storage type of the 16-bit ACTIVATIONS (normed rows, gated outputs, the MLP intermediate, attention
+ * q/k/v and its output). Weights and the embedding table are always bf16. The reference keeps its
+ * 16-bit activations in fp16 because bf16 missed its 0.01 probability tolerance (README.md:88-90,
+ * 207-208); DC_ACT_F16 is the default here for the same reason, and the tensor cores multiply fp16
+ * activations by bf16 weights directly. Wherever this header says "bf16" for an activation buffer,
+ * read "the context's activation type". */
+enum { DC_ACT_BF16 = 0, DC_ACT_F16 = 1 };
+
 /* ---- context: replaces DecideDevice::shared + Kernels::new (device.rs:125-130, mod.rs:54-66) ---- */
 dc_ctx* dc_open(int device, char* err, size_t err_len);
 void dc_close(dc_ctx* ctx);
@@ -62,6 +70,9 @@ size_t dc_last_error(dc_ctx* ctx, char* buf, size_t len);
  * DECIDE_DELTA environment variables are read once, as Gemm::new etc. do. */
 int dc_set_impl(dc_ctx* ctx, uint32_t family, uint32_t impl);
 uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family);
+/* Activation storage type (DC_ACT_*); at open it is read from DECIDE_ACT = f16 | bf16 (default f16). */
+int dc_set_activation_dtype(dc_ctx* ctx, uint32_t act);
+uint32_t dc_get_activation_dtype(dc_ctx* ctx);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
  * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
 int dc_check_status(dc_ctx* ctx, void* stream);

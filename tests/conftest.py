@@ -35,3 +35,13 @@ def k(dev):
     from decide_b200.kernels import Kernels
 
     return Kernels(dev)
+
+
+@pytest.fixture(params=["f16", "bf16"])
+def act(request, dev):
+    """Runs the test once per activation storage type; yields the torch dtype of activation buffers."""
+    from decide_b200.kernels import Act
+
+    dev.set_activation_dtype(Act.F16 if request.param == "f16" else Act.BF16)
+    yield dev.act_torch
+    dev.set_activation_dtype(Act.F16)

@@ -1,13 +1,14 @@
 """GEMM parity on the GPU, through the C ABI, against the restated cpu_ref::gemm_nt +
 swiglu_interleaved (oracle/cpu_ref.py). Inputs are seeded, rounded to bf16 once, and shared
-bit-for-bit by both sides. Tolerances: fp32 outputs atol 2e-4 + rtol 2e-5 (fp32 accumulation of
+bit-for-bit by both sides. X is stored in the context's activation type (fp16 by default, bf16
+also run), W always in bf16: the tensor cores multiply the two formats directly. Tolerances: fp32 outputs atol 2e-4 + rtol 2e-5 (fp32 accumulation of
 up to 9728 bf16 products of magnitude ~0.02); bf16 outputs add bf16's half-ulp, rtol 2^-8."""
 import numpy as np
 import pytest
 import torch
 
 from oracle import cpu_ref
-from tests.util import assert_close, bf16, np32, randn
+from tests.util import assert_close, bf16, half_ulp, np32, randn
 
 pytestmark = pytest.mark.gpu
 
@@ -15,11 +16,12 @@ F32_TOL = dict(atol=2e-4, rtol=2e-5)
 BF16_TOL = dict(atol=2e-3, rtol=2 ** -8)
 
 
-def _operands(seed, m, n, k, ldx=None, ldw=None):
+def _operands(seed, m, n, k, ldx=None, ldw=None, act=torch.float16):
+    """X in the activation type, W in bf16, both rounded once and shared with the oracle."""
     ldx, ldw = ldx or k, ldw or k
-    x = torch.zeros(m, ldx, dtype=torch.bfloat16)
+    x = torch.zeros(m, ldx, dtype=act)
     w = torch.zeros(n, ldw, dtype=torch.bfloat16)
-    x[:, :k] = bf16(randn(seed, m, k))
+    x[:, :k] = randn(seed, m, k).to(act)
     w[:, :k] = bf16(randn(seed + 1, n, k, std=0.02))
     return x, w
 
@@ -38,7 +40,7 @@ def _run(k, x, w, m, n, kk, epi, ldy=None, y0=None, bn=None, block=16):
 
     n_out = n // 2 if epi == 3 else n
     ldy = ldy or n_out
-    dt = torch.float32 if epi in (0, 2) else torch.bfloat16
+    dt = torch.float32 if epi in (0, 2) else k.dev.act_torch
     if y0 is not None:
         y = torch.zeros(m, ldy, dtype=dt)
         y[:, :n_out] = torch.from_numpy(y0)
@@ -60,21 +62,21 @@ def _run(k, x, w, m, n, kk, epi, ldy=None, y0=None, bn=None, block=16):
 @pytest.mark.parametrize("bn", [128, 256])
 @pytest.mark.parametrize("m,n,kk", [(128, 256, 64), (128, 256, 256), (1, 32, 32), (37, 96, 160), (276, 512, 2560),
                                     (300, 8224, 512), (603, 2560, 1024)])
-def test_fast_store_f32_shapes(k, m, n, kk, bn):
+def test_fast_store_f32_shapes(k, m, n, kk, bn, act):
     """One tile / one k-block up to ragged M, N and K tails (TMA zero fill + masked stores)."""
-    x, w = _operands(10 + m, m, n, kk)
+    x, w = _operands(10 + m, m, n, kk, act=act)
     got = _run(k, x, w, m, n, kk, 0, bn=bn)
     assert_close(got, _want(x, w, m, n, kk, 0), what=f"StoreF32 {m}x{n}x{kk} bn{bn}", **F32_TOL)
 
 
 @pytest.mark.parametrize("epi", [0, 1, 2, 3])
 @pytest.mark.parametrize("bn", [128, 256])
-def test_fast_epilogues(k, epi, bn):
+def test_fast_epilogues(k, epi, bn, act):
     m, n, kk = 276, 1024, 2560
-    x, w = _operands(3, m, n, kk)
+    x, w = _operands(3, m, n, kk, act=act)
     y0 = np32(randn(5, m, n)) if epi == 2 else None
     got = _run(k, x, w, m, n, kk, epi, y0=y0, bn=bn)
-    tol = F32_TOL if epi in (0, 2) else BF16_TOL
+    tol = F32_TOL if epi in (0, 2) else dict(atol=2e-3, rtol=half_ulp(act))
     assert_close(got, _want(x, w, m, n, kk, epi, y0), what=f"epilogue {epi} bn{bn}", **tol)
 
 
@@ -105,14 +107,14 @@ def test_config0_gate_up_swiglu(k):
 
 @pytest.mark.parametrize("epi", [0, 1, 2, 3])
 @pytest.mark.parametrize("block", [16, 32])
-def test_baseline_kernel(k, epi, block):
+def test_baseline_kernel(k, epi, block, act):
     """The bisecting kernel (DECIDE_GEMM=baseline) against the same oracle, incl. other SwiGLU blocks."""
     from decide_b200.kernels import Family, Impl
 
     if epi != 3 and block != 16:
         pytest.skip("block only matters for SwiGLU")
     m, n, kk = 70, 192, 96
-    x, w = _operands(40, m, n, kk)
+    x, w = _operands(40, m, n, kk, act=act)
     y0 = np32(randn(41, m, n)) if epi == 2 else None
     k.dev.set_impl(Family.Gemm, Impl.Baseline)
     try:
@@ -129,7 +131,7 @@ def test_fast_equals_baseline_bitwise_when_exact(k):
 
     m, n, kk = 130, 288, 192
     g = torch.Generator().manual_seed(9)
-    x = torch.randint(-4, 5, (m, kk), generator=g).to(torch.bfloat16).cuda()
+    x = torch.randint(-4, 5, (m, kk), generator=g).to(k.dev.act_torch).cuda()
     w = torch.randint(-4, 5, (n, kk), generator=g).to(torch.bfloat16).cuda()
     outs = []
     for impl in (Impl.Fast, Impl.Baseline):
@@ -147,7 +149,7 @@ def test_contract_violations_are_errors(k):
     """What the reference asserts (gemm.rs:140-144, 159-163) comes back as DC_INVALID_ARG, nothing is launched."""
     from decide_b200.kernels import Epilogue, KernelError
 
-    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    x = torch.zeros(4, 64, dtype=k.dev.act_torch, device="cuda")
     w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     y = torch.zeros(4, 64, dtype=torch.float32, device="cuda")
     before = k.dev.launches

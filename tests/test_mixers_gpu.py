@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import cpu_ref
-from tests.util import assert_close, bf16, np32, randn, uniform
+from tests.util import assert_close, bf16, half_ulp, np32, randn, uniform
 
 pytestmark = pytest.mark.gpu
 
@@ -20,19 +20,19 @@ def _u32(x):
 
 # ------------------------------------------------------------------ rope
 @pytest.mark.parametrize("hd,rot,theta,nq", [(128, 128, 1e6, 32), (256, 64, 1e7, 16), (128, 32, 1e6, 4)])
-def test_q_norm_rope(k, hd, rot, theta, nq):
+def test_q_norm_rope(k, hd, rot, theta, nq, act):
     rows, ldq = 50, nq * hd + 64
     pq = randn(1, rows, ldq)
     w = randn(2, hd, std=0.02)
     qpos = np.random.RandomState(3).randint(0, 8192, rows)
     qpos[0], qpos[1] = 0, 8191
     inv_freq = torch.from_numpy(cpu_ref.inv_freq(rot, theta))
-    qo = torch.empty(rows, nq, hd, dtype=torch.bfloat16, device="cuda")
+    qo = torch.empty(rows, nq, hd, dtype=act, device="cuda")
     k.rope.q_norm_rope(None, pq.cuda(), w.cuda(), inv_freq.cuda(), _u32(qpos), qo, rows, ldq, nq, hd, rot)
     seg = np32(pq)[:, :nq * hd].reshape(rows, nq, hd)
     want = cpu_ref.head_norm_rope(seg, np32(w), qpos[:, None].repeat(nq, 1), rot, theta)
     # fp32 angles up to 8191 rad: sin/cos of the same fp32 angle, so only bf16 rounding remains
-    assert_close(np32(qo), want, atol=2e-3, rtol=2 ** -8, what="q_norm_rope")
+    assert_close(np32(qo), want, atol=2e-3 if act == torch.bfloat16 else 3e-4, rtol=half_ulp(act), what="q_norm_rope")
 
 
 @pytest.mark.parametrize("packed", [False, True])
@@ -42,8 +42,9 @@ def test_kv_norm_rope(k, packed):
     p = randn(4, rows, ld)
     w = randn(5, hd, std=0.02)
     inv_freq = torch.from_numpy(cpu_ref.inv_freq(rot, theta))
-    kc = torch.full((cache_rows, nkv, hd), 9.0, dtype=torch.bfloat16, device="cuda")
-    vc = torch.full((cache_rows, nkv, hd), 9.0, dtype=torch.bfloat16, device="cuda")
+    act = k.dev.act_torch
+    kc = torch.full((cache_rows, nkv, hd), 9.0, dtype=act, device="cuda")
+    vc = torch.full((cache_rows, nkv, hd), 9.0, dtype=act, device="cuda")
     if packed:
         pos = np.concatenate([np.arange(20), np.arange(17)])
         k.rope.kv_norm_rope(None, p.cuda(), w.cuda(), inv_freq.cuda(), kc, vc, rows, ld, kcol, vcol, 0, cache_rows, nkv, hd, rot,
@@ -56,7 +57,7 @@ def test_kv_norm_rope(k, packed):
     kseg = np32(p)[:, kcol:kcol + nkv * hd].reshape(rows, nkv, hd)
     want_k = cpu_ref.head_norm_rope(kseg, np32(w), pos[:, None].repeat(nkv, 1), rot, theta)
     assert_close(np32(kc)[dst], want_k, atol=2e-3, rtol=2 ** -8, what="k cache")
-    want_v = np32(bf16(p[:, vcol:vcol + nkv * hd])).reshape(rows, nkv, hd)
+    want_v = np32(p[:, vcol:vcol + nkv * hd].to(act)).reshape(rows, nkv, hd)
     assert np.array_equal(np32(vc)[dst], want_v)
     untouched = np.setdiff1d(np.arange(cache_rows), dst)
     assert (np32(kc)[untouched] == 9.0).all() and (np32(vc)[untouched] == 9.0).all()
@@ -66,17 +67,17 @@ def test_kv_cache_overrun_is_refused(k):
     from decide_b200.kernels import KernelError
 
     z = torch.zeros(8, 2048, device="cuda")
-    c = torch.zeros(8, 8, 128, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(8, 8, 128, dtype=k.dev.act_torch, device="cuda")
     with pytest.raises(KernelError):
         k.rope.kv_norm_rope(None, z, z, z, c, c, 8, 2048, 0, 1024, 1, 8, 8, 128, 128)
 
 
 # ------------------------------------------------------------- attention
-def _attn_case(seed, rows, nq, nkv, hd, gated, qpos=None, npos=None):
+def _attn_case(seed, rows, nq, nkv, hd, gated, qpos=None, npos=None, act=torch.float16):
     npos = npos or rows
-    q = bf16(randn(seed, rows, nq, hd))
-    kc = bf16(randn(seed + 1, npos, nkv, hd))
-    vc = bf16(randn(seed + 2, npos, nkv, hd))
+    q = randn(seed, rows, nq, hd).to(act)
+    kc = randn(seed + 1, npos, nkv, hd).to(act)
+    vc = randn(seed + 2, npos, nkv, hd).to(act)
     gate = randn(seed + 3, rows, nq * hd + 32) if gated else None
     qpos = np.arange(rows) if qpos is None else qpos
     want = cpu_ref.attention(np32(q), qpos, np32(kc), np32(vc), np32(gate)[:, :nq * hd] if gated else None, nq, nkv, hd)
@@ -85,12 +86,12 @@ def _attn_case(seed, rows, nq, nkv, hd, gated, qpos=None, npos=None):
 
 @pytest.mark.parametrize("impl", ["fast", "baseline"])
 @pytest.mark.parametrize("rows,gated", [(1, True), (64, False), (65, True), (300, True), (603, False)])
-def test_attention_single_sequence(k, impl, rows, gated):
+def test_attention_single_sequence(k, impl, rows, gated, act):
     from decide_b200.kernels import Family, Impl
 
     nq, nkv, hd = 8, 2, 128
-    q, kc, vc, gate, qpos, want = _attn_case(10 + rows, rows, nq, nkv, hd, gated)
-    y = torch.empty(rows, nq * hd, dtype=torch.bfloat16, device="cuda")
+    q, kc, vc, gate, qpos, want = _attn_case(10 + rows, rows, nq, nkv, hd, gated, act=act)
+    y = torch.empty(rows, nq * hd, dtype=act, device="cuda")
     k.dev.set_impl(Family.Attn, Impl.Baseline if impl == "baseline" else Impl.Fast)
     try:
         k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda() if gated else None, _u32(qpos), y, rows,
@@ -98,8 +99,8 @@ def test_attention_single_sequence(k, impl, rows, gated):
         k.dev.check_status()
     finally:
         k.dev.set_impl(Family.Attn, Impl.Fast)
-    # P is rounded to bf16 before PV in the fast kernel (as the reference rounds to fp16): atol covers it
-    assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what=f"attention {impl} rows={rows}")
+    # P is rounded to the activation type before PV in the fast kernel (as the reference rounds to fp16): atol covers it
+    assert_close(np32(y), want, atol=6e-3 if act == torch.bfloat16 else 1e-3, rtol=2 * half_ulp(act), what=f"attention {impl} rows={rows}")
 
 
 def test_attention_scattered_query_positions(k):
@@ -107,7 +108,7 @@ def test_attention_scattered_query_positions(k):
     nq, nkv, hd, npos = 4, 1, 128, 500
     qpos = np.array([499, 3, 250, 0, 77, 77, 128, 64, 63])
     q, kc, vc, gate, qpos, want = _attn_case(40, len(qpos), nq, nkv, hd, True, qpos=qpos, npos=npos)
-    y = torch.empty(len(qpos), nq * hd, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(len(qpos), nq * hd, dtype=k.dev.act_torch, device="cuda")
     k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda(), _u32(qpos), y, len(qpos), gate.shape[1], nq, nkv, hd)
     assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
 
@@ -120,12 +121,12 @@ def test_attention_packed_sequences(k, impl):
     lens = [70, 1, 130, 64]
     starts = np.concatenate([[0], np.cumsum(lens)])
     total = int(starts[-1])
-    q = bf16(randn(50, total, nq, hd))
-    kc = bf16(randn(51, total, nkv, hd))
-    vc = bf16(randn(52, total, nkv, hd))
+    q = randn(50, total, nq, hd).to(k.dev.act_torch)
+    kc = randn(51, total, nkv, hd).to(k.dev.act_torch)
+    vc = randn(52, total, nkv, hd).to(k.dev.act_torch)
     gate = randn(53, total, nq * hd)
     qpos = np.concatenate([np.arange(n) for n in lens])
-    y = torch.empty(total, nq * hd, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(total, nq * hd, dtype=k.dev.act_torch, device="cuda")
     k.dev.set_impl(Family.Attn, Impl.Baseline if impl == "baseline" else Impl.Fast)
     try:
         k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda(), _u32(qpos), y, total, nq * hd, nq, nkv, hd,

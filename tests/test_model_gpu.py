@@ -39,7 +39,7 @@ def make(dims, dev, seed, **kw):
 
 
 @pytest.mark.parametrize("dims", [SMALL, REFLIKE], ids=["baseline-like", "reference-like"])
-def test_small_model_logits_and_layers(dev, dims):
+def test_small_model_logits_and_layers(dev, dims, act):
     sd, eng = make(dims, dev, 3, max_rows=512, max_seqs=4, max_answers=16, max_cand=8)
     model = gold_synth.build_model(dims, sd)
     lens = [70, 9, 131]

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import cpu_ref
-from tests.util import assert_close, bf16, np32, randn
+from tests.util import assert_close, bf16, half_ulp, np32, randn
 
 pytestmark = pytest.mark.gpu
 
@@ -13,13 +13,13 @@ H = 2560
 
 
 @pytest.mark.parametrize("rows,h,add_one", [(1, 2560, True), (603, 2560, True), (77, 128, False), (9, 4096, True)])
-def test_rmsnorm(k, rows, h, add_one):
+def test_rmsnorm(k, rows, h, add_one, act):
     x = randn(1, rows, h)
     w = randn(2, h, std=0.02) if add_one else randn(2, h, std=0.02, mean=1.0)
-    y = torch.empty(rows, h, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(rows, h, dtype=act, device="cuda")
     k.norm.rmsnorm(None, x.cuda(), w.cuda(), y, None, rows, h, h, h, add_one)
     want = cpu_ref.rmsnorm(np32(x), np32(w), h, add_one)
-    assert_close(np32(y), want, atol=1e-5, rtol=2 ** -8, what="rmsnorm")
+    assert_close(np32(y), want, atol=1e-5, rtol=half_ulp(act), what="rmsnorm")
 
 
 def test_rmsnorm_rowmap_and_strides(k):
@@ -27,7 +27,7 @@ def test_rmsnorm_rowmap_and_strides(k):
     x = randn(3, 100, h + 4)
     w = randn(4, h, std=0.02)
     rowmap = torch.tensor(np.random.RandomState(0).permutation(100)[:rows].astype(np.int32))
-    y = torch.full((rows, h + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+    y = torch.full((rows, h + 8), 3.0, dtype=k.dev.act_torch, device="cuda")
     k.norm.rmsnorm(None, x.cuda(), w.cuda(), y, rowmap.cuda(), rows, h, h + 4, h + 8, True)
     want = cpu_ref.rmsnorm(np32(x)[rowmap.numpy(), :h], np32(w), h, True)
     assert_close(np32(y)[:, :h], want, atol=1e-5, rtol=2 ** -8, what="rmsnorm rowmap")
@@ -38,7 +38,7 @@ def test_rmsnorm_by_hand(k):
     """The reference's known answer (cpu_ref.rs:204-211) scaled to the kernel's 4-wide vectors."""
     x = torch.tensor([[3.0, 4.0, 3.0, 4.0]])
     w = torch.ones(4)
-    y = torch.empty(1, 4, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(1, 4, dtype=k.dev.act_torch, device="cuda")
     k.norm.rmsnorm(None, x.cuda(), w.cuda(), y, None, 1, 4, 4, 4, True)
     want = np.array([[3.0, 4.0, 3.0, 4.0]]) * 2.0 / np.sqrt(12.5)
     assert_close(np32(y), want, atol=0, rtol=2 ** -8, what="rmsnorm KAT")
@@ -87,12 +87,12 @@ def test_final_head(k, rows, max_cand):
 
 
 @pytest.mark.parametrize("t,nv", [(1, 16), (603, 16), (50, 32)])
-def test_gated_rmsnorm_silu(k, t, nv):
+def test_gated_rmsnorm_silu(k, t, nv, act):
     dv, ldz = 128, nv * 128 + 96
     o = randn(12, t, nv * dv, std=0.5)
     z = randn(13, t, ldz)
     w = randn(14, dv, std=0.02, mean=1.0)
-    y = torch.empty(t, nv * dv, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty(t, nv * dv, dtype=act, device="cuda")
     k.gnorm.gated_rmsnorm_silu(None, o.cuda(), z.cuda(), w.cuda(), y, t, ldz, nv)
     want = cpu_ref.gated_rmsnorm_silu(np32(o), np32(z), ldz, np32(w), t, nv, dv)
-    assert_close(np32(y), want, atol=1e-5, rtol=2 ** -8, what="gated_rmsnorm_silu")
+    assert_close(np32(y), want, atol=1e-5, rtol=half_ulp(act), what="gated_rmsnorm_silu")

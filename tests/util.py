@@ -37,3 +37,8 @@ def assert_close(got, want, atol: float, rtol: float, what: str = ""):
         raise AssertionError(
             f"{what}: max error {err.max():.3e}, {used * 100:.0f}% of tolerance at {i}: got {got[i]!r}, want {want[i]!r}")
     return used
+
+
+def half_ulp(dtype) -> float:
+    """Relative rounding step of a 16-bit activation type, with a little slack."""
+    return 2 ** -8 if dtype == torch.bfloat16 else 2 ** -10
