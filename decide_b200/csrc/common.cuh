@@ -36,7 +36,7 @@ struct dc_ctx {
     uint32_t gemm_impl = DC_IMPL_FAST;
     uint32_t attn_impl = DC_IMPL_FAST;
     uint32_t delta_impl = DC_IMPL_FAST;
-    uint32_t act_dtype = DC_ACT_F16;  // storage type of 16-bit activations (weights are always bf16)
+    uint32_t act_dtype = DC_ACT_F16;  // type of every 16-bit GEMM operand: activations and weight matrices
     void* workspace = nullptr;       // scratch for the chunked delta rule and other multi-pass ops
     size_t workspace_bytes = 0;
 };
@@ -70,8 +70,9 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// The two 16-bit activation formats. Weights are always bf16; 16-bit ACTIVATIONS (normed rows, gated
-// outputs, the MLP intermediate, attention q/k/v) are stored in the context's activation type.
+// The two 16-bit formats. Every 16-bit GEMM operand of a context, activations (normed rows, gated
+// outputs, the MLP intermediate, attention q/k/v) and weight matrices alike, is stored in that
+// context's type; the embedding table is always bf16.
 struct ActBF16 {
     static constexpr uint32_t kUmmaFormat = 1;  // tcgen05 instruction-descriptor code for bf16
     static __device__ __forceinline__ uint32_t pack(float lo, float hi) {

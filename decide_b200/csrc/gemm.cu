@@ -21,7 +21,7 @@ constexpr int RK = 16;   // its k step
 // 64 OUTPUT columns: column j pairs W row gate(j) = (j / sb) * 2 sb + j % sb with row gate(j) + sb.
 template <int EPI, typename Act>
 __global__ void __launch_bounds__(256)
-gemm_baseline_kernel(const uint16_t* __restrict__ x, const __nv_bfloat16* __restrict__ w, void* __restrict__ y,
+gemm_baseline_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, void* __restrict__ y,
                      uint32_t m, uint32_t n, uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t sb) {
     constexpr bool kSwiglu = (EPI == DC_EPI_SWIGLU_BF16);
     __shared__ float xs[RK][RT + 1];
@@ -41,10 +41,10 @@ gemm_baseline_kernel(const uint16_t* __restrict__ x, const __nv_bfloat16* __rest
             if (j < n_out && k0 + kk < k) {
                 if constexpr (kSwiglu) {
                     const uint32_t g = (j / sb) * 2 * sb + (j % sb);
-                    ws[0][kk][r] = __bfloat162float(w[static_cast<size_t>(g) * ldw + k0 + kk]);
-                    ws[1][kk][r] = __bfloat162float(w[static_cast<size_t>(g + sb) * ldw + k0 + kk]);
+                    ws[0][kk][r] = Act::one(w[static_cast<size_t>(g) * ldw + k0 + kk]);
+                    ws[1][kk][r] = Act::one(w[static_cast<size_t>(g + sb) * ldw + k0 + kk]);
                 } else {
-                    ws[0][kk][r] = __bfloat162float(w[static_cast<size_t>(j) * ldw + k0 + kk]);
+                    ws[0][kk][r] = Act::one(w[static_cast<size_t>(j) * ldw + k0 + kk]);
                 }
             } else {
                 ws[0][kk][r] = 0.0f;
@@ -96,9 +96,9 @@ int launch_baseline(dc_ctx* ctx, cudaStream_t s, const void* x, const void* w, v
     const uint32_t n_out = EPI == DC_EPI_SWIGLU_BF16 ? n / 2 : n;
     dim3 grid((n_out + RT - 1) / RT, (m + RT - 1) / RT);
     if (ctx->act_dtype == DC_ACT_F16)
-        gemm_baseline_kernel<EPI, ActF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const __nv_bfloat16*>(w), y, m, n, k, ldx, ldw, ldy, sb);
+        gemm_baseline_kernel<EPI, ActF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), y, m, n, k, ldx, ldw, ldy, sb);
     else
-        gemm_baseline_kernel<EPI, ActBF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const __nv_bfloat16*>(w), y, m, n, k, ldx, ldw, ldy, sb);
+        gemm_baseline_kernel<EPI, ActBF16><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(w), y, m, n, k, ldx, ldw, ldy, sb);
     return dc_check_launch(ctx, "gemm (baseline)");
 }
 

@@ -1,5 +1,5 @@
-// Y = X * W^T with fused epilogues on the 5th-generation tensor cores (tcgen05), bf16 operands,
-// fp32 accumulation in tensor memory (TMEM).
+// Y = X * W^T with fused epilogues on the 5th-generation tensor cores (tcgen05), 16-bit operands
+// (bf16 or fp16, the context's 16-bit type), fp32 accumulation in tensor memory (TMEM).
 //
 // Replaces the reference's tiled GEMM `gemm_nt_fast*` (kernels/gemm_fast.metal:289-351) and its
 // four epilogues (kernels/gemm.rs:16-26). Structure of one CTA (192 threads, one CTA per SM,
@@ -29,7 +29,7 @@ constexpr uint32_t kTmemCols = 512;
 struct GemmArgs {
     uint32_t m, n, k, ldy;
     uint32_t m_tiles, n_tiles, k_blocks, group_m;
-    uint32_t idesc;  // tcgen05 instruction descriptor: A = the activation type, B = bf16, D = fp32
+    uint32_t idesc;  // tcgen05 instruction descriptor: A and B in the context's 16-bit type, D = fp32
 };
 
 template <int BN>
@@ -358,11 +358,14 @@ int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, v
     a.k_blocks = (k + BK - 1) / BK;
     a.group_m = a.m_tiles < 16 ? a.m_tiles : 16;
     const bool f16 = ctx->act_dtype == DC_ACT_F16;
-    a.idesc = umma_idesc(f16 ? ActF16::kUmmaFormat : ActBF16::kUmmaFormat, ActBF16::kUmmaFormat, BM, static_cast<int>(bn));
+    // Both operands carry the same format code: kind::f16 with an fp16 A and a bf16 B raises an
+    // illegal-instruction fault on sm_100a.
+    const uint32_t fmt = f16 ? ActF16::kUmmaFormat : ActBF16::kUmmaFormat;
+    a.idesc = umma_idesc(fmt, fmt, BM, static_cast<int>(bn));
     CUtensorMap tx, tw;
     int rc = make_tmap(ctx, x, m, k, ldx, BM, f16, &tx);
     if (rc != DC_OK) return rc;
-    rc = make_tmap(ctx, w, n, k, ldw, bn, false, &tw);
+    rc = make_tmap(ctx, w, n, k, ldw, bn, f16, &tw);
     if (rc != DC_OK) return rc;
     if (bn == 256) return launch_epi<256>(ctx, stream, tx, tw, y, a, epi);
     return launch_epi<128>(ctx, stream, tx, tw, y, a, epi);

@@ -147,8 +147,8 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
     return d;
 }
 
-// Instruction descriptor of kind::f16: 16-bit A and B (format code 0 = fp16, 1 = bf16, chosen per
-// operand), fp32 accumulator, both operands K-major, M x N tile.
+// Instruction descriptor of kind::f16: 16-bit A and B (format code 0 = fp16, 1 = bf16; the two
+// operands must use the same code), fp32 accumulator, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_format, uint32_t b_format, int m, int n) {
     return (1u << 4)                                  // D format fp32
            | (a_format << 7)                          // A format

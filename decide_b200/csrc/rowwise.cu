@@ -126,12 +126,65 @@ gated_rmsnorm_silu_kernel(const float* __restrict__ o, const float* __restrict__
     reinterpret_cast<uint2*>(y + static_cast<size_t>(idx) * 128)[lane] = out;
 }
 
+// bf16 -> fp16 with the converter's precision-loss counters (convert.rs:73-90): [1] subnormal results,
+// [2] non-zero values flushed to zero, [3] finite values that overflow to infinity.
+__global__ void __launch_bounds__(256)
+convert_bf16_to_f16_kernel(const uint16_t* src, uint16_t* dst, size_t n, unsigned long long* counters) {
+    unsigned long long sub = 0, flushed = 0, over = 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float x = __uint_as_float(static_cast<uint32_t>(src[i]) << 16);
+        const __half h = __float2half_rn(x);
+        const uint16_t bits = __half_as_ushort(h);
+        const uint16_t mag = bits & 0x7fffu;
+        if (mag == 0x7c00u && isfinite(x)) ++over;
+        else if (mag == 0 && x != 0.0f) ++flushed;
+        else if (mag != 0 && mag < 0x0400u) ++sub;
+        dst[i] = bits;
+    }
+    sub = __reduce_add_sync(0xffffffffu, static_cast<unsigned>(sub));
+    flushed = __reduce_add_sync(0xffffffffu, static_cast<unsigned>(flushed));
+    over = __reduce_add_sync(0xffffffffu, static_cast<unsigned>(over));
+    if ((threadIdx.x & 31) == 0) {
+        if (sub) atomicAdd(&counters[1], sub);
+        if (flushed) atomicAdd(&counters[2], flushed);
+        if (over) atomicAdd(&counters[3], over);
+    }
+}
+
 inline uint32_t blocks_for(uint32_t warps) { return (warps + kWarpsPerBlock - 1) / kWarpsPerBlock; }
 inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 }  // namespace
 
 extern "C" {
+
+int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst, size_t n, dc_convert_report* report) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, src && dst, "convert: null operand");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long* counters = static_cast<unsigned long long*>(dc_workspace(ctx, 64));
+    if (!counters) return dc_fail(ctx, DC_CUDA_ERROR, "convert: no workspace");
+    cudaError_t e = cudaMemsetAsync(counters, 0, 32, s);
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "convert: %s", cudaGetErrorString(e));
+    if (n) {
+        const size_t want = (n + 255) / 256;
+        const uint32_t blocks = static_cast<uint32_t>(want < static_cast<size_t>(ctx->sm_count) * 16 ? want : static_cast<size_t>(ctx->sm_count) * 16);
+        convert_bf16_to_f16_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), n, counters);
+        int rc = dc_check_launch(ctx, "convert_bf16_to_f16");
+        if (rc != DC_OK) return rc;
+    }
+    unsigned long long host[4] = {0, 0, 0, 0};
+    e = cudaMemcpyAsync(host, counters, 32, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "convert: %s", cudaGetErrorString(e));
+    if (report) {
+        report->values += n;
+        report->f16_subnormal += host[1];
+        report->f16_flushed_to_zero += host[2];
+        report->f16_overflow += host[3];
+    }
+    return DC_OK;
+}
 
 int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* y, const uint32_t* rowmap, uint32_t rows,
                uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps, uint32_t add_one) {

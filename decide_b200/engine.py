@@ -14,7 +14,7 @@ import ctypes
 import numpy as np
 import torch
 
-from .kernels import Device, KernelError, _stream
+from .kernels import Act, ConvertReport, Device, KernelError, _stream
 from .synth import Batch
 from .weights import LAYER_FIELDS, CDims, CLayerWeights, Dims, fuse_layer
 
@@ -41,6 +41,19 @@ class Engine:
                 fused_layers.append({k: v.to(cuda) for k, v in fuse_layer(state_dict, l, dims).items()})
             embed = state_dict["embed_tokens.weight"].to(torch.bfloat16).to(cuda)
             final_norm = state_dict["norm.weight"].to(torch.float32).to(cuda)
+        # Weight matrices are stored in the context's 16-bit type. In fp16 mode the bf16 checkpoint values
+        # are converted once, in place, refusing a model whose weights overflow fp16
+        # (crates/decide-engine/src/convert.rs:73-98).
+        self.convert_report = ConvertReport()
+        if self.dev.act == Act.F16:
+            for lw in fused_layers:
+                for name in ("w_in", "w_out", "w_gu", "w_down"):
+                    if lw[name].dtype == torch.bfloat16:
+                        lw[name] = self.dev.convert_bf16_to_f16(lw[name], self.convert_report)
+            if self.convert_report.f16_overflow:
+                raise ValueError(f"{self.convert_report.f16_overflow} weights overflow fp16")
+        want = torch.float16 if self.dev.act == Act.F16 else torch.bfloat16
+        assert all(lw[n].dtype == want for lw in fused_layers for n in ("w_in", "w_out", "w_gu", "w_down")), "weights are not in the context's 16-bit type"
         self.layers, self.embed, self.final_norm = fused_layers, embed, final_norm  # keep the device tensors alive
         arr = (CLayerWeights * dims.n_layers)()
         for l, lw in enumerate(fused_layers):

@@ -48,9 +48,17 @@ class Family(enum.IntEnum):
 
 
 class Act(enum.IntEnum):
-    """Storage type of the 16-bit activations (DC_ACT_*); weights are always bf16."""
+    """The context's 16-bit type (DC_ACT_*): activations and weight matrices alike."""
     BF16 = 0
     F16 = 1
+
+
+class ConvertReport(ctypes.Structure):
+    """dc_convert_report: the converter's fp16 precision-loss counters (convert.rs:64-71)."""
+    _fields_ = [(n, ctypes.c_uint64) for n in ("values", "f16_subnormal", "f16_flushed_to_zero", "f16_overflow")]
+
+    def as_dict(self):
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
 
 
 def _ptr(arg) -> int:
@@ -126,6 +134,14 @@ class Device:
     def act_torch(self) -> torch.dtype:
         """torch dtype of the 16-bit activation buffers this context reads and writes."""
         return torch.float16 if self.act == Act.F16 else torch.bfloat16
+
+    def convert_bf16_to_f16(self, t: torch.Tensor, report: ConvertReport | None = None) -> torch.Tensor:
+        """Converts a bf16 device tensor to fp16 IN PLACE and returns it viewed as fp16; adds the
+        precision-loss counts to `report`. Synchronises."""
+        assert t.dtype == torch.bfloat16 and t.is_cuda and t.is_contiguous()
+        self.call("dc_convert_bf16_to_f16", _stream(None), t.data_ptr(), t.data_ptr(), t.numel(),
+                  ctypes.byref(report) if report is not None else None)
+        return t.view(torch.float16)
 
     @property
     def launches(self) -> int:

@@ -53,12 +53,14 @@ enum {
 enum { DC_IMPL_FAST = 0, DC_IMPL_BASELINE = 1 };
 enum { DC_FAMILY_GEMM = 0, DC_FAMILY_ATTN = 1, DC_FAMILY_DELTA = 2 };
 
-/* Storage type of the 16-bit ACTIVATIONS (normed rows, gated outputs, the MLP intermediate, attention
- * q/k/v and its output). Weights and the embedding table are always bf16. The reference keeps its
- * 16-bit activations in fp16 because bf16 missed its 0.01 probability tolerance (README.md:88-90,
- * 207-208); DC_ACT_F16 is the default here for the same reason, and the tensor cores multiply fp16
- * activations by bf16 weights directly. Wherever this header says "bf16" for an activation buffer,
- * read "the context's activation type". */
+/* The 16-bit type of a context: every 16-bit GEMM operand, i.e. the activations (normed rows, gated
+ * outputs, the MLP intermediate, attention q/k/v and its output) AND the weight matrices, is stored
+ * in it. The embedding table is always bf16. The reference converts its bf16 checkpoint to fp16 and
+ * keeps fp16 activations because bf16 missed its 0.01 probability tolerance (README.md:88-90,
+ * 207-208; convert.rs:73-90); DC_ACT_F16 is the default here for the same measured reason (bf16
+ * activations alone put ~0.6% relative error into the residual per layer). dc_convert_bf16_to_f16
+ * converts bf16 weights. Wherever this header says "bf16" for a GEMM operand or an activation
+ * buffer, read "the context's 16-bit type". The tensor cores cannot mix the two in one MMA. */
 enum { DC_ACT_BF16 = 0, DC_ACT_F16 = 1 };
 
 /* ---- context: replaces DecideDevice::shared + Kernels::new (device.rs:125-130, mod.rs:54-66) ---- */
@@ -70,7 +72,7 @@ size_t dc_last_error(dc_ctx* ctx, char* buf, size_t len);
  * DECIDE_DELTA environment variables are read once, as Gemm::new etc. do. */
 int dc_set_impl(dc_ctx* ctx, uint32_t family, uint32_t impl);
 uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family);
-/* Activation storage type (DC_ACT_*); at open it is read from DECIDE_ACT = f16 | bf16 (default f16). */
+/* The context's 16-bit type (DC_ACT_*); at open it is read from DECIDE_ACT = f16 | bf16 (default f16). */
 int dc_set_activation_dtype(dc_ctx* ctx, uint32_t act);
 uint32_t dc_get_activation_dtype(dc_ctx* ctx);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
@@ -83,6 +85,15 @@ uint64_t dc_launch_count(dc_ctx* ctx);
 int dc_reserve_workspace(dc_ctx* ctx, size_t bytes);
 /* Number of SMs of the context's device. */
 int dc_sm_count(dc_ctx* ctx);
+
+/* ---- weight conversion (bf16_to_f16 of the converter, crates/decide-engine/src/convert.rs:73-90) ----
+ * dst[i] = fp16(src[i]) for n bf16 values, round to nearest even; dst may be src (in place). Adds to
+ * *report (host memory, may be NULL) how many values became fp16 subnormals, were flushed to zero or
+ * overflowed to infinity, as the reference's precision-loss report does. Synchronises the stream. */
+typedef struct dc_convert_report {
+    uint64_t values, f16_subnormal, f16_flushed_to_zero, f16_overflow;
+} dc_convert_report;
+int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst, size_t n, dc_convert_report* report);
 
 /* ---- Gemm::gemm (kernels/gemm.rs:138-175; spec cpu_ref.rs:25-50) ----
  * Y = X * W^T then `epilogue`. X bf16 [M,K] row stride ldx; W bf16 [N,K] row stride ldw;

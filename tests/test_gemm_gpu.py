@@ -1,7 +1,7 @@
 """GEMM parity on the GPU, through the C ABI, against the restated cpu_ref::gemm_nt +
 swiglu_interleaved (oracle/cpu_ref.py). Inputs are seeded, rounded to bf16 once, and shared
-bit-for-bit by both sides. X is stored in the context's activation type (fp16 by default, bf16
-also run), W always in bf16: the tensor cores multiply the two formats directly. Tolerances: fp32 outputs atol 2e-4 + rtol 2e-5 (fp32 accumulation of
+bit-for-bit by both sides. X and W are stored in the context's 16-bit type (fp16 by default, bf16
+also run). Tolerances: fp32 outputs atol 2e-4 + rtol 2e-5 (fp32 accumulation of
 up to 9728 bf16 products of magnitude ~0.02); bf16 outputs add bf16's half-ulp, rtol 2^-8."""
 import numpy as np
 import pytest
@@ -17,12 +17,12 @@ BF16_TOL = dict(atol=2e-3, rtol=2 ** -8)
 
 
 def _operands(seed, m, n, k, ldx=None, ldw=None, act=torch.float16):
-    """X in the activation type, W in bf16, both rounded once and shared with the oracle."""
+    """X and W in the context's 16-bit type, rounded once and shared with the oracle."""
     ldx, ldw = ldx or k, ldw or k
     x = torch.zeros(m, ldx, dtype=act)
-    w = torch.zeros(n, ldw, dtype=torch.bfloat16)
+    w = torch.zeros(n, ldw, dtype=act)
     x[:, :k] = randn(seed, m, k).to(act)
-    w[:, :k] = bf16(randn(seed + 1, n, k, std=0.02))
+    w[:, :k] = randn(seed + 1, n, k, std=0.02).to(act)
     return x, w
 
 
@@ -132,7 +132,7 @@ def test_fast_equals_baseline_bitwise_when_exact(k):
     m, n, kk = 130, 288, 192
     g = torch.Generator().manual_seed(9)
     x = torch.randint(-4, 5, (m, kk), generator=g).to(k.dev.act_torch).cuda()
-    w = torch.randint(-4, 5, (n, kk), generator=g).to(torch.bfloat16).cuda()
+    w = torch.randint(-4, 5, (n, kk), generator=g).to(k.dev.act_torch).cuda()
     outs = []
     for impl in (Impl.Fast, Impl.Baseline):
         k.dev.set_impl(Family.Gemm, impl)
@@ -150,7 +150,7 @@ def test_contract_violations_are_errors(k):
     from decide_b200.kernels import Epilogue, KernelError
 
     x = torch.zeros(4, 64, dtype=k.dev.act_torch, device="cuda")
-    w = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(64, 64, dtype=k.dev.act_torch, device="cuda")
     y = torch.zeros(4, 64, dtype=torch.float32, device="cuda")
     before = k.dev.launches
     for args in [(4, 48, 64, 64, 64, 64), (4, 64, 48, 64, 64, 64), (0, 64, 64, 64, 64, 64), (4, 64, 64, 32, 64, 64),

@@ -96,3 +96,23 @@ def test_gated_rmsnorm_silu(k, t, nv, act):
     k.gnorm.gated_rmsnorm_silu(None, o.cuda(), z.cuda(), w.cuda(), y, t, ldz, nv)
     want = cpu_ref.gated_rmsnorm_silu(np32(o), np32(z), ldz, np32(w), t, nv, dv)
     assert_close(np32(y), want, atol=1e-5, rtol=half_ulp(act), what="gated_rmsnorm_silu")
+
+
+def test_convert_bf16_to_f16_with_report(k):
+    """The weight converter's rounding and its precision-loss counters (convert.rs:73-90)."""
+    from decide_b200.kernels import ConvertReport
+
+    x = randn(20, 4096, std=0.02)
+    x[:8] = torch.tensor([0.0, 1e-5, -3e-6, 1e-9, 7e4, -1e30, 65504.0, 6.2e-5])  # subnormal x2, flushed, overflow x2
+    src = bf16(x)
+    rep = ConvertReport()
+    out = k.dev.convert_bf16_to_f16(src.clone().cuda(), rep)
+    want = src.float().to(torch.float16)
+    assert torch.equal(out.cpu(), want)
+    mag = want.float().abs()
+    finite_src = torch.isfinite(src.float())
+    assert rep.values == 4096
+    assert rep.f16_overflow == int((torch.isinf(want) & finite_src).sum())
+    assert rep.f16_flushed_to_zero == int(((want == 0) & (src.float() != 0)).sum())
+    assert rep.f16_subnormal == int(((mag > 0) & (mag < 2 ** -14)).sum())
+    assert rep.f16_overflow == 2 and rep.f16_flushed_to_zero >= 1 and rep.f16_subnormal >= 2
