@@ -55,3 +55,18 @@ def test_scale_probabilities_errors():
     assert head_math.scale_probabilities(["a", "b"], [0.25, 0.75], 1.0) == [0.25, 0.75]
     p = head_math.scale_probabilities(["a", "b"], [0.0, 1.0], 2.0)
     assert p == [0.0, 1.0]
+
+
+def test_check_table_rules():
+    """The parity table: |dlogit| and |dp| bars, and the margin rule for decisions (check.rs:22-25)."""
+    from decide_b200 import check
+
+    want = np.array([[2.0, 1.0, 0.0], [1.00, 0.99, 0.0], [1.0, 0.9, 0.0]], dtype=np.float32)
+    got = want.copy()
+    got[1] = [0.99, 1.0, 0.0]      # near-tie flip: gold margin 0.01 < 0.05
+    t = check.compare(got, want, [3, 3, 3])
+    assert t["failures"] == [] and len(t["small_flips"]) == 1 and t["agree"] == 2
+    got[2] = [0.94, 0.96, 0.0]     # flip with gold margin 0.1 >= 0.05, and |dlogit| 0.06 > 0.02
+    t = check.compare(got, want, [3, 3, 3])
+    assert any("decision differs" in f for f in t["failures"]) and any("dlogit" in f for f in t["failures"])
+    assert check.top2_margin(np.array([3.0])) == float("inf")

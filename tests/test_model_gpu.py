@@ -7,7 +7,7 @@ argmax decisions. Per-layer residual comparison follows the reference's debug_la
 import numpy as np
 import pytest
 
-from decide_b200 import head
+from decide_b200 import check
 from decide_b200.synth import Batch, synth_batch, synth_state_dict
 from decide_b200.weights import BASELINE_DIMS, Dims
 from oracle import gold_synth
@@ -17,18 +17,14 @@ pytestmark = pytest.mark.gpu
 SMALL = Dims(hidden=256, n_layers=4, nq=4, nkv=2, head_dim=128, rot_dim=128, gdn_nk=16, gdn_nv=16, inter=512, vocab=1000)
 REFLIKE = Dims(hidden=256, n_layers=4, nq=4, nkv=1, head_dim=128, rot_dim=32, gdn_nk=8, gdn_nv=16, inter=256, vocab=500, rope_theta=1e7)
 
-LOGIT_TOL, P_TOL = 0.02, 0.01
-
-
 def check_parity(got, want, ncand, what):
-    dl = max(np.abs(got[i, :n] - want[i, :n]).max() for i, n in enumerate(ncand))
-    pg, dg = head.decide(got, ncand)
-    pw, dw = head.decide(want, ncand)
-    dp = np.abs(pg - pw).max()
-    assert dl <= LOGIT_TOL, f"{what}: max |dlogit| = {dl:.4f}"
-    assert dp <= P_TOL, f"{what}: calibrated max |dp| = {dp:.4f}"
-    assert (dg == dw).all(), f"{what}: decisions differ at {np.nonzero(dg != dw)[0].tolist()}"
-    return dl, dp
+    """max |dlogit| <= 0.02, calibrated max |dp| <= 0.01, decisions equal wherever the gold top-2 logit
+    margin is >= 0.05 (check.rs:22-25); near-tie flips under that margin are printed, not failed."""
+    t = check.compare(got, want, ncand)
+    assert not t["failures"], f"{what}: {t['failures']}"
+    if t["small_flips"]:
+        print(f"{what}: near-tie flips (gold margin < {check.MARGIN}): {t['small_flips']}")
+    return t["max_dlogit"], t["max_dp"]
 
 
 def make(dims, dev, seed, **kw):
