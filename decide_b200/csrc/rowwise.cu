@@ -151,6 +151,11 @@ convert_bf16_to_f16_kernel(const uint16_t* src, uint16_t* dst, size_t n, unsigne
     }
 }
 
+// Scratch of dc_convert_bf16_to_f16_noalloc: the four precision-loss counters, resident in every
+// GPU that loads the library. In host code this name is only a stand-in for the device symbol; the
+// device address comes from cudaGetSymbolAddress (see noalloc_counters()).
+static __device__ __align__(256) unsigned long long g_noalloc_counters[4];
+
 inline uint32_t blocks_for(uint32_t warps) { return (warps + kWarpsPerBlock - 1) / kWarpsPerBlock; }
 inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
@@ -177,6 +182,62 @@ int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst
     e = cudaMemcpyAsync(host, counters, 32, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "convert: %s", cudaGetErrorString(e));
+    if (report) {
+        report->values += n;
+        report->f16_subnormal += host[1];
+        report->f16_flushed_to_zero += host[2];
+        report->f16_overflow += host[3];
+    }
+    return DC_OK;
+}
+
+// Device address of g_noalloc_counters on the current device, looked up once per device.
+static cudaError_t noalloc_counters(int device, unsigned long long** out) {
+    constexpr int kMaxDevices = 64;
+    static unsigned long long* cached[kMaxDevices] = {};
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!cached[device]) {
+        unsigned long long* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_counters);
+        if (e != cudaSuccess) return e;
+        cached[device] = p;
+    }
+    *out = cached[device];
+    return cudaSuccess;
+}
+
+int dc_convert_bf16_to_f16_noalloc(void* stream, const void* src, void* dst, size_t n, dc_convert_report* report, char* err,
+                                   size_t err_len) {
+    auto fail = [&](int code, const char* msg, const char* detail) {
+        if (err && err_len) snprintf(err, err_len, "dc_convert_bf16_to_f16_noalloc: %s%s%s", msg, detail ? ": " : "", detail ? detail : "");
+        return code;
+    };
+    if (err && err_len) err[0] = 0;
+    if (!src || !dst) return fail(DC_INVALID_ARG, "null operand", nullptr);
+    if (n > DC_NOALLOC_MAX_VALUES) return fail(DC_INVALID_ARG, "more than DC_NOALLOC_MAX_VALUES (2^32) values in one call; split the tensor", nullptr);
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return fail(DC_CUDA_ERROR, "no current device", cudaGetErrorString(e));
+    unsigned long long* counters = nullptr;
+    e = noalloc_counters(device, &counters);
+    if (e != cudaSuccess) return fail(DC_CUDA_ERROR, "cannot resolve the scratch symbol", cudaGetErrorString(e));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    e = cudaMemsetAsync(counters, 0, 4 * sizeof(unsigned long long), s);  // the array keeps the last call's counts
+    if (e != cudaSuccess) return fail(DC_CUDA_ERROR, "clearing the scratch failed", cudaGetErrorString(e));
+    if (n) {
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess || sms <= 0) return fail(DC_CUDA_ERROR, "cannot read the SM count", e != cudaSuccess ? cudaGetErrorString(e) : nullptr);
+        const size_t want = (n + 255) / 256;
+        const uint32_t blocks = static_cast<uint32_t>(want < static_cast<size_t>(sms) * 16 ? want : static_cast<size_t>(sms) * 16);
+        convert_bf16_to_f16_kernel<<<blocks, 256, 0, s>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), n, counters);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(DC_CUDA_ERROR, "launch failed", cudaGetErrorString(e));
+    }
+    unsigned long long host[4] = {0, 0, 0, 0};
+    e = cudaMemcpyAsync(host, counters, sizeof host, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(DC_CUDA_ERROR, "reading the counters back failed", cudaGetErrorString(e));
     if (report) {
         report->values += n;
         report->f16_subnormal += host[1];

@@ -95,6 +95,28 @@ typedef struct dc_convert_report {
 } dc_convert_report;
 int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst, size_t n, dc_convert_report* report);
 
+/* ---- the same conversion for callers that must not allocate ----
+ * No counterpart in the reference. It exists for hosts that swap a checkpoint in while another
+ * stream is serving requests, or that have already handed all device memory to one arena: for them
+ * cudaMalloc is off the table (it stalls every stream of the device while it runs, and it can simply
+ * fail when the arena owns the memory), and dc_open / dc_convert_bf16_to_f16 both allocate (the
+ * status word, the workspace holding the counters). This entry point needs no context and calls no
+ * cudaMalloc, cudaFree or other allocating routine: its four 64-bit counters live in a static array
+ * inside the library image, 256-byte aligned, which every GPU that loads the library holds until the
+ * process exits. It works on the CURRENT device and `stream` must belong to it.
+ *  - Limit: at most DC_NOALLOC_MAX_VALUES (2^32) values per call; larger n is refused with
+ *    DC_INVALID_ARG and a message in `err` (split the tensor).
+ *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress);
+ *    make that first call before any stream capture begins on that device.
+ *  - All calls share the one array, which still holds the previous call's counts: it is cleared on
+ *    `stream` at the start of every call. Two calls that overlap on the GPU (different streams, or
+ *    host threads racing on one device) corrupt each other's report; serialise them.
+ * Otherwise as dc_convert_bf16_to_f16: dst may be src, *report (may be NULL) is added to, the stream
+ * is synchronised before returning. `err` (may be NULL) receives the message of a failure. */
+#define DC_NOALLOC_MAX_VALUES (1ull << 32)
+int dc_convert_bf16_to_f16_noalloc(void* stream, const void* src, void* dst, size_t n, dc_convert_report* report,
+                                   char* err, size_t err_len);
+
 /* ---- Gemm::gemm (kernels/gemm.rs:138-175; spec cpu_ref.rs:25-50) ----
  * Y = X * W^T then `epilogue`. X bf16 [M,K] row stride ldx; W bf16 [N,K] row stride ldw;
  * ldy in elements of Y's type. fp32 accumulation. Requires N%32==0, K%32==0, M>=1,
