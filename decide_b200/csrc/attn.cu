@@ -59,6 +59,21 @@ __device__ __forceinline__ void load_tile(uint16_t* tile, const uint16_t* src, s
     }
 }
 
+// The same copy with cp.async (16 bytes per request, zero fill past `valid`): completes with the
+// thread's next cp.async.wait_group, so the next K/V tiles stream in under the current tile's MMAs.
+__device__ __forceinline__ void load_tile_async(uint16_t* tile, const uint16_t* src, size_t ld, int valid) {
+    for (int e = threadIdx.x; e < BKV * (HD / 8); e += kThreads) {
+        const int r = e >> 4, c = e & 15;
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(tile + tile_off(r, c * 8)));
+        const uint16_t* g = src + static_cast<size_t>(r < valid ? r : 0) * ld + c * 8;
+        const int bytes = r < valid ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g), "r"(bytes) : "memory");
+    }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <typename Act>
 __global__ void __launch_bounds__(kThreads)
 attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
@@ -66,9 +81,8 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
                  uint32_t ldg, uint32_t nq, uint32_t nkv, float scale_log2, const uint32_t* __restrict__ seq_start) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint16_t* qs = reinterpret_cast<uint16_t*>(smem_raw);
-    uint16_t* ks = qs + BQ * HD;
-    uint16_t* vs = ks + BKV * HD;
-    int* qp = reinterpret_cast<int*>(vs + BKV * HD);  // [BQ] position of each query row, -1 = no row
+    uint16_t* kv_tiles = qs + BQ * HD;   // two stages of (K tile, V tile)
+    int* qp = reinterpret_cast<int*>(kv_tiles + 4 * BKV * HD);  // [BQ] position of each query row, -1 = no row
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, kvh = h / (nq / nkv);
     const uint32_t row_lo = seq_start ? seq_start[seq] : 0u;
@@ -100,12 +114,25 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
     const uint16_t* vbase = vc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
     const size_t ldkv = static_cast<size_t>(nkv) * HD;
 
-    for (int j0 = 0; j0 < kv_end; j0 += BKV) {
-        __syncthreads();  // previous tiles consumed
-        const int valid = min(kv_end - j0, BKV);
-        load_tile(ks, kbase + static_cast<size_t>(j0) * ldkv, ldkv, valid);
-        load_tile(vs, vbase + static_cast<size_t>(j0) * ldkv, ldkv, valid);
+    // two-stage pipeline: tile it+1 is in flight while tile it is multiplied
+    load_tile_async(kv_tiles, kbase, ldkv, min(kv_end, BKV));
+    load_tile_async(kv_tiles + BKV * HD, vbase, ldkv, min(kv_end, BKV));
+    cp_async_commit();
+    int stage = 0;
+    for (int j0 = 0; j0 < kv_end; j0 += BKV, stage ^= 1) {
+        const int j1 = j0 + BKV;
+        if (j1 < kv_end) {
+            uint16_t* nxt = kv_tiles + (stage ^ 1) * 2 * BKV * HD;
+            load_tile_async(nxt, kbase + static_cast<size_t>(j1) * ldkv, ldkv, min(kv_end - j1, BKV));
+            load_tile_async(nxt + BKV * HD, vbase + static_cast<size_t>(j1) * ldkv, ldkv, min(kv_end - j1, BKV));
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
         __syncthreads();
+        const uint16_t* ks = kv_tiles + stage * 2 * BKV * HD;
+        const uint16_t* vs = ks + BKV * HD;
 
         float sacc[BKV / 8][4];
 #pragma unroll
@@ -174,6 +201,7 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
                 mma_16<Act>(oacc[2 * dp + 1], pf[kk], bfr[2], bfr[3]);
             }
         }
+        __syncthreads();  // this stage is free for the prefetch of the iteration after next
     }
     // row sums live split over the 4 lanes of a quad
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -284,7 +312,7 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
                                                  gate, qpos, static_cast<uint16_t*>(y), rows, ldg, nq, nkv, scale, seq_start, n_seq);
         return dc_check_launch(ctx, "attention (baseline)");
     }
-    constexpr size_t smem = (BQ + 2 * BKV) * HD * 2 + BQ * sizeof(int);
+    constexpr size_t smem = (BQ + 4 * BKV) * HD * 2 + BQ * sizeof(int);
     static bool attr_set[16] = {};
     auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;
     if (!attr_set[ctx->device & 15]) {

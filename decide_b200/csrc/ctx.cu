@@ -80,6 +80,11 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
     ctx->gemm_impl = impl_from_env("DECIDE_GEMM", &bad);
     ctx->attn_impl = impl_from_env("DECIDE_ATTN", &bad);
     ctx->delta_impl = impl_from_env("DECIDE_DELTA", &bad);
+    if (const char* d = getenv("DECIDE_DELTA_SPLIT")) {
+        if (strcmp(d, "1") == 0) ctx->delta_split = 1;
+        else if (strcmp(d, "3") == 0 || !*d) ctx->delta_split = 3;
+        else bad = true;
+    }
     if (const char* a = getenv("DECIDE_ACT")) {
         if (strcmp(a, "bf16") == 0) ctx->act_dtype = DC_ACT_BF16;
         else if (strcmp(a, "f16") == 0 || !*a) ctx->act_dtype = DC_ACT_F16;
@@ -159,6 +164,13 @@ int dc_set_activation_dtype(dc_ctx* ctx, uint32_t act) {
 }
 
 uint32_t dc_get_activation_dtype(dc_ctx* ctx) { return ctx ? ctx->act_dtype : DC_ACT_F16; }
+
+int dc_set_delta_split(dc_ctx* ctx, uint32_t split) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, split == 1 || split == 3, "dc_set_delta_split: %u is neither 1 nor 3", split);
+    ctx->delta_split = split;
+    return DC_OK;
+}
 
 int dc_check_status(dc_ctx* ctx, void* stream) {
     if (!ctx) return DC_INVALID_ARG;

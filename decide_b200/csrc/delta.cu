@@ -4,12 +4,20 @@
 //   S <- g S;  kv = S k;  delta = (v - kv) beta;  S <- S + k (x) delta;  o = S q
 // with the state S[h] stored [dv][dk].
 //
-// Sequential kernel: a group of DKS lanes owns one value column of one head and keeps that state
+// This file holds the SEQUENTIAL kernel, the reference's own algorithm (delta.metal, delta_fast.metal),
+// kept as the baseline (DECIDE_DELTA=baseline) that bisects the chunked kernel of delta_chunk.cu.
+// A group of DKS lanes owns one value column of one head and keeps that state
 // row in registers (128/DKS values per lane), so the two dot products per token are in-register
 // FMA chains plus log2(DKS) shuffles. Tokens are staged through shared memory 16 at a time. The
 // value columns of all heads and sequences run in parallel; DKS trades per-thread work for more
 // threads when there are few sequences.
 #include "common.cuh"
+
+size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv);
+int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const float* k, const float* v, const float* a, const float* b,
+                           const float* a_log, const float* dt_bias, const float* state_in, float* state_out, float* o, uint32_t t,
+                           uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, const uint32_t* seq_start, uint32_t n_seq,
+                           uint32_t max_len, uint32_t split);
 
 namespace {
 
@@ -126,7 +134,7 @@ inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 1
 extern "C" int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, const float* v, const float* a,
                               const float* b, const float* a_log, const float* dt_bias, const float* state_in,
                               float* state_out, float* o, uint32_t t, uint32_t ldab, uint32_t write_state, uint32_t nk,
-                              uint32_t nv, uint32_t dk, uint32_t dv, const uint32_t* seq_start, uint32_t n_seq) {
+                              uint32_t nv, uint32_t dk, uint32_t dv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
     if (!ctx) return DC_INVALID_ARG;
     DC_REQUIRE(ctx, q && k && v && a && b && a_log && dt_bias && o, "gated_delta: null operand");
     DC_REQUIRE(ctx, !write_state || state_out, "gated_delta: write_state without a state_out buffer");
@@ -138,10 +146,17 @@ extern "C" int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const f
     if (!seq_start) {
         DC_REQUIRE(ctx, t >= 1, "delta: T must be at least 1");
         n_seq = 1;
+        max_len = t;
     }
+    if (max_len == 0 || max_len > t) max_len = t;
     DC_REQUIRE(ctx, n_seq >= 1 && n_seq <= 65535, "gated_delta: %u sequences", n_seq);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Enough threads to fill the GPU: one lane per value column when there are many sequences,
+    if (ctx->delta_impl == DC_IMPL_FAST) {
+        DC_REQUIRE(ctx, aligned16(v) && aligned16(o) && ldab >= nv, "gated_delta (chunked): v and o must be 16-byte aligned");
+        return dc_gated_delta_chunked(ctx, s, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, write_state, nk, nv, seq_start, n_seq,
+                                      max_len, ctx->delta_split);
+    }
+    // Baseline: the sequential recurrence. Enough threads to fill the GPU: one lane per value column when there are many sequences,
     // up to 8 lanes per column for a single sequence.
     const uint64_t cols = static_cast<uint64_t>(n_seq) * nv * 128;
     const uint64_t want = static_cast<uint64_t>(ctx->sm_count) * 512;
@@ -153,3 +168,5 @@ extern "C" int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const f
         launch_seq<8>(s, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, nk, nv, write_state, seq_start, n_seq);
     return dc_check_launch(ctx, "gated_delta");
 }
+
+extern "C" size_t dc_gated_delta_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) { return dc_delta_chunk_scratch_bytes(t, n_seq ? n_seq : 1, nv); }

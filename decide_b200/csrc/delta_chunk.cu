@@ -1,0 +1,507 @@
+// Chunk-64 gated delta rule (the WY / UT-transform form) on tensor cores.
+//
+// Same recurrence as the sequential kernel of delta.cu (spec cpu_ref.rs:101-129), regrouped per
+// chunk of C = 64 tokens as the reference's gold model does (the torch_chunk_gated_delta_rule of the
+// transformers Qwen3.5 model). With G_i the cumulative log decay inside the chunk, beta_i the write
+// strength and S the state before the chunk (here S is [dk][dv]):
+//   L   = strictly-lower( beta_i (k_i . k_j) e^{G_i - G_j} )            T = (I + L)^-1
+//   W   = T (beta k e^{G})                 U = T (beta v)
+//   v'  = U - W S                          o = (q e^{G}) S + lower((q_i . k_j) e^{G_i - G_j}) v'
+//   S  <- e^{G_last} S + (k e^{G_last - G})^T v'
+// Kernel 1 (all chunks of all heads and sequences in parallel) builds T, W, U and the masked q.k
+// matrix into scratch. Kernel 2 walks the chunks of one (sequence, head, value-column block) in
+// order with the state in registers. All products run on mma.sync bf16 with fp32 accumulation; by
+// default every fp32 operand is split into hi + lo bf16 parts (3 MMAs per product, relative error
+// ~1e-5 against fp32), because a single bf16/fp16 pass puts ~5e-4 relative error into o.
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace {
+
+using namespace dc;
+
+constexpr int C = 64;            // chunk length
+constexpr int D = 128;           // dk = dv
+constexpr int LD = 65;           // padded row stride of the fp32 64x64 work matrices
+constexpr int kSlotFloats = 2 * C * D + C * C + C;  // W, U, QK, G per (chunk, head)
+
+struct ChunkArgs {
+    const float *q, *k, *v, *a, *b, *a_log, *dt_bias;
+    const float* state_in;
+    float* state_out;
+    float* o;
+    float* scratch;
+    const uint32_t* seq_start;
+    uint32_t t, ldab, nk, nv, write_state;
+};
+
+__device__ __forceinline__ void seq_bounds(const ChunkArgs& p, uint32_t seq, uint32_t& row_lo, uint32_t& len) {
+    row_lo = p.seq_start ? p.seq_start[seq] : 0u;
+    len = p.seq_start ? p.seq_start[seq + 1] - row_lo : p.t;
+}
+// Scratch slot of chunk c of a sequence: row_lo / 64 + seq + c never collides between sequences.
+__device__ __forceinline__ float* slot_ptr(const ChunkArgs& p, uint32_t row_lo, uint32_t seq, uint32_t c, uint32_t h) {
+    const size_t slot = static_cast<size_t>(row_lo / C + seq + c);
+    return p.scratch + (slot * p.nv + h) * kSlotFloats;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Inverse of I + L for a strictly lower triangular 64x64 L (fp32, row stride LD) into N, by 16x16
+// blocks: the four diagonal blocks by in-warp forward substitution, then the off-diagonal blocks
+// one block-diagonal at a time, N_ij = -N_ii * sum_{k=j}^{i-1} L_ik N_kj. Four warps.
+__device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict__ N, float* __restrict__ P, int warp, int lane) {
+    {   // diagonal block `warp`: lane l < 16 holds column l; row i of the result needs rows < i
+        const int b0 = 16 * warp;
+        const int l = lane & 15;
+        float a[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) a[i] = L[(b0 + i) * LD + b0 + l];
+#pragma unroll
+        for (int i = 1; i < 16; ++i) {
+            float acc = a[i];
+#pragma unroll
+            for (int j = 0; j < i; ++j) {
+                const float cij = __shfl_sync(0xffffffffu, a[i], j);  // L[i][j], not yet overwritten
+                acc = fmaf(-cij, a[j], acc);                           // a[j] is already row j of the result
+            }
+            // (I + L)^-1 = I + X with X_i = -L_i - sum_j L_ij X_j; a[] holds Y = -X: Y_i = L_i - sum_j L_ij Y_j
+            a[i] = acc;
+        }
+        if (lane < 16) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) N[(b0 + i) * LD + b0 + l] = (i == l) ? 1.0f : (l < i ? -a[i] : 0.0f);
+        }
+        // blocks above the diagonal are zero
+        for (int e = lane; e < 16 * 16 * 3; e += 32) {
+            const int jb = e / 256, r = (e / 16) % 16, cc = e % 16;
+            const int bj = (warp + 1 + jb);
+            if (bj < 4) N[(b0 + r) * LD + 16 * bj + cc] = 0.0f;
+        }
+    }
+    float* Pw = P + warp * 16 * 17;
+    const int r = lane >> 1, c0 = (lane & 1) * 8;
+    for (int d = 1; d < 4; ++d) {
+        __syncthreads();
+        const int i = d + warp, j = warp;  // block (i, j) with i - j = d
+        if (i < 4) {
+            float acc[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+            for (int kb = j; kb < i; ++kb) {
+#pragma unroll 4
+                for (int t = 0; t < 16; ++t) {
+                    const float lv = L[(16 * i + r) * LD + 16 * kb + t];
+                    const float* nrow = N + (16 * kb + t) * LD + 16 * j + c0;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) acc[c] = fmaf(lv, nrow[c], acc[c]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) Pw[r * 17 + c0 + c] = acc[c];
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+#pragma unroll 4
+            for (int t = 0; t < 16; ++t) {
+                const float nv = N[(16 * i + r) * LD + 16 * i + t];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[c] = fmaf(nv, Pw[t * 17 + c0 + c], acc[c]);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) N[(16 * i + r) * LD + 16 * j + c0 + c] = -acc[c];
+        }
+    }
+    __syncthreads();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 1: one CTA (4 warps) per (chunk, head, sequence). Shared memory: K and Q tiles (hi, lo),
+// reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased onto L.
+constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 2 * C * 4;
+
+template <int SPLIT>
+__global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArgs p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __nv_bfloat16* kh = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* kl = kh + C * D;
+    __nv_bfloat16* qh = kl + C * D;
+    __nv_bfloat16* ql = qh + C * D;
+    float* Lf = reinterpret_cast<float*>(ql + C * D);
+    float* Nf = Lf + C * LD;
+    float* Pf = Nf + C * LD;
+    float* Gs = Pf + 4 * 16 * 17;
+    float* Bs = Gs + C;
+    __nv_bfloat16* th = reinterpret_cast<__nv_bfloat16*>(Lf);  // T tiles reuse L once the inverse is in N
+    __nv_bfloat16* tl = th + C * C;
+
+    const uint32_t seq = blockIdx.z, h = blockIdx.y, c = blockIdx.x;
+    uint32_t row_lo, len;
+    seq_bounds(p, seq, row_lo, len);
+    const uint32_t r0 = c * C;
+    if (r0 >= len) return;
+    const int n = static_cast<int>(min(static_cast<uint32_t>(C), len - r0));
+    const uint32_t hk = h / (p.nv / p.nk);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t row_base = static_cast<size_t>(row_lo) + r0;
+    float* slot = slot_ptr(p, row_lo, seq, c, h);
+    float* sW = slot;
+    float* sU = slot + C * D;
+    float* sQK = slot + 2 * C * D;
+    float* sG = slot + 2 * C * D + C * C;
+
+    // gates; rows past the sequence end are padding: no decay, no write (g = 0, beta = 0, k = v = q = 0)
+    if (tid < C) {
+        float g = 0.f, be = 0.f;
+        if (tid < n) {
+            const size_t row = row_base + tid;
+            g = -expf(p.a_log[h]) * softplus_precise(p.a[row * p.ldab + h] + p.dt_bias[h]);
+            be = 1.0f / (1.0f + expf(-p.b[row * p.ldab + h]));
+        }
+        Lf[tid] = g;  // staging for the prefix sum
+        Bs[tid] = be;
+    }
+    for (int e = tid; e < C * (D / 4); e += 128) {
+        const int r = e >> 5, c4 = (e & 31) * 4;
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), qv = kv;
+        if (r < n) {
+            kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+            qv = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
+        }
+        put4<D, SPLIT>(kh, kl, r, c4, kv);
+        put4<D, SPLIT>(qh, ql, r, c4, qv);
+    }
+    __syncthreads();
+    if (tid < C) {
+        float acc = 0.f;
+        for (int i = 0; i <= tid; ++i) acc += Lf[i];
+        Gs[tid] = acc;
+        sG[tid] = acc;
+    }
+    __syncthreads();
+
+    const int m0 = 16 * warp;
+    {   // k.k^T and q.k^T, 16 rows per warp
+        float akk[8][4], aqk[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) akk[i][j] = aqk[i][j] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t kah[4], kal[4], qah[4], qal[4];
+            lda<D>(kah, kh, m0, 16 * ks, lane);
+            lda<D>(qah, qh, m0, 16 * ks, lane);
+            if constexpr (SPLIT == 3) {
+                lda<D>(kal, kl, m0, 16 * ks, lane);
+                lda<D>(qal, ql, m0, 16 * ks, lane);
+            }
+#pragma unroll
+            for (int np = 0; np < C / 16; ++np) {
+                uint32_t bh[4], bl[4];
+                ldb_nt<D>(bh, kh, 16 * np, 16 * ks, lane);
+                if constexpr (SPLIT == 3) ldb_nt<D>(bl, kl, 16 * np, 16 * ks, lane);
+                mma_split<SPLIT>(akk[2 * np], akk[2 * np + 1], kah, kal, bh, bl);
+                mma_split<SPLIT>(aqk[2 * np], aqk[2 * np + 1], qah, qal, bh, bl);
+            }
+        }
+        __syncthreads();  // Lf was the gate staging area until every thread had its prefix sum
+        const int i0 = m0 + (lane >> 2), i1 = i0 + 8;
+        const float g0 = Gs[i0], g1 = Gs[i1], b0 = Bs[i0], b1 = Bs[i1];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = nt * 8 + 2 * (lane & 3) + e;
+                const float gj = Gs[j];
+                const float d0 = j <= i0 ? expf(g0 - gj) : 0.f;
+                const float d1 = j <= i1 ? expf(g1 - gj) : 0.f;
+                Lf[i0 * LD + j] = j < i0 ? b0 * akk[nt][e] * d0 : 0.f;
+                Lf[i1 * LD + j] = j < i1 ? b1 * akk[nt][2 + e] * d1 : 0.f;
+                aqk[nt][e] *= d0;
+                aqk[nt][2 + e] *= d1;
+            }
+            const int j = nt * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2*>(sQK + i0 * C + j) = make_float2(aqk[nt][0], aqk[nt][1]);
+            *reinterpret_cast<float2*>(sQK + i1 * C + j) = make_float2(aqk[nt][2], aqk[nt][3]);
+        }
+    }
+    __syncthreads();
+    invert_unit_lower(Lf, Nf, Pf, warp, lane);
+
+    // T tiles; beta*k*e^G into the Q tiles, beta*v into the K tiles (both [token][feature])
+    for (int e = tid; e < C * (C / 2); e += 128) {
+        const int r = e >> 5, c2 = (e & 31) * 2;
+        put2<C, SPLIT>(th, tl, r, c2, Nf[r * LD + c2], Nf[r * LD + c2 + 1]);
+    }
+    for (int e = tid; e < C * (D / 4); e += 128) {
+        const int r = e >> 5, c4 = (e & 31) * 4;
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+        if (r < n) {
+            kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+            vv = *reinterpret_cast<const float4*>(p.v + ((row_base + r) * p.nv + h) * D + c4);
+            const float be = Bs[r], sk = be * expf(Gs[r]);
+            kv.x *= sk; kv.y *= sk; kv.z *= sk; kv.w *= sk;
+            vv.x *= be; vv.y *= be; vv.z *= be; vv.w *= be;
+        }
+        put4<D, SPLIT>(qh, ql, r, c4, kv);
+        put4<D, SPLIT>(kh, kl, r, c4, vv);
+    }
+    __syncthreads();
+
+    // W = T (beta k e^G), U = T (beta v)
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const __nv_bfloat16* bh_t = which == 0 ? qh : kh;
+        const __nv_bfloat16* bl_t = which == 0 ? ql : kl;
+        float* dst = which == 0 ? sW : sU;
+        float acc[16][4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks) {
+            uint32_t ah[4], al[4];
+            lda<C>(ah, th, m0, 16 * ks, lane);
+            if constexpr (SPLIT == 3) lda<C>(al, tl, m0, 16 * ks, lane);
+#pragma unroll
+            for (int np = 0; np < D / 16; ++np) {
+                uint32_t bh[4], bl[4];
+                ldb_nn<D>(bh, bh_t, 16 * ks, 16 * np, lane);
+                if constexpr (SPLIT == 3) ldb_nn<D>(bl, bl_t, 16 * ks, 16 * np, lane);
+                mma_split<SPLIT>(acc[2 * np], acc[2 * np + 1], ah, al, bh, bl);
+            }
+        }
+        const int i0 = m0 + (lane >> 2), i1 = i0 + 8;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+            const int j = nt * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2*>(dst + i0 * D + j) = make_float2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<float2*>(dst + i1 * D + j) = make_float2(acc[nt][2], acc[nt][3]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 2: one CTA (8 warps) per (value-column block of DVB, head, sequence) walks the chunks in
+// order. The state block S[dk][DVB] lives in registers (warp w owns dk rows 16w..16w+15) and, split
+// into bf16 tiles, in shared memory as the B operand of W S and (q e^G) S.
+template <int DVB, int SPLIT>
+constexpr size_t apply_smem() {
+    return static_cast<size_t>(SPLIT == 3 ? 2 : 1) * 2 * (D * DVB + 3 * C * D + C * C + C * DVB) + C * 4;
+}
+
+template <int DVB, int SPLIT>
+__global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs p) {
+    constexpr int NL = SPLIT == 3 ? 2 : 1;            // tiles per operand: hi (+ lo)
+    constexpr int NTW = DVB / 16;                     // n-tiles per warp for the 64-row products
+    constexpr int NTS = DVB / 8;                      // n-tiles of the state block
+    extern __shared__ __align__(16) uint8_t smem[];
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(smem);
+    __nv_bfloat16* Sh = base;                  __nv_bfloat16* Sl = Sh + (NL - 1) * D * DVB;
+    __nv_bfloat16* Wh = Sh + NL * D * DVB;     __nv_bfloat16* Wl = Wh + (NL - 1) * C * D;
+    __nv_bfloat16* Qh = Wh + NL * C * D;       __nv_bfloat16* Ql = Qh + (NL - 1) * C * D;
+    __nv_bfloat16* Kh = Qh + NL * C * D;       __nv_bfloat16* Kl = Kh + (NL - 1) * C * D;
+    __nv_bfloat16* Ah = Kh + NL * C * D;       __nv_bfloat16* Al = Ah + (NL - 1) * C * C;
+    __nv_bfloat16* Vh = Ah + NL * C * C;       __nv_bfloat16* Vl = Vh + (NL - 1) * C * DVB;
+    float* Gs = reinterpret_cast<float*>(Vh + NL * C * DVB);
+
+    const uint32_t seq = blockIdx.z, h = blockIdx.y;
+    const int dv0 = blockIdx.x * DVB;
+    uint32_t row_lo, len;
+    seq_bounds(p, seq, row_lo, len);
+    const uint32_t hk = h / (p.nv / p.nk);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wr = warp & 3, wc = warp >> 2;
+    const int m0 = 16 * wr;                 // row strip of the 64-row products
+    const int nw0 = wc * (DVB / 2);         // column half of this warp in those products
+    const int ms = 16 * warp;               // dk rows of the state owned by this warp
+    const int i0 = lane >> 2, cq = 2 * (lane & 3);
+
+    // state block into registers: Sreg[nt][{0,1}] = S[ms+i0][8nt+cq+{0,1}], [{2,3}] = row ms+i0+8
+    float Sreg[NTS][4];
+    const size_t sbase = (static_cast<size_t>(seq) * p.nv + h) * D * D;   // [dv][dk]
+#pragma unroll
+    for (int nt = 0; nt < NTS; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int dk = ms + i0 + (e >> 1) * 8, dv = dv0 + nt * 8 + cq + (e & 1);
+            Sreg[nt][e] = p.state_in ? p.state_in[sbase + static_cast<size_t>(dv) * D + dk] : 0.f;
+        }
+
+    const uint32_t n_chunks = (len + C - 1) / C;
+    for (uint32_t c = 0; c < n_chunks; ++c) {
+        const uint32_t r0 = c * C;
+        const int n = static_cast<int>(min(static_cast<uint32_t>(C), len - r0));
+        const size_t row_base = static_cast<size_t>(row_lo) + r0;
+        const float* slot = slot_ptr(p, row_lo, seq, c, h);
+        const float* sW = slot;
+        const float* sU = slot + C * D;
+        const float* sQK = slot + 2 * C * D;
+        const float* sG = slot + 2 * C * D + C * C;
+
+        // state tiles for this chunk's products, and the chunk's operands
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt) {
+            put2<DVB, SPLIT>(Sh, Sl, ms + i0, nt * 8 + cq, Sreg[nt][0], Sreg[nt][1]);
+            put2<DVB, SPLIT>(Sh, Sl, ms + i0 + 8, nt * 8 + cq, Sreg[nt][2], Sreg[nt][3]);
+        }
+        if (tid < C) Gs[tid] = sG[tid];
+        const float glast = sG[C - 1];
+        for (int e = tid; e < C * (D / 4); e += 256) {
+            const int r = e >> 5, c4 = (e & 31) * 4;
+            const float gr = sG[r];
+            put4<D, SPLIT>(Wh, Wl, r, c4, *reinterpret_cast<const float4*>(sW + r * D + c4));
+            float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+            if (r < n) {
+                qv = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
+                kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+                const float eq = expf(gr), ek = expf(glast - gr);
+                qv.x *= eq; qv.y *= eq; qv.z *= eq; qv.w *= eq;
+                kv.x *= ek; kv.y *= ek; kv.z *= ek; kv.w *= ek;
+            }
+            put4<D, SPLIT>(Qh, Ql, r, c4, qv);
+            put4<D, SPLIT>(Kh, Kl, r, c4, kv);
+        }
+        for (int e = tid; e < C * (C / 4); e += 256) {
+            const int r = e >> 4, c4 = (e & 15) * 4;
+            put4<C, SPLIT>(Ah, Al, r, c4, *reinterpret_cast<const float4*>(sQK + r * C + c4));
+        }
+        __syncthreads();
+
+        // v' = U - W S   and   o = (q e^G) S   for rows m0.., columns nw0..
+        float vp[NTW][4], oi[NTW][4];
+#pragma unroll
+        for (int i = 0; i < NTW; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) vp[i][j] = oi[i][j] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t wah[4], wal[4], qah[4], qal[4];
+            lda<D>(wah, Wh, m0, 16 * ks, lane);
+            lda<D>(qah, Qh, m0, 16 * ks, lane);
+            if constexpr (SPLIT == 3) {
+                lda<D>(wal, Wl, m0, 16 * ks, lane);
+                lda<D>(qal, Ql, m0, 16 * ks, lane);
+            }
+#pragma unroll
+            for (int np = 0; np < NTW / 2; ++np) {
+                uint32_t bh[4], bl[4];
+                ldb_nn<DVB>(bh, Sh, 16 * ks, nw0 + 16 * np, lane);
+                if constexpr (SPLIT == 3) ldb_nn<DVB>(bl, Sl, 16 * ks, nw0 + 16 * np, lane);
+                mma_split<SPLIT>(vp[2 * np], vp[2 * np + 1], wah, wal, bh, bl);
+                mma_split<SPLIT>(oi[2 * np], oi[2 * np + 1], qah, qal, bh, bl);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            const int col = nw0 + nt * 8 + cq;
+            const float2 u0 = *reinterpret_cast<const float2*>(sU + (m0 + i0) * D + dv0 + col);
+            const float2 u1 = *reinterpret_cast<const float2*>(sU + (m0 + i0 + 8) * D + dv0 + col);
+            put2<DVB, SPLIT>(Vh, Vl, m0 + i0, col, u0.x - vp[nt][0], u0.y - vp[nt][1]);
+            put2<DVB, SPLIT>(Vh, Vl, m0 + i0 + 8, col, u1.x - vp[nt][2], u1.y - vp[nt][3]);
+        }
+        __syncthreads();
+
+        // o += lower(q.k e^{..}) v'
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks) {
+            uint32_t ah[4], al[4];
+            lda<C>(ah, Ah, m0, 16 * ks, lane);
+            if constexpr (SPLIT == 3) lda<C>(al, Al, m0, 16 * ks, lane);
+#pragma unroll
+            for (int np = 0; np < NTW / 2; ++np) {
+                uint32_t bh[4], bl[4];
+                ldb_nn<DVB>(bh, Vh, 16 * ks, nw0 + 16 * np, lane);
+                if constexpr (SPLIT == 3) ldb_nn<DVB>(bl, Vl, 16 * ks, nw0 + 16 * np, lane);
+                mma_split<SPLIT>(oi[2 * np], oi[2 * np + 1], ah, al, bh, bl);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            const int col = dv0 + nw0 + nt * 8 + cq;
+            if (m0 + i0 < n) *reinterpret_cast<float2*>(p.o + ((row_base + m0 + i0) * p.nv + h) * D + col) = make_float2(oi[nt][0], oi[nt][1]);
+            if (m0 + i0 + 8 < n) *reinterpret_cast<float2*>(p.o + ((row_base + m0 + i0 + 8) * p.nv + h) * D + col) = make_float2(oi[nt][2], oi[nt][3]);
+        }
+
+        // S <- e^{G_last} S + (k e^{G_last - G})^T v'   for dk rows ms..ms+15, all DVB columns
+        const float dl = expf(glast);
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) Sreg[nt][e] *= dl;
+#pragma unroll
+        for (int ks = 0; ks < C / 16; ++ks) {
+            uint32_t ah[4], al[4];
+            lda_t<D>(ah, Kh, 16 * ks, ms, lane);
+            if constexpr (SPLIT == 3) lda_t<D>(al, Kl, 16 * ks, ms, lane);
+#pragma unroll
+            for (int np = 0; np < NTS / 2; ++np) {
+                uint32_t bh[4], bl[4];
+                ldb_nn<DVB>(bh, Vh, 16 * ks, 16 * np, lane);
+                if constexpr (SPLIT == 3) ldb_nn<DVB>(bl, Vl, 16 * ks, 16 * np, lane);
+                mma_split<SPLIT>(Sreg[2 * np], Sreg[2 * np + 1], ah, al, bh, bl);
+            }
+        }
+        __syncthreads();  // every warp is done with this chunk's tiles before they are overwritten
+    }
+    if (p.write_state) {
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int dk = ms + i0 + (e >> 1) * 8, dv = dv0 + nt * 8 + cq + (e & 1);
+                p.state_out[sbase + static_cast<size_t>(dv) * D + dk] = Sreg[nt][e];
+            }
+    }
+}
+
+template <int DVB, int SPLIT>
+int launch_apply(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq) {
+    constexpr size_t smem = apply_smem<DVB, SPLIT>();
+    static bool attr_set[16] = {};
+    auto kern = delta_chunk_apply_kernel<DVB, SPLIT>;
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    kern<<<dim3(D / DVB, a.nv, n_seq), 256, smem, s>>>(a);
+    return dc_check_launch(ctx, "gated_delta (chunk apply)");
+}
+
+template <int SPLIT>
+int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq, uint32_t max_chunks) {
+    static bool attr_set[16] = {};
+    auto prep = delta_chunk_prepare_kernel<SPLIT>;
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem));
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", kPrepSmem, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    prep<<<dim3(max_chunks, a.nv, n_seq), 128, kPrepSmem, s>>>(a);
+    int rc = dc_check_launch(ctx, "gated_delta (chunk prepare)");
+    if (rc != DC_OK) return rc;
+    // few (sequence, head) pairs: split the value columns over more CTAs
+    if (static_cast<uint64_t>(n_seq) * a.nv >= static_cast<uint64_t>(ctx->sm_count)) return launch_apply<128, SPLIT>(ctx, s, a, n_seq);
+    return launch_apply<32, SPLIT>(ctx, s, a, n_seq);
+}
+
+}  // namespace
+
+size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) {
+    return (static_cast<size_t>(t) / C + n_seq + 1) * nv * kSlotFloats * sizeof(float);
+}
+
+int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const float* k, const float* v, const float* a, const float* b,
+                           const float* a_log, const float* dt_bias, const float* state_in, float* state_out, float* o, uint32_t t,
+                           uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, const uint32_t* seq_start, uint32_t n_seq,
+                           uint32_t max_len, uint32_t split) {
+    ChunkArgs args{q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, nullptr, seq_start, t, ldab, nk, nv, write_state};
+    const size_t bytes = dc_delta_chunk_scratch_bytes(t, n_seq, nv);
+    args.scratch = static_cast<float*>(dc_workspace(ctx, bytes));
+    if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);
+    const uint32_t max_chunks = (max_len + C - 1) / C;
+    if (split == 1) return launch_chunked<1>(ctx, s, args, n_seq, max_chunks);
+    return launch_chunked<3>(ctx, s, args, n_seq, max_chunks);
+}

@@ -104,7 +104,7 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
             const float* b = m->p + m->conv_dim + m->value_dim;  // fused order qkv|z|b|a (config.rs:14-17)
             const float* a = b + d.gdn_nv;
             RUN("gated_delta", dc_gated_delta(c, st, m->q, m->k, m->v, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
-                                              d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq));
+                                              d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
             RUN("gated_rmsnorm_silu", dc_gated_rmsnorm_silu(c, st, m->o, m->p + m->conv_dim, w.gnorm, m->g, rows, d.gdn_nv, d.gdn_dv, ld, d.eps));
             out_k = m->value_dim;
         } else {
@@ -235,6 +235,13 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     for (auto& wnt : wants) {
         *wnt.ptr = m->arena + off;
         off += align_up(wnt.bytes, 1024);
+    }
+    // scratch of the chunked delta rule for the largest batch, so that no forward allocates
+    if (!dc_workspace(ctx, dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv))) {
+        cudaFree(m->arena);
+        delete m;
+        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate the delta-rule scratch");
+        return nullptr;
     }
     // RoPE inverse frequencies in fp32, as the reference and HF compute them (config.rs:44-46)
     std::vector<float> f(d.rot_dim / 2);

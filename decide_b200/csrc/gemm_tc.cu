@@ -26,6 +26,9 @@ constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
+constexpr int kEpiLd = 36;                                   // padded row of the per-warp epilogue staging tile
+constexpr uint32_t kEpiBytes = 4 * 32 * kEpiLd * 4;          // 4 epilogue warps x [32][36] fp32
+
 struct GemmArgs {
     uint32_t m, n, k, ldy;
     uint32_t m_tiles, n_tiles, k_blocks, group_m;
@@ -39,7 +42,7 @@ struct Cfg {
     static constexpr uint32_t kBBytes = BN * BK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
     static constexpr uint32_t kBarBytes = 256;
-    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+    static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes + kEpiBytes;
 };
 
 // Output tiles are walked in groups of `group_m` row tiles: inside a group the row tile moves
@@ -64,55 +67,77 @@ __device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
     return true;
 }
 
+
+// One 32-row x 32-column chunk of the accumulator. tcgen05.ld hands each thread one ROW (32 columns);
+// stored like that, a warp instruction would touch 32 different 128-byte lines. The chunk goes through
+// a per-warp shared-memory tile instead and is re-read with 8 lanes per row, so every global
+// load/store instruction covers 4 whole rows segments (fully used sectors).
 template <int EPI, typename Act>
-__device__ __forceinline__ void epilogue_store(void* __restrict__ y, size_t row, uint32_t col0, uint32_t ldy,
-                                               const uint32_t (&r)[32]) {
-    if constexpr (EPI == DC_EPI_STORE_F32) {
-        float4* p = reinterpret_cast<float4*>(static_cast<float*>(y) + row * ldy + col0);
+__device__ __forceinline__ void epilogue_chunk(void* __restrict__ y, float* __restrict__ st, size_t row0, uint32_t m, uint32_t col0,
+                                               uint32_t ldy, const uint32_t (&r)[32], int lane) {
+    if constexpr (EPI == DC_EPI_STORE_BF16 || EPI == DC_EPI_SWIGLU_BF16) {
+        // 16-bit outputs: a thread's 32 columns are 64 (or, after SwiGLU, 32) contiguous bytes, stored directly
+        const size_t row = row0 + lane;
+        if (row >= m) return;
+        if constexpr (EPI == DC_EPI_STORE_BF16) {
+            uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + col0);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            p[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
-                               __uint_as_float(r[4 * j + 3]));
-    } else if constexpr (EPI == DC_EPI_ADD_F32) {
-        float4* p = reinterpret_cast<float4*>(static_cast<float*>(y) + row * ldy + col0);
-        float4 v[8];
+            for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = Act::pack(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
+                v.y = Act::pack(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                v.z = Act::pack(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                v.w = Act::pack(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                p[j] = v;
+            }
+        } else {
+            // SwiGLU over interleaved blocks of 16: columns [0,16) of this chunk are the gate, [16,32) the
+            // up projection of the same 16 output columns (cpu_ref.rs:39-50)
+            uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + (col0 >> 1));
+            float o[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = p[j];
+            for (int j = 0; j < 16; ++j) o[j] = silu_f(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[j].x += __uint_as_float(r[4 * j]);
-            v[j].y += __uint_as_float(r[4 * j + 1]);
-            v[j].z += __uint_as_float(r[4 * j + 2]);
-            v[j].w += __uint_as_float(r[4 * j + 3]);
-            p[j] = v[j];
-        }
-    } else if constexpr (EPI == DC_EPI_STORE_BF16) {
-        uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + col0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = Act::pack(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1]));
-            v.y = Act::pack(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            v.z = Act::pack(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            v.w = Act::pack(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            p[j] = v;
+            for (int j = 0; j < 2; ++j) {
+                uint4 v;
+                v.x = Act::pack(o[8 * j], o[8 * j + 1]);
+                v.y = Act::pack(o[8 * j + 2], o[8 * j + 3]);
+                v.z = Act::pack(o[8 * j + 4], o[8 * j + 5]);
+                v.w = Act::pack(o[8 * j + 6], o[8 * j + 7]);
+                p[j] = v;
+            }
         }
     } else {
-        // SwiGLU over interleaved blocks of 16: columns [0,16) of this 32-column chunk are the gate,
-        // [16,32) the up projection of the same 16 output columns (cpu_ref.rs:39-50).
-        uint4* p = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + row * ldy + (col0 >> 1));
-        float o[16];
+        // fp32 outputs: tcgen05.ld hands each thread one ROW (32 columns = 128 bytes); stored like that, a
+        // warp instruction would touch 32 different lines. The chunk goes through a per-warp
+        // shared-memory tile and is re-read with 8 lanes per row, so each global instruction covers 4
+        // whole 128-byte row segments.
+        float4* mine = reinterpret_cast<float4*>(st + lane * kEpiLd);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j] = silu_f(__uint_as_float(r[j])) * __uint_as_float(r[16 + j]);
+        for (int j = 0; j < 8; ++j)
+            mine[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        __syncwarp();
+        const int sub = lane >> 3, l8 = lane & 7;
+        float* yf = static_cast<float*>(y) + col0 + 4 * l8;
+        float4 old[8];
+        if constexpr (EPI == DC_EPI_ADD_F32) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            uint4 v;
-            v.x = Act::pack(o[8 * j], o[8 * j + 1]);
-            v.y = Act::pack(o[8 * j + 2], o[8 * j + 3]);
-            v.z = Act::pack(o[8 * j + 4], o[8 * j + 5]);
-            v.w = Act::pack(o[8 * j + 6], o[8 * j + 7]);
-            p[j] = v;
+            for (int it = 0; it < 8; ++it) {   // all eight reads of the residual in flight before the first add
+                const size_t row = row0 + it * 4 + sub;
+                old[it] = row < m ? *reinterpret_cast<const float4*>(yf + row * ldy) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + sub;
+            const size_t row = row0 + rr;
+            float4 v = *reinterpret_cast<const float4*>(st + rr * kEpiLd + 4 * l8);
+            if constexpr (EPI == DC_EPI_ADD_F32) {
+                v.x += old[it].x; v.y += old[it].y; v.z += old[it].z; v.w += old[it].w;
+            }
+            if (row < m) *reinterpret_cast<float4*>(yf + row * ldy) = v;
+        }
+        __syncwarp();
     }
 }
 
@@ -134,6 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     uint64_t* acc_empty = bars + 2 * S + 2;  // [2] epilogue -> MMA: accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* epi_stage = reinterpret_cast<float*>(smem + S * C::kStageBytes + C::kBarBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -248,7 +274,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after_sync();
-            const size_t row = static_cast<size_t>(tm) * BM + q * 32u + lane;
+            const size_t row0 = static_cast<size_t>(tm) * BM + q * 32u;
+            float* st = epi_stage + (warp - 2) * 32 * kEpiLd;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN / 32; ++c) {
@@ -257,7 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c * 32u, r);
                 tmem_ld_wait();
-                if (row < a.m) epilogue_store<EPI, Act>(y, row, col0, a.ldy, r);
+                epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
             }
             tc_fence_before_sync();
             __syncwarp();

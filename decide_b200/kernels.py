@@ -126,6 +126,10 @@ class Device:
     def set_activation_dtype(self, act: Act):
         self.call("dc_set_activation_dtype", int(act))
 
+    def set_delta_split(self, split: int):
+        """Operand precision of the chunked delta rule: 3 = hi/lo split (default), 1 = single bf16 pass."""
+        self.call("dc_set_delta_split", split)
+
     @property
     def act(self) -> Act:
         return Act(self.lib.dc_get_activation_dtype(self.handle))
@@ -249,10 +253,10 @@ class Delta(_Family):
         return self.dev.get_impl(Family.Delta)
 
     def gated_delta(self, stream, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, write_state: bool,
-                    nk: int, nv: int, dk: int = 128, dv: int = 128, seq_start=None, n_seq: int = 1):
+                    nk: int, nv: int, dk: int = 128, dv: int = 128, seq_start=None, n_seq: int = 1, max_len: int = 0):
         """The gated delta rule (kernels/delta.rs:53-100)."""
         self.dev.call("dc_gated_delta", _stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias),
-                      _ptr(state_in), _ptr(state_out), _ptr(o), t, ldab, int(write_state), nk, nv, dk, dv, _ptr(seq_start), n_seq)
+                      _ptr(state_in), _ptr(state_out), _ptr(o), t, ldab, int(write_state), nk, nv, dk, dv, _ptr(seq_start), n_seq, max_len)
 
 
 class Kernels:

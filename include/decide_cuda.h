@@ -75,6 +75,10 @@ uint32_t dc_get_impl(dc_ctx* ctx, uint32_t family);
 /* The context's 16-bit type (DC_ACT_*); at open it is read from DECIDE_ACT = f16 | bf16 (default f16). */
 int dc_set_activation_dtype(dc_ctx* ctx, uint32_t act);
 uint32_t dc_get_activation_dtype(dc_ctx* ctx);
+/* Operand precision of the chunked gated delta rule's tensor-core products: 3 (default; also
+ * DECIDE_DELTA_SPLIT=3) takes every fp32 operand as hi + lo bf16 parts, 3 MMAs per product, ~1e-5
+ * relative error against fp32; 1 is a single bf16 pass, 3x fewer MMAs, ~3e-3 relative error in o. */
+int dc_set_delta_split(dc_ctx* ctx, uint32_t split);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
  * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
 int dc_check_status(dc_ctx* ctx, void* stream);
@@ -212,11 +216,15 @@ int dc_conv_state_update(dc_ctx* ctx, void* stream, const float* p, const float*
  * The gated delta rule over t rows, fp32: q,k [t,nk,dk], v and o [t,nv,dv]; a,b read from rows of stride
  * ldab (value head h at column h); a_log, dt_bias fp32 [nv]; state fp32 [nv][dv][dk]; state_in may be
  * state_out (NULL state_in = zero state); state_out is written only with write_state. dk = dv = 128.
- * Packed sequences: seq_start u32 [n_seq+1] and states [n_seq][nv][dv][dk]. */
+ * Packed sequences: seq_start u32 [n_seq+1], states [n_seq][nv][dv][dk], max_len the longest sequence
+ * (0 = unknown). The fast kernels are the chunk-64 form on tensor cores (scratch from the context's
+ * workspace: reserve dc_gated_delta_scratch_bytes up front to keep a forward allocation-free); the
+ * baseline is the reference's sequential recurrence. */
 int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, const float* v, const float* a,
                    const float* b, const float* a_log, const float* dt_bias, const float* state_in, float* state_out,
                    float* o, uint32_t t, uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk,
-                   uint32_t dv, const uint32_t* seq_start, uint32_t n_seq);
+                   uint32_t dv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
+size_t dc_gated_delta_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv);
 
 /* ======================================================================================
  * Whole-model prefill: the host loop of Forward (crates/decide-engine/src/forward.rs:1129-1328)

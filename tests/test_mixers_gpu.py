@@ -189,6 +189,19 @@ def test_conv_state_update(k, t):
 
 
 # ----------------------------------------------------------------- delta
+@pytest.fixture(params=["chunked", "sequential"])
+def delta_impl(request, k):
+    """Runs a delta-rule test on the chunk-64 tensor-core kernels (fast) and on the sequential kernel (baseline)."""
+    from decide_b200.kernels import Family, Impl
+
+    k.dev.set_impl(Family.Delta, Impl.Fast if request.param == "chunked" else Impl.Baseline)
+    yield request.param
+    k.dev.set_impl(Family.Delta, Impl.Fast)
+
+
+# fp32 sequential kernel vs the f64-accumulating oracle: ~1e-6; chunked kernel with hi/lo split operands: ~1e-5
+DELTA_TOL = dict(atol=6e-5, rtol=3e-4)
+
 def _delta_inputs(seed, t, nk, nv):
     q = randn(seed, t, nk, 128)
     kk = randn(seed + 1, t, nk, 128)
@@ -210,19 +223,19 @@ def _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, state, t, nk, nv, write=
     return o
 
 
-@pytest.mark.parametrize("t,nk,nv", [(1, 16, 16), (17, 16, 16), (130, 16, 16), (40, 16, 32)])
-def test_gated_delta_vs_sequential_reference(k, t, nk, nv):
+@pytest.mark.parametrize("t,nk,nv", [(1, 16, 16), (17, 16, 16), (64, 16, 16), (130, 16, 16), (40, 16, 32), (603, 16, 16)])
+def test_gated_delta_vs_sequential_reference(k, t, nk, nv, delta_impl):
     q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(70 + t, t, nk, nv)
     s0 = randn(80, nv, 128, 128, std=0.1)
     state = s0.clone().cuda()
     o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, state, t, nk, nv)
     ref_state = np32(s0).copy()
     want = cpu_ref.gated_delta(np32(q), np32(kk), np32(v), np32(a), np32(b), ldab, np32(a_log), np32(dt_bias), ref_state, t, nk, nv, 128, 128)
-    assert_close(np32(o), want, atol=2e-5, rtol=2e-4, what="delta o")
-    assert_close(np32(state), ref_state, atol=2e-5, rtol=2e-4, what="delta state")
+    assert_close(np32(o), want, what="delta o", **DELTA_TOL)
+    assert_close(np32(state), ref_state, what="delta state", **DELTA_TOL)
 
 
-def test_gated_delta_by_hand(k):
+def test_gated_delta_by_hand(k, delta_impl):
     """The reference's known answer (cpu_ref.rs:222-236): one step, beta = 1, g = 1 -> o = v, S = k delta^T."""
     nk = nv = 16
     kk = torch.zeros(1, nk, 128)
@@ -238,22 +251,23 @@ def test_gated_delta_by_hand(k):
     assert o.abs().sum().item() == pytest.approx(3.0, abs=1e-4)
 
 
-def test_gated_delta_chunk_continuation_is_exact(k):
+def test_gated_delta_chunk_continuation_is_exact(k, delta_impl):
     """Whole sequence vs the same rows in two calls carrying the state (the engine's chunk continuation,
-    forward.rs:1214-1234): fp32 through memory, so bit-identical."""
-    t, nk, nv = 90, 16, 16
+    forward.rs:1214-1234): fp32 through memory, so bit-identical. The chunked kernel regroups tokens by
+    64, so for it the cut must fall on a chunk boundary to be bit-identical."""
+    t, nk, nv = 150, 16, 16
     q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(90, t, nk, nv)
     s_whole = torch.zeros(nv, 128, 128, device="cuda")
     o_whole = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, s_whole, t, nk, nv)
     s_split = torch.zeros(nv, 128, 128, device="cuda")
-    cut = 33
+    cut = 64 if delta_impl == "chunked" else 33
     o1 = _delta_gpu(k, q[:cut], kk[:cut], v[:cut], a[:cut], b[:cut], ldab, a_log, dt_bias, s_split, cut, nk, nv)
     o2 = _delta_gpu(k, q[cut:], kk[cut:], v[cut:], a[cut:], b[cut:], ldab, a_log, dt_bias, s_split, t - cut, nk, nv)
     assert torch.equal(torch.cat([o1, o2]), o_whole)
     assert torch.equal(s_split, s_whole)
 
 
-def test_gated_delta_write_state_false_leaves_state(k):
+def test_gated_delta_write_state_false_leaves_state(k, delta_impl):
     t, nk, nv = 10, 16, 16
     q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(95, t, nk, nv)
     state = torch.full((nv, 128, 128), 0.25, device="cuda")
@@ -261,9 +275,9 @@ def test_gated_delta_write_state_false_leaves_state(k):
     assert (state == 0.25).all()
 
 
-def test_gated_delta_packed_sequences(k):
+def test_gated_delta_packed_sequences(k, delta_impl):
     nk = nv = 16
-    lens = [20, 1, 45]
+    lens = [20, 1, 145, 64]
     starts = np.concatenate([[0], np.cumsum(lens)])
     total = int(starts[-1])
     q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(97, total, nk, nv)
@@ -274,26 +288,48 @@ def test_gated_delta_packed_sequences(k):
         st = np.zeros((nv, 128, 128), np.float32)
         want = cpu_ref.gated_delta(np32(q)[lo:hi], np32(kk)[lo:hi], np32(v)[lo:hi], np32(a)[lo:hi], np32(b)[lo:hi], ldab,
                                    np32(a_log), np32(dt_bias), st, n, nk, nv, 128, 128)
-        assert_close(np32(o)[lo:hi], want, atol=2e-5, rtol=2e-4, what=f"packed delta seq {s}")
-        assert_close(np32(states[s]), st, atol=2e-5, rtol=2e-4, what=f"packed delta state {s}")
+        assert_close(np32(o)[lo:hi], want, what=f"packed delta seq {s}", **DELTA_TOL)
+        assert_close(np32(states[s]), st, what=f"packed delta state {s}", **DELTA_TOL)
 
 
 @pytest.mark.parametrize("n_seq", [10, 40])
-def test_gated_delta_many_sequences_use_wider_lanes(k, n_seq):
-    """With many sequences the kernel gives each value column fewer lanes (4, then 1) than for a single
-    sequence (8); every variant must match the sequential reference."""
+def test_gated_delta_many_sequences_use_wider_lanes(k, n_seq, delta_impl):
+    """With many sequences the sequential kernel gives each value column fewer lanes (4, then 1) than for a
+    single sequence (8), and the chunked kernel keeps all 128 value columns in one CTA instead of 32;
+    every variant must match the sequential reference."""
     nk = nv = 16
     rs = np.random.RandomState(n_seq)
     lens = rs.randint(1, 24, n_seq).tolist()
+    if n_seq == 10:
+        lens += [30] * 150  # 160 sequences x 16 heads: above the SM count, the one-CTA-per-head variant
     starts = np.concatenate([[0], np.cumsum(lens)])
     total = int(starts[-1])
     q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(120 + n_seq, total, nk, nv)
+    n_seq = len(lens)
     states = torch.zeros(n_seq, nv, 128, 128, device="cuda")
-    o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, states, total, nk, nv, seq_start=_u32(starts), n_seq=n_seq)
+    o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, states, total, nk, nv, seq_start=_u32(starts), n_seq=n_seq, max_len=max(lens))
     for s in (0, n_seq // 2, n_seq - 1):
         lo, hi = int(starts[s]), int(starts[s + 1])
         st = np.zeros((nv, 128, 128), np.float32)
         want = cpu_ref.gated_delta(np32(q)[lo:hi], np32(kk)[lo:hi], np32(v)[lo:hi], np32(a)[lo:hi], np32(b)[lo:hi], ldab,
                                    np32(a_log), np32(dt_bias), st, hi - lo, nk, nv, 128, 128)
-        assert_close(np32(o)[lo:hi], want, atol=2e-5, rtol=2e-4, what=f"delta seq {s} of {n_seq}")
-        assert_close(np32(states[s]), st, atol=2e-5, rtol=2e-4, what=f"delta state {s} of {n_seq}")
+        assert_close(np32(o)[lo:hi], want, what=f"delta seq {s} of {n_seq}", **DELTA_TOL)
+        assert_close(np32(states[s]), st, what=f"delta state {s} of {n_seq}", **DELTA_TOL)
+
+
+def test_gated_delta_single_pass_precision(k):
+    """The chunked kernel with unsplit bf16 operands (dc_set_delta_split 1) is a looser, faster mode:
+    it must still track the reference to bf16 accuracy, and the default split-3 mode must be much closer."""
+    t, nk, nv = 200, 16, 16
+    q, kk, v, a, b, ldab, a_log, dt_bias = _delta_inputs(300, t, nk, nv)
+    st = np.zeros((nv, 128, 128), np.float32)
+    want = cpu_ref.gated_delta(np32(q), np32(kk), np32(v), np32(a), np32(b), ldab, np32(a_log), np32(dt_bias), st, t, nk, nv, 128, 128)
+    errs = {}
+    for split in (3, 1):
+        k.dev.set_delta_split(split)
+        try:
+            o = _delta_gpu(k, q, kk, v, a, b, ldab, a_log, dt_bias, torch.zeros(nv, 128, 128, device="cuda"), t, nk, nv)
+        finally:
+            k.dev.set_delta_split(3)
+        errs[split] = float(np.linalg.norm(np32(o) - want) / np.linalg.norm(want))
+    assert errs[3] < 5e-5 and errs[1] < 2e-2 and errs[3] < errs[1] / 20, errs
