@@ -23,14 +23,33 @@ using namespace dc;
 constexpr int C = 64;            // chunk length
 constexpr int D = 128;           // dk = dv
 constexpr int LD = 65;           // padded row stride of the fp32 64x64 work matrices
-constexpr int kSlotFloats = 2 * C * D + C * C + C;  // W, U, QK, G per (chunk, head)
+
+// Scratch of one (chunk, head), written by kernel 1 in exactly the shared-memory form kernel 2 wants
+// (bf16 hi [+ lo] tiles, already swizzled), so kernel 2 fills its operands with flat cp.async copies:
+//   W  [64][128]   T (beta k e^G)                       A operand of W S
+//   Qg [64][128]   q e^G                                A operand of (q e^G) S
+//   Kd [64][128]   k e^{G_last - G}                     A^T operand of the state update
+//   A  [64][64]    lower((q_i . k_j) e^{G_i - G_j})     A operand of A v'
+//   U  [64][128]   fp32, T (beta v)
+//   e^{G_last}
+template <int SPLIT>
+struct Slot {
+    static constexpr int NL = SPLIT == 3 ? 2 : 1;            // tiles per operand: hi (+ lo)
+    static constexpr size_t kW = 0;                           // byte offsets
+    static constexpr size_t kQg = kW + NL * C * D * 2;
+    static constexpr size_t kKd = kQg + NL * C * D * 2;
+    static constexpr size_t kA = kKd + NL * C * D * 2;
+    static constexpr size_t kU = kA + NL * C * C * 2;
+    static constexpr size_t kDecay = kU + C * D * 4;
+    static constexpr size_t kBytes = kDecay + 16;
+};
 
 struct ChunkArgs {
     const float *q, *k, *v, *a, *b, *a_log, *dt_bias;
     const float* state_in;
     float* state_out;
     float* o;
-    float* scratch;
+    uint8_t* scratch;
     const uint32_t* seq_start;
     uint32_t t, ldab, nk, nv, write_state;
 };
@@ -40,17 +59,19 @@ __device__ __forceinline__ void seq_bounds(const ChunkArgs& p, uint32_t seq, uin
     len = p.seq_start ? p.seq_start[seq + 1] - row_lo : p.t;
 }
 // Scratch slot of chunk c of a sequence: row_lo / 64 + seq + c never collides between sequences.
-__device__ __forceinline__ float* slot_ptr(const ChunkArgs& p, uint32_t row_lo, uint32_t seq, uint32_t c, uint32_t h) {
+template <int SPLIT>
+__device__ __forceinline__ uint8_t* slot_ptr(const ChunkArgs& p, uint32_t row_lo, uint32_t seq, uint32_t c, uint32_t h) {
     const size_t slot = static_cast<size_t>(row_lo / C + seq + c);
-    return p.scratch + (slot * p.nv + h) * kSlotFloats;
+    return p.scratch + (slot * p.nv + h) * Slot<SPLIT>::kBytes;
 }
 
 // ---------------------------------------------------------------------------------------------
 // Inverse of I + L for a strictly lower triangular 64x64 L (fp32, row stride LD) into N, by 16x16
 // blocks: the four diagonal blocks by in-warp forward substitution, then the off-diagonal blocks
-// one block-diagonal at a time, N_ij = -N_ii * sum_{k=j}^{i-1} L_ik N_kj. Four warps.
+// one block-diagonal at a time, N_ij = -N_ii * sum_{k=j}^{i-1} L_ik N_kj. Warps 0..3 work; every warp
+// of the CTA must call it (it synchronises the CTA).
 __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict__ N, float* __restrict__ P, int warp, int lane) {
-    {   // diagonal block `warp`: lane l < 16 holds column l; row i of the result needs rows < i
+    if (warp < 4) {   // diagonal block `warp`: lane l < 16 holds column l; row i of the result needs rows < i
         const int b0 = 16 * warp;
         const int l = lane & 15;
         float a[16];
@@ -83,7 +104,7 @@ __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict
     for (int d = 1; d < 4; ++d) {
         __syncthreads();
         const int i = d + warp, j = warp;  // block (i, j) with i - j = d
-        if (i < 4) {
+        if (warp < 4 && i < 4) {
             float acc[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[c] = 0.f;
@@ -114,13 +135,23 @@ __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict
     __syncthreads();
 }
 
+
+// (x0, x1) at (row, col) of a swizzled bf16 tile pair [rows][CW] in GLOBAL memory: hi at `base`, lo right after it.
+template <int CW, int ROWS, int SPLIT>
+__device__ __forceinline__ void gput2(uint8_t* base, int row, int col, float x0, float x1) {
+    __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(base);
+    put2<CW, SPLIT>(hi, hi + ROWS * CW, row, col, x0, x1);
+}
+
 // ---------------------------------------------------------------------------------------------
-// Kernel 1: one CTA (4 warps) per (chunk, head, sequence). Shared memory: K and Q tiles (hi, lo),
-// reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased onto L.
+// Kernel 1: one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
+// tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
+// onto L.
 constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 2 * C * 4;
 
 template <int SPLIT>
-__global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArgs p) {
+__global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const ChunkArgs p) {
+    using SL = Slot<SPLIT>;
     extern __shared__ __align__(16) uint8_t smem[];
     __nv_bfloat16* kh = reinterpret_cast<__nv_bfloat16*>(smem);
     __nv_bfloat16* kl = kh + C * D;
@@ -142,12 +173,9 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
     const int n = static_cast<int>(min(static_cast<uint32_t>(C), len - r0));
     const uint32_t hk = h / (p.nv / p.nk);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wr = warp & 3, wc = warp >> 2;
     const size_t row_base = static_cast<size_t>(row_lo) + r0;
-    float* slot = slot_ptr(p, row_lo, seq, c, h);
-    float* sW = slot;
-    float* sU = slot + C * D;
-    float* sQK = slot + 2 * C * D;
-    float* sG = slot + 2 * C * D + C * C;
+    uint8_t* slot = slot_ptr<SPLIT>(p, row_lo, seq, c, h);
 
     // gates; rows past the sequence end are padding: no decay, no write (g = 0, beta = 0, k = v = q = 0)
     if (tid < C) {
@@ -157,33 +185,49 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
             g = -expf(p.a_log[h]) * softplus_precise(p.a[row * p.ldab + h] + p.dt_bias[h]);
             be = 1.0f / (1.0f + expf(-p.b[row * p.ldab + h]));
         }
-        Lf[tid] = g;  // staging for the prefix sum
+        Nf[tid] = g;  // staging for the prefix sum
         Bs[tid] = be;
-    }
-    for (int e = tid; e < C * (D / 4); e += 128) {
-        const int r = e >> 5, c4 = (e & 31) * 4;
-        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), qv = kv;
-        if (r < n) {
-            kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
-            qv = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
-        }
-        put4<D, SPLIT>(kh, kl, r, c4, kv);
-        put4<D, SPLIT>(qh, ql, r, c4, qv);
     }
     __syncthreads();
     if (tid < C) {
         float acc = 0.f;
-        for (int i = 0; i <= tid; ++i) acc += Lf[i];
+        for (int i = 0; i <= tid; ++i) acc += Nf[i];
         Gs[tid] = acc;
-        sG[tid] = acc;
+    }
+    __syncthreads();
+    const float glast = Gs[C - 1];
+    if (tid == 0) *reinterpret_cast<float*>(slot + SL::kDecay) = expf(glast);
+
+    {   // K and Q tiles into shared memory; q e^G and k e^{G_last - G} tiles straight to scratch
+        float4 kv[8], qv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
+            kv[i] = qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < n) {
+                kv[i] = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+                qv[i] = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
+            put4<D, SPLIT>(kh, kl, r, c4, kv[i]);
+            put4<D, SPLIT>(qh, ql, r, c4, qv[i]);
+            const float eq = expf(Gs[r]), ek = expf(glast - Gs[r]);
+            gput2<D, C, SPLIT>(slot + SL::kQg, r, c4, qv[i].x * eq, qv[i].y * eq);
+            gput2<D, C, SPLIT>(slot + SL::kQg, r, c4 + 2, qv[i].z * eq, qv[i].w * eq);
+            gput2<D, C, SPLIT>(slot + SL::kKd, r, c4, kv[i].x * ek, kv[i].y * ek);
+            gput2<D, C, SPLIT>(slot + SL::kKd, r, c4 + 2, kv[i].z * ek, kv[i].w * ek);
+        }
     }
     __syncthreads();
 
-    const int m0 = 16 * warp;
-    {   // k.k^T and q.k^T, 16 rows per warp
-        float akk[8][4], aqk[8][4];
+    const int m0 = 16 * wr;
+    {   // k.k^T and q.k^T: 16 rows x 32 columns per warp
+        float akk[4][4], aqk[4][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) akk[i][j] = aqk[i][j] = 0.f;
 #pragma unroll
@@ -196,22 +240,22 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
                 lda<D>(qal, ql, m0, 16 * ks, lane);
             }
 #pragma unroll
-            for (int np = 0; np < C / 16; ++np) {
+            for (int np = 0; np < 2; ++np) {
                 uint32_t bh[4], bl[4];
-                ldb_nt<D>(bh, kh, 16 * np, 16 * ks, lane);
-                if constexpr (SPLIT == 3) ldb_nt<D>(bl, kl, 16 * np, 16 * ks, lane);
+                ldb_nt<D>(bh, kh, 32 * wc + 16 * np, 16 * ks, lane);
+                if constexpr (SPLIT == 3) ldb_nt<D>(bl, kl, 32 * wc + 16 * np, 16 * ks, lane);
                 mma_split<SPLIT>(akk[2 * np], akk[2 * np + 1], kah, kal, bh, bl);
                 mma_split<SPLIT>(aqk[2 * np], aqk[2 * np + 1], qah, qal, bh, bl);
             }
         }
-        __syncthreads();  // Lf was the gate staging area until every thread had its prefix sum
         const int i0 = m0 + (lane >> 2), i1 = i0 + 8;
         const float g0 = Gs[i0], g1 = Gs[i1], b0 = Bs[i0], b1 = Bs[i1];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 4; ++nt) {
+            const int jb = 32 * wc + nt * 8 + 2 * (lane & 3);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int j = nt * 8 + 2 * (lane & 3) + e;
+                const int j = jb + e;
                 const float gj = Gs[j];
                 const float d0 = j <= i0 ? expf(g0 - gj) : 0.f;
                 const float d1 = j <= i1 ? expf(g1 - gj) : 0.f;
@@ -220,43 +264,50 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
                 aqk[nt][e] *= d0;
                 aqk[nt][2 + e] *= d1;
             }
-            const int j = nt * 8 + 2 * (lane & 3);
-            *reinterpret_cast<float2*>(sQK + i0 * C + j) = make_float2(aqk[nt][0], aqk[nt][1]);
-            *reinterpret_cast<float2*>(sQK + i1 * C + j) = make_float2(aqk[nt][2], aqk[nt][3]);
+            gput2<C, C, SPLIT>(slot + SL::kA, i0, jb, aqk[nt][0], aqk[nt][1]);
+            gput2<C, C, SPLIT>(slot + SL::kA, i1, jb, aqk[nt][2], aqk[nt][3]);
         }
     }
     __syncthreads();
     invert_unit_lower(Lf, Nf, Pf, warp, lane);
 
     // T tiles; beta*k*e^G into the Q tiles, beta*v into the K tiles (both [token][feature])
-    for (int e = tid; e < C * (C / 2); e += 128) {
-        const int r = e >> 5, c2 = (e & 31) * 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = tid + 256 * i, r = e >> 5, c2 = (e & 31) * 2;
         put2<C, SPLIT>(th, tl, r, c2, Nf[r * LD + c2], Nf[r * LD + c2 + 1]);
     }
-    for (int e = tid; e < C * (D / 4); e += 128) {
-        const int r = e >> 5, c4 = (e & 31) * 4;
-        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-        if (r < n) {
-            kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
-            vv = *reinterpret_cast<const float4*>(p.v + ((row_base + r) * p.nv + h) * D + c4);
-            const float be = Bs[r], sk = be * expf(Gs[r]);
-            kv.x *= sk; kv.y *= sk; kv.z *= sk; kv.w *= sk;
-            vv.x *= be; vv.y *= be; vv.z *= be; vv.w *= be;
+    {
+        float4 kv[8], vv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
+            kv[i] = vv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < n) {
+                kv[i] = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+                vv[i] = *reinterpret_cast<const float4*>(p.v + ((row_base + r) * p.nv + h) * D + c4);
+            }
         }
-        put4<D, SPLIT>(qh, ql, r, c4, kv);
-        put4<D, SPLIT>(kh, kl, r, c4, vv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
+            const float be = Bs[r], sk = be * expf(Gs[r]);
+            kv[i].x *= sk; kv[i].y *= sk; kv[i].z *= sk; kv[i].w *= sk;
+            vv[i].x *= be; vv[i].y *= be; vv[i].z *= be; vv[i].w *= be;
+            put4<D, SPLIT>(qh, ql, r, c4, kv[i]);
+            put4<D, SPLIT>(kh, kl, r, c4, vv[i]);
+        }
     }
     __syncthreads();
 
-    // W = T (beta k e^G), U = T (beta v)
+    // W = T (beta k e^G), U = T (beta v): 16 rows x 64 columns per warp
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
         const __nv_bfloat16* bh_t = which == 0 ? qh : kh;
         const __nv_bfloat16* bl_t = which == 0 ? ql : kl;
-        float* dst = which == 0 ? sW : sU;
-        float acc[16][4];
+        float acc[8][4];
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 #pragma unroll
@@ -265,19 +316,25 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
             lda<C>(ah, th, m0, 16 * ks, lane);
             if constexpr (SPLIT == 3) lda<C>(al, tl, m0, 16 * ks, lane);
 #pragma unroll
-            for (int np = 0; np < D / 16; ++np) {
+            for (int np = 0; np < 4; ++np) {
                 uint32_t bh[4], bl[4];
-                ldb_nn<D>(bh, bh_t, 16 * ks, 16 * np, lane);
-                if constexpr (SPLIT == 3) ldb_nn<D>(bl, bl_t, 16 * ks, 16 * np, lane);
+                ldb_nn<D>(bh, bh_t, 16 * ks, 64 * wc + 16 * np, lane);
+                if constexpr (SPLIT == 3) ldb_nn<D>(bl, bl_t, 16 * ks, 64 * wc + 16 * np, lane);
                 mma_split<SPLIT>(acc[2 * np], acc[2 * np + 1], ah, al, bh, bl);
             }
         }
         const int i0 = m0 + (lane >> 2), i1 = i0 + 8;
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-            const int j = nt * 8 + 2 * (lane & 3);
-            *reinterpret_cast<float2*>(dst + i0 * D + j) = make_float2(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<float2*>(dst + i1 * D + j) = make_float2(acc[nt][2], acc[nt][3]);
+        for (int nt = 0; nt < 8; ++nt) {
+            const int j = 64 * wc + nt * 8 + 2 * (lane & 3);
+            if (which == 0) {
+                gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
+                gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
+            } else {
+                float* sU = reinterpret_cast<float*>(slot + SL::kU);
+                *reinterpret_cast<float2*>(sU + i0 * D + j) = make_float2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<float2*>(sU + i1 * D + j) = make_float2(acc[nt][2], acc[nt][3]);
+            }
         }
     }
 }
@@ -285,32 +342,45 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(const ChunkArg
 // ---------------------------------------------------------------------------------------------
 // Kernel 2: one CTA (8 warps) per (value-column block of DVB, head, sequence) walks the chunks in
 // order. The state block S[dk][DVB] lives in registers (warp w owns dk rows 16w..16w+15) and, split
-// into bf16 tiles, in shared memory as the B operand of W S and (q e^G) S.
-template <int DVB, int SPLIT>
-constexpr size_t apply_smem() {
-    return static_cast<size_t>(SPLIT == 3 ? 2 : 1) * 2 * (D * DVB + 3 * C * D + C * C + C * DVB) + C * 4;
+// into bf16 tiles, in shared memory as the B operand of W S and (q e^G) S. The chunk operands arrive
+// by cp.async in two groups that overlap with the MMAs: {W, Qg} of chunk c+1 stream in while chunk c
+// does its second half, {Kd, A} of chunk c while it does its first half.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void copy_async(uint8_t* dst, const uint8_t* src, int bytes, int tid) {
+    for (int o = tid * 16; o < bytes; o += 256 * 16) cp_async16(dst + o, src + o);
 }
 
 template <int DVB, int SPLIT>
-__global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs p) {
-    constexpr int NL = SPLIT == 3 ? 2 : 1;            // tiles per operand: hi (+ lo)
+constexpr size_t apply_smem() {
+    return Slot<SPLIT>::kU + static_cast<size_t>(Slot<SPLIT>::NL) * 2 * (D * DVB + C * DVB);
+}
+
+template <int DVB, int SPLIT>
+__global__ void __launch_bounds__(256, 1) delta_chunk_apply_kernel(const ChunkArgs p) {
+    using SL = Slot<SPLIT>;
+    constexpr int NL = SL::NL;
     constexpr int NTW = DVB / 16;                     // n-tiles per warp for the 64-row products
     constexpr int NTS = DVB / 8;                      // n-tiles of the state block
     extern __shared__ __align__(16) uint8_t smem[];
-    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(smem);
-    __nv_bfloat16* Sh = base;                  __nv_bfloat16* Sl = Sh + (NL - 1) * D * DVB;
-    __nv_bfloat16* Wh = Sh + NL * D * DVB;     __nv_bfloat16* Wl = Wh + (NL - 1) * C * D;
-    __nv_bfloat16* Qh = Wh + NL * C * D;       __nv_bfloat16* Ql = Qh + (NL - 1) * C * D;
-    __nv_bfloat16* Kh = Qh + NL * C * D;       __nv_bfloat16* Kl = Kh + (NL - 1) * C * D;
-    __nv_bfloat16* Ah = Kh + NL * C * D;       __nv_bfloat16* Al = Ah + (NL - 1) * C * C;
-    __nv_bfloat16* Vh = Ah + NL * C * C;       __nv_bfloat16* Vl = Vh + (NL - 1) * C * DVB;
-    float* Gs = reinterpret_cast<float*>(Vh + NL * C * DVB);
+    // the first kU bytes mirror a scratch slot: W, Qg | Kd, A
+    __nv_bfloat16* Wh = reinterpret_cast<__nv_bfloat16*>(smem + SL::kW);   __nv_bfloat16* Wl = Wh + (NL - 1) * C * D;
+    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(smem + SL::kQg);  __nv_bfloat16* Ql = Qh + (NL - 1) * C * D;
+    __nv_bfloat16* Kh = reinterpret_cast<__nv_bfloat16*>(smem + SL::kKd);  __nv_bfloat16* Kl = Kh + (NL - 1) * C * D;
+    __nv_bfloat16* Ah = reinterpret_cast<__nv_bfloat16*>(smem + SL::kA);   __nv_bfloat16* Al = Ah + (NL - 1) * C * C;
+    __nv_bfloat16* Sh = reinterpret_cast<__nv_bfloat16*>(smem + SL::kU);   __nv_bfloat16* Sl = Sh + (NL - 1) * D * DVB;
+    __nv_bfloat16* Vh = Sh + NL * D * DVB;                                 __nv_bfloat16* Vl = Vh + (NL - 1) * C * DVB;
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y;
     const int dv0 = blockIdx.x * DVB;
     uint32_t row_lo, len;
     seq_bounds(p, seq, row_lo, len);
-    const uint32_t hk = h / (p.nv / p.nk);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wr = warp & 3, wc = warp >> 2;
     const int m0 = 16 * wr;                 // row strip of the 64-row products
@@ -330,43 +400,32 @@ __global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs 
         }
 
     const uint32_t n_chunks = (len + C - 1) / C;
+    if (n_chunks) copy_async(smem + SL::kW, slot_ptr<SPLIT>(p, row_lo, seq, 0, h) + SL::kW, static_cast<int>(SL::kKd - SL::kW), tid);
+    cp_async_commit();
     for (uint32_t c = 0; c < n_chunks; ++c) {
         const uint32_t r0 = c * C;
         const int n = static_cast<int>(min(static_cast<uint32_t>(C), len - r0));
         const size_t row_base = static_cast<size_t>(row_lo) + r0;
-        const float* slot = slot_ptr(p, row_lo, seq, c, h);
-        const float* sW = slot;
-        const float* sU = slot + C * D;
-        const float* sQK = slot + 2 * C * D;
-        const float* sG = slot + 2 * C * D + C * C;
+        const uint8_t* slot = slot_ptr<SPLIT>(p, row_lo, seq, c, h);
+        const float* sU = reinterpret_cast<const float*>(slot + SL::kU);
 
-        // state tiles for this chunk's products, and the chunk's operands
+        copy_async(smem + SL::kKd, slot + SL::kKd, static_cast<int>(SL::kU - SL::kKd), tid);
+        cp_async_commit();
+        // U values this thread will need after the first products, and the chunk's total decay
+        float2 u0[NTW], u1[NTW];
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+            const int col = dv0 + nw0 + nt * 8 + cq;
+            u0[nt] = *reinterpret_cast<const float2*>(sU + (m0 + i0) * D + col);
+            u1[nt] = *reinterpret_cast<const float2*>(sU + (m0 + i0 + 8) * D + col);
+        }
+        const float dl = *reinterpret_cast<const float*>(slot + SL::kDecay);
 #pragma unroll
         for (int nt = 0; nt < NTS; ++nt) {
             put2<DVB, SPLIT>(Sh, Sl, ms + i0, nt * 8 + cq, Sreg[nt][0], Sreg[nt][1]);
             put2<DVB, SPLIT>(Sh, Sl, ms + i0 + 8, nt * 8 + cq, Sreg[nt][2], Sreg[nt][3]);
         }
-        if (tid < C) Gs[tid] = sG[tid];
-        const float glast = sG[C - 1];
-        for (int e = tid; e < C * (D / 4); e += 256) {
-            const int r = e >> 5, c4 = (e & 31) * 4;
-            const float gr = sG[r];
-            put4<D, SPLIT>(Wh, Wl, r, c4, *reinterpret_cast<const float4*>(sW + r * D + c4));
-            float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
-            if (r < n) {
-                qv = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
-                kv = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
-                const float eq = expf(gr), ek = expf(glast - gr);
-                qv.x *= eq; qv.y *= eq; qv.z *= eq; qv.w *= eq;
-                kv.x *= ek; kv.y *= ek; kv.z *= ek; kv.w *= ek;
-            }
-            put4<D, SPLIT>(Qh, Ql, r, c4, qv);
-            put4<D, SPLIT>(Kh, Kl, r, c4, kv);
-        }
-        for (int e = tid; e < C * (C / 4); e += 256) {
-            const int r = e >> 4, c4 = (e & 15) * 4;
-            put4<C, SPLIT>(Ah, Al, r, c4, *reinterpret_cast<const float4*>(sQK + r * C + c4));
-        }
+        cp_async_wait<1>();   // {W, Qg} of this chunk have landed (issued one iteration ago)
         __syncthreads();
 
         // v' = U - W S   and   o = (q e^G) S   for rows m0.., columns nw0..
@@ -396,12 +455,13 @@ __global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs 
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt) {
             const int col = nw0 + nt * 8 + cq;
-            const float2 u0 = *reinterpret_cast<const float2*>(sU + (m0 + i0) * D + dv0 + col);
-            const float2 u1 = *reinterpret_cast<const float2*>(sU + (m0 + i0 + 8) * D + dv0 + col);
-            put2<DVB, SPLIT>(Vh, Vl, m0 + i0, col, u0.x - vp[nt][0], u0.y - vp[nt][1]);
-            put2<DVB, SPLIT>(Vh, Vl, m0 + i0 + 8, col, u1.x - vp[nt][2], u1.y - vp[nt][3]);
+            put2<DVB, SPLIT>(Vh, Vl, m0 + i0, col, u0[nt].x - vp[nt][0], u0[nt].y - vp[nt][1]);
+            put2<DVB, SPLIT>(Vh, Vl, m0 + i0 + 8, col, u1[nt].x - vp[nt][2], u1[nt].y - vp[nt][3]);
         }
-        __syncthreads();
+        cp_async_wait<0>();   // {Kd, A} of this chunk
+        __syncthreads();      // v' tiles and {Kd, A} visible; everyone is done with W, Qg and the S tiles
+        if (c + 1 < n_chunks) copy_async(smem + SL::kW, slot_ptr<SPLIT>(p, row_lo, seq, c + 1, h) + SL::kW, static_cast<int>(SL::kKd - SL::kW), tid);
+        cp_async_commit();
 
         // o += lower(q.k e^{..}) v'
 #pragma unroll
@@ -425,7 +485,6 @@ __global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs 
         }
 
         // S <- e^{G_last} S + (k e^{G_last - G})^T v'   for dk rows ms..ms+15, all DVB columns
-        const float dl = expf(glast);
 #pragma unroll
         for (int nt = 0; nt < NTS; ++nt)
 #pragma unroll
@@ -443,8 +502,9 @@ __global__ void __launch_bounds__(256) delta_chunk_apply_kernel(const ChunkArgs 
                 mma_split<SPLIT>(Sreg[2 * np], Sreg[2 * np + 1], ah, al, bh, bl);
             }
         }
-        __syncthreads();  // every warp is done with this chunk's tiles before they are overwritten
+        __syncthreads();  // every warp is done with {Kd, A}, v' and the S tiles before they are overwritten
     }
+    cp_async_wait<0>();
     if (p.write_state) {
 #pragma unroll
         for (int nt = 0; nt < NTS; ++nt)
@@ -479,7 +539,7 @@ int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_s
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", kPrepSmem, cudaGetErrorString(e));
         attr_set[ctx->device & 15] = true;
     }
-    prep<<<dim3(max_chunks, a.nv, n_seq), 128, kPrepSmem, s>>>(a);
+    prep<<<dim3(max_chunks, a.nv, n_seq), 256, kPrepSmem, s>>>(a);
     int rc = dc_check_launch(ctx, "gated_delta (chunk prepare)");
     if (rc != DC_OK) return rc;
     // few (sequence, head) pairs: split the value columns over more CTAs
@@ -490,7 +550,7 @@ int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_s
 }  // namespace
 
 size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) {
-    return (static_cast<size_t>(t) / C + n_seq + 1) * nv * kSlotFloats * sizeof(float);
+    return (static_cast<size_t>(t) / C + n_seq + 1) * nv * Slot<3>::kBytes;
 }
 
 int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const float* k, const float* v, const float* a, const float* b,
@@ -499,7 +559,7 @@ int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const fl
                            uint32_t max_len, uint32_t split) {
     ChunkArgs args{q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, nullptr, seq_start, t, ldab, nk, nv, write_state};
     const size_t bytes = dc_delta_chunk_scratch_bytes(t, n_seq, nv);
-    args.scratch = static_cast<float*>(dc_workspace(ctx, bytes));
+    args.scratch = static_cast<uint8_t*>(dc_workspace(ctx, bytes));
     if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);
     const uint32_t max_chunks = (max_len + C - 1) / C;
     if (split == 1) return launch_chunked<1>(ctx, s, args, n_seq, max_chunks);
