@@ -68,10 +68,12 @@ __device__ __forceinline__ uint8_t* slot_ptr(const ChunkArgs& p, uint32_t row_lo
 // ---------------------------------------------------------------------------------------------
 // Inverse of I + L for a strictly lower triangular 64x64 L (fp32, row stride LD) into N, by 16x16
 // blocks: the four diagonal blocks by in-warp forward substitution, then the off-diagonal blocks
-// one block-diagonal at a time, N_ij = -N_ii * sum_{k=j}^{i-1} L_ik N_kj. Warps 0..3 work; every warp
-// of the CTA must call it (it synchronises the CTA).
+// one block-diagonal at a time, N_ij = -N_ii * sum_{k=j}^{i-1} L_ik N_kj. Called by warps 0..3 only,
+// which synchronise among themselves on named barrier 1.
+__device__ __forceinline__ void bar4() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict__ N, float* __restrict__ P, int warp, int lane) {
-    if (warp < 4) {   // diagonal block `warp`: lane l < 16 holds column l; row i of the result needs rows < i
+    {   // diagonal block `warp`: lane l < 16 holds column l; row i of the result needs rows < i
         const int b0 = 16 * warp;
         const int l = lane & 15;
         float a[16];
@@ -102,9 +104,9 @@ __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict
     float* Pw = P + warp * 16 * 17;
     const int r = lane >> 1, c0 = (lane & 1) * 8;
     for (int d = 1; d < 4; ++d) {
-        __syncthreads();
+        bar4();
         const int i = d + warp, j = warp;  // block (i, j) with i - j = d
-        if (warp < 4 && i < 4) {
+        if (i < 4) {
             float acc[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[c] = 0.f;
@@ -132,7 +134,7 @@ __device__ void invert_unit_lower(const float* __restrict__ L, float* __restrict
             for (int c = 0; c < 8; ++c) N[(16 * i + r) * LD + 16 * j + c0 + c] = -acc[c];
         }
     }
-    __syncthreads();
+    bar4();
 }
 
 
@@ -143,11 +145,17 @@ __device__ __forceinline__ void gput2(uint8_t* base, int row, int col, float x0,
     put2<CW, SPLIT>(hi, hi + ROWS * CW, row, col, x0, x1);
 }
 
+template <int CW, int ROWS, int SPLIT>
+__device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const float4& v) {
+    __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(base);
+    put4<CW, SPLIT>(hi, hi + ROWS * CW, row, col, v);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel 1: one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
 // tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
 // onto L.
-constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 2 * C * 4;
+constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 5 * C * 4;
 
 template <int SPLIT>
 __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const ChunkArgs p) {
@@ -197,6 +205,17 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
     __syncthreads();
     const float glast = Gs[C - 1];
     if (tid == 0) *reinterpret_cast<float*>(slot + SL::kDecay) = expf(glast);
+    // per-row scale factors: e^G (for q), e^{G_last - G} (for k), beta e^G (for W's operand)
+    float* Eq = Bs + C;
+    float* Ek = Eq + C;
+    float* Es = Ek + C;
+    if (tid < C) {
+        const float g = Gs[tid];
+        Eq[tid] = expf(g);
+        Ek[tid] = expf(glast - g);
+        Es[tid] = Bs[tid] * expf(g);
+    }
+    __syncthreads();
 
     {   // K and Q tiles into shared memory; q e^G and k e^{G_last - G} tiles straight to scratch
         float4 kv[8], qv[8];
@@ -214,11 +233,9 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
             put4<D, SPLIT>(kh, kl, r, c4, kv[i]);
             put4<D, SPLIT>(qh, ql, r, c4, qv[i]);
-            const float eq = expf(Gs[r]), ek = expf(glast - Gs[r]);
-            gput2<D, C, SPLIT>(slot + SL::kQg, r, c4, qv[i].x * eq, qv[i].y * eq);
-            gput2<D, C, SPLIT>(slot + SL::kQg, r, c4 + 2, qv[i].z * eq, qv[i].w * eq);
-            gput2<D, C, SPLIT>(slot + SL::kKd, r, c4, kv[i].x * ek, kv[i].y * ek);
-            gput2<D, C, SPLIT>(slot + SL::kKd, r, c4 + 2, kv[i].z * ek, kv[i].w * ek);
+            const float eq = Eq[r], ek = Ek[r];
+            gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq));
+            gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
         }
     }
     __syncthreads();
@@ -269,33 +286,38 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         }
     }
     __syncthreads();
-    invert_unit_lower(Lf, Nf, Pf, warp, lane);
-
-    // T tiles; beta*k*e^G into the Q tiles, beta*v into the K tiles (both [token][feature])
+    if (warp < 4) {
+        // warps 0..3: T = (I + L)^-1, then its bf16 tiles (which reuse L's storage)
+        invert_unit_lower(Lf, Nf, Pf, warp, lane);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int e = tid + 256 * i, r = e >> 5, c2 = (e & 31) * 2;
-        put2<C, SPLIT>(th, tl, r, c2, Nf[r * LD + c2], Nf[r * LD + c2 + 1]);
-    }
-    {
-        float4 kv[8], vv[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
-            kv[i] = vv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < n) {
-                kv[i] = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
-                vv[i] = *reinterpret_cast<const float4*>(p.v + ((row_base + r) * p.nv + h) * D + c4);
-            }
+        for (int i = 0; i < 16; ++i) {
+            const int e = tid + 128 * i, r = e >> 5, c2 = (e & 31) * 2;
+            put2<C, SPLIT>(th, tl, r, c2, Nf[r * LD + c2], Nf[r * LD + c2 + 1]);
         }
+    } else {
+        // warps 4..7 meanwhile: beta*k*e^G into the Q tiles, beta*v into the K tiles (both [token][feature])
+        const int t2 = tid - 128;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+            float4 kv[8], vv[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
-            const float be = Bs[r], sk = be * expf(Gs[r]);
-            kv[i].x *= sk; kv[i].y *= sk; kv[i].z *= sk; kv[i].w *= sk;
-            vv[i].x *= be; vv[i].y *= be; vv[i].z *= be; vv[i].w *= be;
-            put4<D, SPLIT>(qh, ql, r, c4, kv[i]);
-            put4<D, SPLIT>(kh, kl, r, c4, vv[i]);
+            for (int i = 0; i < 8; ++i) {
+                const int e = t2 + 128 * (8 * half + i), r = e >> 5, c4 = (e & 31) * 4;
+                kv[i] = vv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < n) {
+                    kv[i] = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+                    vv[i] = *reinterpret_cast<const float4*>(p.v + ((row_base + r) * p.nv + h) * D + c4);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = t2 + 128 * (8 * half + i), r = e >> 5, c4 = (e & 31) * 4;
+                const float be = Bs[r], sk = Es[r];
+                kv[i].x *= sk; kv[i].y *= sk; kv[i].z *= sk; kv[i].w *= sk;
+                vv[i].x *= be; vv[i].y *= be; vv[i].z *= be; vv[i].w *= be;
+                put4<D, SPLIT>(qh, ql, r, c4, kv[i]);
+                put4<D, SPLIT>(kh, kl, r, c4, vv[i]);
+            }
         }
     }
     __syncthreads();

@@ -5,7 +5,7 @@
 // four epilogues (kernels/gemm.rs:16-26). Structure of one CTA (192 threads, one CTA per SM,
 // persistent over output tiles of 128 x BN):
 //   warp 0      TMA producer: X tile [128 x 64] and W tile [BN x 64] per k-block into a ring of
-//               128-byte-swizzled shared-memory stages (plain per-CTA loads, no multicast);
+//               128-byte-swizzled shared-memory stages (plain loads issued by this CTA for itself only);
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) over each stage and
 //               commits the stage back to the producer; owns the TMEM allocation;
 //   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread, 32 columns at

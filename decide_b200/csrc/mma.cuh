@@ -81,10 +81,22 @@ __device__ __forceinline__ void put2(__nv_bfloat16* hi, __nv_bfloat16* lo, int r
         *reinterpret_cast<__nv_bfloat162*>(lo + off) = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
     }
 }
+// Four values at (row, col), col a multiple of 4: one 8-byte store per tile.
 template <int C, int SPLIT>
 __device__ __forceinline__ void put4(__nv_bfloat16* hi, __nv_bfloat16* lo, int row, int col, const float4& v) {
-    put2<C, SPLIT>(hi, lo, row, col, v.x, v.y);
-    put2<C, SPLIT>(hi, lo, row, col + 2, v.z, v.w);
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+    const int off = tile_off<C>(row, col);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&h0);
+    w.y = *reinterpret_cast<const uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(hi + off) = w;
+    if constexpr (SPLIT == 3) {
+        const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+        const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+        w.x = *reinterpret_cast<const uint32_t*>(&l0);
+        w.y = *reinterpret_cast<const uint32_t*>(&l1);
+        *reinterpret_cast<uint2*>(lo + off) = w;
+    }
 }
 
 }  // namespace dc

@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the GEMM uses: mbarriers, TMA
-// tile loads (never multicast), tensor memory (TMEM) and tcgen05 MMA.
+// tile loads (each CTA loads only for itself), tensor memory (TMEM) and tcgen05 MMA.
 // Every wait is bounded: see mbar_wait().
 #pragma once
 #include <cstdint>
