@@ -136,7 +136,7 @@ def run_engine(args):
     import torch
     import torch.distributed as dist
 
-    from decide_b200 import check
+    from decide_b200 import check, dist as ddist
     from decide_b200.engine import Engine
     from decide_b200.kernels import Device
     from decide_b200.synth import synth_batch, synth_fused_on_device
@@ -175,11 +175,7 @@ def run_engine(args):
         torch.cuda.synchronize()
 
     def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], dtype=torch.float64, device=cuda)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return ddist.max_over_ranks(ms, cuda)
 
     stream = torch.cuda.current_stream()
     # ---- warm-up (also fills the tensor-map cache and leaves the batch resident on the device)
@@ -215,6 +211,24 @@ def run_engine(args):
     clocks = sampler.stop()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     dev.check_status()
+
+    # ---- single-request latency (p50 forward ms of the metric): one 2,307-token and one 603-token request,
+    # host buffers in, logits out, 3 warm-up + 10 timed calls each; linear-interpolated median as the
+    # reference's bench does (crates/decide-cli/src/bench.rs:103-112)
+    latency = {}
+    if rank == 0:
+        for toks, nans in ((2307, 3), (603, 6)):
+            one = synth_batch(dims, 1, toks, seed=7, n_answers=nans, n_cand=CANDS, max_cand=CANDS)
+            for _ in range(3):
+                eng.logits(one)
+            samples = []
+            for _ in range(10):
+                e0.record(stream)
+                eng.logits(one)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                samples.append(e0.elapsed_time(e1))
+            latency[f"tokens_{toks}"] = {"p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)), "runs": len(samples)}
 
     tokens = world * rows * args.steps
     value = tokens / (ms_value / 1e3)
@@ -266,6 +280,7 @@ def run_engine(args):
             "gemm_tflops_all_projections": gemm_tflops,
             "gemm_frac_of_peak": gemm_tflops / peaks["bf16_tflops_sustained"] if gemm_tflops else None,
             "per_op_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(prof.items(), key=lambda kv: -kv[1][0])},
+            "single_request_latency": latency,
             "cpu_baseline": cpu_baseline,
         }))
     eng.close()
