@@ -49,6 +49,12 @@ __device__ __forceinline__ void mma_16(float (&c)[4], const uint32_t (&a)[4], ui
     }
 }
 
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Copies `nrows` x 128 bf16 (rows beyond `valid` zero-filled) from global (row stride `ld`) into a swizzled tile.
 __device__ __forceinline__ void load_tile(uint16_t* tile, const uint16_t* src, size_t ld, int valid) {
     for (int e = threadIdx.x; e < BKV * (HD / 8); e += kThreads) {
@@ -105,6 +111,12 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
         ldsm_x4(qf[kk], qs + tile_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kk * 16 + (lane >> 4) * 8));
 
     const int qp0 = qp[warp * 16 + (lane >> 2)], qp1 = qp[warp * 16 + (lane >> 2) + 8];
+    int qp_warp_max = max(qp0, qp1), qp_warp_min = min(qp0, qp1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        qp_warp_max = max(qp_warp_max, __shfl_xor_sync(0xffffffffu, qp_warp_max, o));
+        qp_warp_min = min(qp_warp_min, __shfl_xor_sync(0xffffffffu, qp_warp_min, o));
+    }
     float m0 = kMasked, m1 = kMasked, l0 = 0.f, l1 = 0.f;
     float oacc[HD / 8][4];
 #pragma unroll
@@ -134,37 +146,58 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
         const uint16_t* ks = kv_tiles + stage * 2 * BKV * HD;
         const uint16_t* vs = ks + BKV * HD;
 
+        // 16-column groups of this tile that at least one row of this warp may see, and whether the whole
+        // tile is visible to every row of the warp (then no mask is needed); both warp-uniform
+        const int np_lim = qp_warp_max < j0 ? 0 : min(BKV / 16, (qp_warp_max - j0) / 16 + 1);
+        const bool no_mask = j0 + BKV - 1 <= qp_warp_min;
+
         float sacc[BKV / 8][4];
 #pragma unroll
         for (int i = 0; i < BKV / 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+        if (np_lim > 0) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+            for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
-            for (int np = 0; np < BKV / 16; ++np) {
-                uint32_t bfr[4];
-                ldsm_x4(bfr, ks + tile_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
-                mma_16<Act>(sacc[2 * np], qf[kk], bfr[0], bfr[1]);
-                mma_16<Act>(sacc[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+                for (int np = 0; np < BKV / 16; ++np) {
+                    if (np < np_lim) {
+                        uint32_t bfr[4];
+                        ldsm_x4(bfr, ks + tile_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
+                        mma_16<Act>(sacc[2 * np], qf[kk], bfr[0], bfr[1]);
+                        mma_16<Act>(sacc[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+                    }
+                }
             }
         }
         // scale, causal mask, running max
         float mx0 = kMasked, mx1 = kMasked;
+        if (no_mask) {
 #pragma unroll
-        for (int i = 0; i < BKV / 8; ++i) {
-            const int c = j0 + i * 8 + 2 * (lane & 3);
-            sacc[i][0] = c <= qp0 ? sacc[i][0] * scale_log2 : kMasked;
-            sacc[i][1] = c + 1 <= qp0 ? sacc[i][1] * scale_log2 : kMasked;
-            sacc[i][2] = c <= qp1 ? sacc[i][2] * scale_log2 : kMasked;
-            sacc[i][3] = c + 1 <= qp1 ? sacc[i][3] * scale_log2 : kMasked;
-            mx0 = fmaxf(mx0, fmaxf(sacc[i][0], sacc[i][1]));
-            mx1 = fmaxf(mx1, fmaxf(sacc[i][2], sacc[i][3]));
+            for (int i = 0; i < BKV / 8; ++i) {
+                sacc[i][0] *= scale_log2;
+                sacc[i][1] *= scale_log2;
+                sacc[i][2] *= scale_log2;
+                sacc[i][3] *= scale_log2;
+                mx0 = fmaxf(mx0, fmaxf(sacc[i][0], sacc[i][1]));
+                mx1 = fmaxf(mx1, fmaxf(sacc[i][2], sacc[i][3]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < BKV / 8; ++i) {
+                const int c = j0 + i * 8 + 2 * (lane & 3);
+                sacc[i][0] = c <= qp0 ? sacc[i][0] * scale_log2 : kMasked;
+                sacc[i][1] = c + 1 <= qp0 ? sacc[i][1] * scale_log2 : kMasked;
+                sacc[i][2] = c <= qp1 ? sacc[i][2] * scale_log2 : kMasked;
+                sacc[i][3] = c + 1 <= qp1 ? sacc[i][3] * scale_log2 : kMasked;
+                mx0 = fmaxf(mx0, fmaxf(sacc[i][0], sacc[i][1]));
+                mx1 = fmaxf(mx1, fmaxf(sacc[i][2], sacc[i][3]));
+            }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float corr0 = exp2f(m0 - mn0), corr1 = exp2f(m1 - mn1);
+        const float corr0 = ex2(m0 - mn0), corr1 = ex2(m1 - mn1);
         m0 = mn0;
         m1 = mn1;
         float rs0 = 0.f, rs1 = 0.f;
@@ -172,10 +205,10 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
 #pragma unroll
         for (int i = 0; i < BKV / 8; ++i) {
             // a masked score stays masked even when the whole row is masked so far (m = sentinel)
-            const float p0 = sacc[i][0] > 0.5f * kMasked ? exp2f(sacc[i][0] - mn0) : 0.f;
-            const float p1 = sacc[i][1] > 0.5f * kMasked ? exp2f(sacc[i][1] - mn0) : 0.f;
-            const float p2 = sacc[i][2] > 0.5f * kMasked ? exp2f(sacc[i][2] - mn1) : 0.f;
-            const float p3 = sacc[i][3] > 0.5f * kMasked ? exp2f(sacc[i][3] - mn1) : 0.f;
+            const float p0 = sacc[i][0] > 0.5f * kMasked ? ex2(sacc[i][0] - mn0) : 0.f;
+            const float p1 = sacc[i][1] > 0.5f * kMasked ? ex2(sacc[i][1] - mn0) : 0.f;
+            const float p2 = sacc[i][2] > 0.5f * kMasked ? ex2(sacc[i][2] - mn1) : 0.f;
+            const float p3 = sacc[i][3] > 0.5f * kMasked ? ex2(sacc[i][3] - mn1) : 0.f;
             const uint32_t lo = Act::pack(p0, p1), hi = Act::pack(p2, p3);
             rs0 += Act::lo(lo) + Act::hi(lo);
             rs1 += Act::lo(hi) + Act::hi(hi);
@@ -193,6 +226,7 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
         }
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
+            if (kk >= np_lim) break;   // the weights of those cache rows are all zero for this warp
 #pragma unroll
             for (int dp = 0; dp < HD / 16; ++dp) {
                 uint32_t bfr[4];

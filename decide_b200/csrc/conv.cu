@@ -12,7 +12,7 @@ namespace {
 using namespace dc;
 
 constexpr int kWarps = 4;
-constexpr int kRowsPerWarp = 16;
+constexpr int kRowsPerWarp = 32;
 
 // seq_start: [n_seq + 1] row offsets of packed sequences, or null for one sequence of `t` rows.
 // prev: [n_seq, 3, conv_dim] raw rows before each sequence (oldest first), or null for zeros.
@@ -46,8 +46,7 @@ conv_silu_l2_kernel(const float* __restrict__ p, const float* __restrict__ prev,
     const uint32_t s_end = min(s0 + kRowsPerWarp, len);
     const bool is_q = slot < nk, is_k = !is_q && slot < 2 * nk;
     const float qscale = 0.08838834764831845f;  // 128^-1/2
-    for (uint32_t s = s0; s < s_end; ++s) {
-        const float4 x3 = raw(static_cast<int>(s));
+    auto emit = [&](uint32_t s, const float4& x3) {
         float4 y;
         // channel c0+0 uses taps w0.{x,y,z,w} on rows s-3..s, and so on
         y.x = silu_f(fmaf(w0.w, x3.x, fmaf(w0.z, x2.x, fmaf(w0.y, x1.x, w0.x * x0.x))));
@@ -71,7 +70,17 @@ conv_silu_l2_kernel(const float* __restrict__ p, const float* __restrict__ prev,
             float* dst = v + (row * nv + (slot - 2 * nk)) * 128 + 4 * lane;
             *reinterpret_cast<float4*>(dst) = y;
         }
+    };
+    // four rows' loads in flight at a time
+    uint32_t s = s0;
+    for (; s + 4 <= s_end; s += 4) {
+        const float4 a0 = raw(static_cast<int>(s)), a1 = raw(static_cast<int>(s) + 1), a2 = raw(static_cast<int>(s) + 2), a3 = raw(static_cast<int>(s) + 3);
+        emit(s, a0);
+        emit(s + 1, a1);
+        emit(s + 2, a2);
+        emit(s + 3, a3);
     }
+    for (; s < s_end; ++s) emit(s, raw(static_cast<int>(s)));
 }
 
 // prev_out[i] = raw row (t - 3 + i) of the chunk, drawn from prev_in when t < 3; in-place safe
