@@ -67,13 +67,18 @@ __device__ __forceinline__ void load_tile(uint16_t* tile, const uint16_t* src, s
 
 // The same copy with cp.async (16 bytes per request, zero fill past `valid`): completes with the
 // thread's next cp.async.wait_group, so the next K/V tiles stream in under the current tile's MMAs.
+// Thread t copies chunk (t & 15) of rows (t >> 4) + 8 i: the swizzled chunk position is the same for
+// all its rows, so source and destination advance by constants.
 __device__ __forceinline__ void load_tile_async(uint16_t* tile, const uint16_t* src, size_t ld, int valid) {
-    for (int e = threadIdx.x; e < BKV * (HD / 8); e += kThreads) {
-        const int r = e >> 4, c = e & 15;
-        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(tile + tile_off(r, c * 8)));
-        const uint16_t* g = src + static_cast<size_t>(r < valid ? r : 0) * ld + c * 8;
-        const int bytes = r < valid ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g), "r"(bytes) : "memory");
+    const int r0 = threadIdx.x >> 4, c = threadIdx.x & 15;
+    uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(tile + tile_off(r0, c * 8)));
+    const uint16_t* g = src + static_cast<size_t>(r0) * ld + c * 8;
+#pragma unroll
+    for (int i = 0; i < BKV / 8; ++i) {
+        const int bytes = r0 + 8 * i < valid ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(bytes ? g : src), "r"(bytes) : "memory");
+        dst += 8 * HD * 2;
+        g += 8 * ld;
     }
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -81,13 +86,13 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <typename Act>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc, const uint16_t* __restrict__ vc,
                  const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t rows,
                  uint32_t ldg, uint32_t nq, uint32_t nkv, float scale_log2, const uint32_t* __restrict__ seq_start) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    uint16_t* qs = reinterpret_cast<uint16_t*>(smem_raw);
-    uint16_t* kv_tiles = qs + BQ * HD;   // two stages of (K tile, V tile)
+    uint16_t* kv_tiles = reinterpret_cast<uint16_t*>(smem_raw);   // two stages of (K tile, V tile)
+    uint16_t* qs = kv_tiles + 2 * BKV * HD;                       // the Q tile borrows stage 1 until its fragments are in registers
     int* qp = reinterpret_cast<int*>(kv_tiles + 4 * BKV * HD);  // [BQ] position of each query row, -1 = no row
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, kvh = h / (nq / nkv);
@@ -126,6 +131,7 @@ attn_fast_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
     const uint16_t* vbase = vc + (static_cast<size_t>(row_lo) * nkv + kvh) * HD;
     const size_t ldkv = static_cast<size_t>(nkv) * HD;
 
+    __syncthreads();  // every warp has its Q fragments: stage 1 may be overwritten
     // two-stage pipeline: tile it+1 is in flight while tile it is multiplied
     load_tile_async(kv_tiles, kbase, ldkv, min(kv_end, BKV));
     load_tile_async(kv_tiles + BKV * HD, vbase, ldkv, min(kv_end, BKV));
@@ -346,7 +352,7 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
                                                  gate, qpos, static_cast<uint16_t*>(y), rows, ldg, nq, nkv, scale, seq_start, n_seq);
         return dc_check_launch(ctx, "attention (baseline)");
     }
-    constexpr size_t smem = (BQ + 4 * BKV) * HD * 2 + BQ * sizeof(int);
+    constexpr size_t smem = 4 * BKV * HD * 2 + BQ * sizeof(int);
     static bool attr_set[16] = {};
     auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;
     if (!attr_set[ctx->device & 15]) {
