@@ -216,7 +216,7 @@ def run_engine(args):
     # host buffers in, logits out, 3 warm-up + 10 timed calls each; linear-interpolated median as the
     # reference's bench does (crates/decide-cli/src/bench.rs:103-112)
     latency = {}
-    if rank == 0:
+    if rank == 0 and not args.no_latency:
         for toks, nans in ((2307, 3), (603, 6)):
             one = synth_batch(dims, 1, toks, seed=7, n_answers=nans, n_cand=CANDS, max_cand=CANDS)
             for _ in range(3):
@@ -294,6 +294,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
+    ap.add_argument("--no-latency", action="store_true", help="skip the single-request latency runs (for short profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU forward (weights are then drawn on the GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
