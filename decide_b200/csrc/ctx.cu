@@ -112,6 +112,13 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         return nullptr;
     }
     *ctx->status_host = 0;
+    const size_t ws = static_cast<size_t>(ctx->sm_count) * 128 * 256 * sizeof(float);
+    if ((e = cudaMalloc(&ctx->gemm_part_ws, ws)) != cudaSuccess || (e = cudaMalloc(&ctx->gemm_part_cnt, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess) {
+        say("dc_open: cannot allocate the GEMM split workspace", cudaGetErrorString(e));
+        dc_close(ctx);
+        return nullptr;
+    }
     return ctx;
 }
 
@@ -121,6 +128,8 @@ void dc_close(dc_ctx* ctx) {
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->gemm_part_ws) cudaFree(ctx->gemm_part_ws);
+    if (ctx->gemm_part_cnt) cudaFree(ctx->gemm_part_cnt);
     delete ctx;
 }
 

@@ -8,7 +8,7 @@
 
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override);
-uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, int sm_count);
+uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count);
 
 namespace {
 
@@ -152,5 +152,5 @@ extern "C" int dc_gemm_tile(dc_ctx* ctx, void* stream, const void* x, const void
 }
 
 extern "C" uint32_t dc_gemm_plan(dc_ctx* ctx, uint32_t m, uint32_t n) {
-    return dc_gemm_plan_bn(m, n, ctx ? ctx->sm_count : 148);
+    return dc_gemm_plan_bn(m, n, 0, ctx ? ctx->sm_count : 148);
 }

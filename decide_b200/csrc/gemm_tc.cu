@@ -14,6 +14,8 @@
 // tile i+1. M, N and K tails come from TMA's out-of-bounds zero fill plus masked stores.
 // Every mbarrier wait is bounded; on expiry the CTA sets the status word, drains its own
 // copies in flight, frees its TMEM and returns.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -33,7 +35,35 @@ struct GemmArgs {
     uint32_t m, n, k, ldy;
     uint32_t m_tiles, n_tiles, k_blocks, group_m;
     uint32_t idesc;  // tcgen05 instruction descriptor: A and B in the context's 16-bit type, D = fp32
+    // Work units: the first `full_tiles` tiles are whole tiles; each of the remaining (tail-wave) tiles
+    // is cut into `split` parts along K of `kb_per_part` k-blocks, so the last wave fills the SMs too.
+    uint32_t full_tiles, split, kb_per_part;
+    float* part_ws;   // [tail tile][part][128][BN] fp32 partial accumulators
+    int* part_cnt;    // [tail tile][4 row quadrants] arrival counters, zero between launches
 };
+
+struct Unit {
+    uint32_t tile, part, kb0, kb1;
+    bool split;
+};
+__device__ __forceinline__ Unit unit_of(uint32_t u, const GemmArgs& a) {
+    Unit w;
+    if (u < a.full_tiles || a.split == 1u) {
+        w.tile = u;
+        w.part = 0;
+        w.kb0 = 0;
+        w.kb1 = a.k_blocks;
+        w.split = false;
+    } else {
+        const uint32_t v = u - a.full_tiles;
+        w.tile = a.full_tiles + v / a.split;
+        w.part = v - (v / a.split) * a.split;
+        w.kb0 = w.part * a.kb_per_part;
+        w.kb1 = min(a.k_blocks, w.kb0 + a.kb_per_part);
+        w.split = true;
+    }
+    return w;
+}
 
 template <int BN>
 struct Cfg {
@@ -164,6 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t num_tiles = a.m_tiles * a.n_tiles;
+    const uint32_t num_units = a.full_tiles + (num_tiles - a.full_tiles) * a.split;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -193,10 +224,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         if (lane == 0) {
             uint32_t s = 0, ph = 0, issued = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            for (uint32_t u = blockIdx.x; ok && u < num_units; u += gridDim.x) {
+                const Unit w = unit_of(u, a);
                 uint32_t tm, tn;
-                tile_coords(t, a, tm, tn);
-                for (uint32_t kb = 0; kb < a.k_blocks; ++kb) {
+                tile_coords(w.tile, a, tm, tn);
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, status, 1)) {
                         ok = false;
                         break;
@@ -235,12 +267,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             const uint32_t idesc = a.idesc;
             uint32_t s = 0, ph = 0, lt = 0;
             bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++lt) {
+            for (uint32_t u = blockIdx.x; ok && u < num_units; u += gridDim.x, ++lt) {
+                const Unit w = unit_of(u, a);
                 const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
                 if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1u, abort_flag, status, 2)) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < a.k_blocks; ++kb) {
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!mbar_wait(&full[s], ph, abort_flag, status, 3)) {
                         ok = false;
                         break;
@@ -251,7 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 #pragma unroll
                     for (uint32_t kk = 0; kk < BK / 16; ++kk) {
                         // 16 elements along K = 32 bytes = 2 units of the descriptor's 16-byte address field
-                        umma_bf16_ss(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (kb | kk) != 0u ? 1u : 0u);
+                        umma_bf16_ss(d_tmem, ad + 2 * kk, bd + 2 * kk, idesc, (kb != w.kb0 || kk != 0u) ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);
                     if (++s == S) {
@@ -266,9 +299,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         // ---------------------------------------------------------------- epilogue
         const uint32_t q = static_cast<uint32_t>(warp) & 3u;  // TMEM lane quadrant this warp may read
         uint32_t lt = 0;
-        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++lt) {
+        for (uint32_t u = blockIdx.x; u < num_units; u += gridDim.x, ++lt) {
+            const Unit w = unit_of(u, a);
             uint32_t tm, tn;
-            tile_coords(t, a, tm, tn);
+            tile_coords(w.tile, a, tm, tn);
             const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
             bool ok = mbar_wait(&acc_full[acc], acc_ph, abort_flag, status, 4);
             ok = __all_sync(0xffffffffu, ok);
@@ -277,18 +311,102 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             const size_t row0 = static_cast<size_t>(tm) * BM + q * 32u;
             float* st = epi_stage + (warp - 2) * 32 * kEpiLd;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+            if (!w.split) {
 #pragma unroll 1
-            for (uint32_t c = 0; c < BN / 32; ++c) {
-                const uint32_t col0 = tn * BN + c * 32u;
-                if (col0 >= a.n) break;
-                uint32_t r[32];
-                tmem_ld_32x32(taddr + c * 32u, r);
-                tmem_ld_wait();
-                epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    const uint32_t col0 = tn * BN + c * 32u;
+                    if (col0 >= a.n) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c * 32u, r);
+                    tmem_ld_wait();
+                    epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            } else {
+                // One part of a K-split tile: park the raw accumulator in the workspace, laid out
+                // [part][32-column chunk][128 rows][32] so that every warp instruction moves 4 whole rows of
+                // a chunk (512 contiguous bytes). The warp that arrives last for these 32 rows adds the parts
+                // in part order (so the result does not depend on who was last) and runs the epilogue.
+                // Nobody waits for anybody.
+                const uint32_t rt = w.tile - a.full_tiles;
+                const int sub = lane >> 3, l8 = lane & 7;
+                constexpr uint32_t kChunkFloats = BM * 32;                 // one chunk of all 128 rows
+                constexpr uint32_t kPartFloats = BM * BN;
+                float* mine = a.part_ws + static_cast<size_t>(rt * a.split + w.part) * kPartFloats + q * 32u * 32u;
+#pragma unroll 1
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    if (tn * BN + c * 32u >= a.n) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c * 32u, r);
+                    tmem_ld_wait();
+                    float4* row = reinterpret_cast<float4*>(st + lane * kEpiLd);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        row[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    __syncwarp();
+                    float* dst = mine + c * kChunkFloats;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + sub;
+                        __stcg(reinterpret_cast<float4*>(dst + rr * 32 + 4 * l8), *reinterpret_cast<const float4*>(st + rr * kEpiLd + 4 * l8));
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before_sync();
+                __threadfence();
+                __syncwarp();
+                int prev = 0;
+                if (lane == 0) {
+                    mbar_arrive(&acc_empty[acc]);
+                    prev = atomicAdd(&a.part_cnt[rt * 4u + q], 1);
+                }
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                if (prev == static_cast<int>(a.split) - 1) {
+                    __threadfence();
+                    const float* base = a.part_ws + static_cast<size_t>(rt * a.split) * kPartFloats + q * 32u * 32u;
+#pragma unroll 1
+                    for (uint32_t c = 0; c < BN / 32; ++c) {
+                        const uint32_t col0 = tn * BN + c * 32u;
+                        if (col0 >= a.n) break;
+                        float4 sum[8];
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (uint32_t pt = 0; pt < 4; ++pt) {
+                            if (pt < a.split) {
+                                const float* src = base + pt * kPartFloats + c * kChunkFloats;
+#pragma unroll
+                                for (int it = 0; it < 8; ++it) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (it * 4 + sub) * 32 + 4 * l8));
+                                    sum[it].x += v.x;
+                                    sum[it].y += v.y;
+                                    sum[it].z += v.z;
+                                    sum[it].w += v.w;
+                                }
+                            }
+                        }
+                        // back to one row per thread for the common epilogue
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) *reinterpret_cast<float4*>(st + (it * 4 + sub) * kEpiLd + 4 * l8) = sum[it];
+                        __syncwarp();
+                        uint32_t r[32];
+                        const uint4* row = reinterpret_cast<const uint4*>(st + lane * kEpiLd);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint4 v = row[j];
+                            r[4 * j] = v.x;
+                            r[4 * j + 1] = v.y;
+                            r[4 * j + 2] = v.z;
+                            r[4 * j + 3] = v.w;
+                        }
+                        __syncwarp();
+                        epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
+                    }
+                    if (lane == 0) atomicExch(&a.part_cnt[rt * 4u + q], 0);
+                }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[acc]);
         }
     }
 
@@ -336,8 +454,8 @@ int launch(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtens
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cannot opt in to %u bytes of shared memory: %s", C::kSmemBytes, cudaGetErrorString(e));
         attr_set[ctx->device & 15] = true;
     }
-    const uint32_t tiles = a.m_tiles * a.n_tiles;
-    const uint32_t grid = tiles < static_cast<uint32_t>(ctx->sm_count) ? tiles : static_cast<uint32_t>(ctx->sm_count);
+    const uint32_t units = a.full_tiles + (a.m_tiles * a.n_tiles - a.full_tiles) * a.split;
+    const uint32_t grid = units < static_cast<uint32_t>(ctx->sm_count) ? units : static_cast<uint32_t>(ctx->sm_count);
     kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tx, tw, y, a, ctx->status_dev);
     return dc_check_launch(ctx, "gemm (tcgen05)");
 }
@@ -359,22 +477,51 @@ int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CU
 }  // namespace
 
 // Tile plan: the analogue of gemm_configs::plan (crates/decide-metal/src/gemm_configs.rs:312).
-// 128 x 256 tiles unless the narrower 128 x 128 tile fills the SMs in clearly fewer waves.
-uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, int sm_count) {
-    const uint32_t m_tiles = (m + BM - 1) / BM;
-    auto waves = [&](uint32_t bn) {
-        const uint32_t tiles = m_tiles * ((n + bn - 1) / bn);
-        return (tiles + sm_count - 1) / sm_count;
+// Whole waves of 128 x BN tiles run as whole tiles; the tiles of the last, partial wave are cut along
+// K into up to 4 parts so that wave fills the SMs as well. BN = 256 unless the narrower tile is
+// clearly cheaper under this model, calibrated on the B200: relative time = waves x tile width; a
+// 128-wide tile costs 0.9 of a 256-wide one (its operand feed, not its MMAs, sets its pace); the
+// fix-up of a split tile costs as much as ~45 k-blocks of main loop, so only long-K GEMMs split.
+namespace {
+struct Plan {
+    uint32_t bn, full_tiles, split, kb_per_part;
+    double cost;
+};
+Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t max_split = 4) {
+    const uint32_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+    const uint32_t k_blocks = (k + BK - 1) / BK;
+    const uint32_t rest = tiles % sms;
+    Plan p{bn, tiles - rest, 1, k_blocks, 0.0};
+    if (rest > 0) {
+        uint32_t split = sms / rest < max_split ? sms / rest : max_split;
+        while (split > 1 && k_blocks / split < 8) --split;
+        p.split = split ? split : 1;
+        p.kb_per_part = (k_blocks + p.split - 1) / p.split;
+    }
+    auto tail_of = [&](uint32_t split) {
+        const uint32_t per = (k_blocks + split - 1) / split;
+        return static_cast<double>(per) / k_blocks + (split > 1 ? 45.0 / k_blocks : 0.0);
     };
-    // relative time: waves x tile width, with a 12% penalty for the narrow tile's lower operand reuse
-    const double t256 = waves(256) * 256.0;
-    const double t128 = waves(128) * 128.0 * 1.12;
-    return t128 < t256 ? 128u : 256u;
+    while (p.split > 1 && tail_of(p.split) >= 1.0) --p.split;   // not worth it
+    p.kb_per_part = (k_blocks + p.split - 1) / p.split;
+    const double tail = rest == 0 ? 0.0 : tail_of(p.split);
+    p.cost = (tiles / sms + tail) * bn * (bn == 128 ? 1.8 : 1.0);
+    return p;
 }
+Plan best_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t bn_override, uint32_t max_split = 4) {
+    if (bn_override) return plan_for(bn_override, m, n, k, sms, max_split);
+    const Plan a = plan_for(256, m, n, k, sms, max_split), b = plan_for(128, m, n, k, sms, max_split);
+    return b.cost < a.cost ? b : a;
+}
+}  // namespace
+
+uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count) { return best_plan(m, n, k ? k : 2560, sm_count, 0).bn; }
 
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override) {
-    const uint32_t bn = bn_override ? bn_override : dc_gemm_plan_bn(m, n, ctx->sm_count);
+    static const uint32_t max_split = getenv("DECIDE_GEMM_SPLIT") ? static_cast<uint32_t>(atoi(getenv("DECIDE_GEMM_SPLIT"))) : 4u;
+    const Plan pl = best_plan(m, n, k, static_cast<uint32_t>(ctx->sm_count), bn_override, max_split ? max_split : 1u);
+    const uint32_t bn = pl.bn;
     GemmArgs a;
     a.m = m;
     a.n = n;
@@ -384,6 +531,11 @@ int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, v
     a.n_tiles = (n + bn - 1) / bn;
     a.k_blocks = (k + BK - 1) / BK;
     a.group_m = a.m_tiles < 16 ? a.m_tiles : 16;
+    a.full_tiles = pl.full_tiles;
+    a.split = pl.split;
+    a.kb_per_part = pl.kb_per_part;
+    a.part_ws = ctx->gemm_part_ws;
+    a.part_cnt = ctx->gemm_part_cnt;
     const bool f16 = ctx->act_dtype == DC_ACT_F16;
     // Both operands carry the same format code: kind::f16 with an fp16 A and a bf16 B raises an
     // illegal-instruction fault on sm_100a.
