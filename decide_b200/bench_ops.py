@@ -100,10 +100,11 @@ def conv(k, n_seq, tokens, nk, nv, iters, warmup):
     return {"op": "conv_silu_l2", "rows": rows, "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}
 
 
-def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3):
-    from .kernels import Family, Impl
+def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3, engine="tcgen05"):
+    from .kernels import DeltaEngine, Family, Impl
     k.dev.set_impl(Family.Delta, Impl.Fast if impl == "fast" else Impl.Baseline)
     k.dev.set_delta_split(split)
+    k.dev.set_delta_engine(DeltaEngine.Tcgen05 if engine == "tcgen05" else DeltaEngine.MmaSync)
     rows = n_seq * tokens
     q = torch.nn.functional.normalize(torch.randn(rows, nk, 128, device="cuda"), dim=-1) * 128 ** -0.5
     kk = torch.nn.functional.normalize(torch.randn(rows, nk, 128, device="cuda"), dim=-1)
@@ -117,9 +118,10 @@ def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3):
     us = _time(fn, iters, warmup)
     k.dev.set_impl(Family.Delta, Impl.Fast)
     k.dev.set_delta_split(3)
+    k.dev.set_delta_engine(DeltaEngine.Tcgen05)
     nbytes = rows * (2 * nk + 2 * nv) * 128 * 4.0
     flops = rows * nv * 128.0 * 128.0 * 7.0  # the sequential recurrence: decay, two dots, rank-1 update per state element
-    return {"op": "gated_delta", "impl": impl if impl != "fast" else f"chunked split {split}", "seqs": n_seq, "tokens": tokens, "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3, "flops": flops, "tflops_fp32": flops / us / 1e6,
+    return {"op": "gated_delta", "impl": impl if impl != "fast" else f"chunked split {split}" + (f" {engine}" if split == 3 else ""), "seqs": n_seq, "tokens": tokens, "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3, "flops": flops, "tflops_fp32": flops / us / 1e6,
             "us_per_token_step": us / tokens}
 
 
@@ -187,6 +189,7 @@ def main():
         out.append(conv(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup))
     elif a.op == "delta":
         out.append(delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup))
+        out.append(delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup, engine="mma"))
     elif a.op == "rope":
         out.append(rope(k, a.rows, 32, 8, True, a.iters, a.warmup))
     elif a.op == "attention":
@@ -198,7 +201,8 @@ def main():
         for seqs, tokens in ((64, 603), (1, 2307)):
             rows = seqs * tokens
             out += [rmsnorm(k, rows, 2560, a.iters, a.warmup), gnorm(k, rows, 16, a.iters, a.warmup), conv(k, seqs, tokens, 16, 16, a.iters, a.warmup),
-                    delta(k, seqs, tokens, 16, 16, a.iters, a.warmup), delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, split=1),
+                    delta(k, seqs, tokens, 16, 16, a.iters, a.warmup), delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, engine="mma"),
+                    delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, split=1),
                     delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, impl="baseline"), rope(k, rows, 32, 8, True, a.iters, a.warmup),
                     attention(k, seqs, tokens, 32, 8, True, a.iters, a.warmup)]
     dev.check_status()

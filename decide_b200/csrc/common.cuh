@@ -36,6 +36,7 @@ struct dc_ctx {
     uint32_t gemm_impl = DC_IMPL_FAST;
     uint32_t attn_impl = DC_IMPL_FAST;
     uint32_t delta_impl = DC_IMPL_FAST;
+    uint32_t delta_engine = DC_DELTA_TCGEN05;  // serial kernel of the chunked delta rule (split 3)
     uint32_t delta_split = 3;         // chunked delta rule: 3 = hi/lo split operands (near fp32), 1 = single bf16 pass
     uint32_t act_dtype = DC_ACT_F16;  // type of every 16-bit GEMM operand: activations and weight matrices
     float* gemm_part_ws = nullptr;   // partial accumulators of K-split tail tiles: sm_count x 128 x 256 fp32

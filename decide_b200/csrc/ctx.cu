@@ -85,13 +85,18 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         else if (strcmp(d, "3") == 0 || !*d) ctx->delta_split = 3;
         else bad = true;
     }
+    if (const char* d = getenv("DECIDE_DELTA_ENGINE")) {
+        if (strcmp(d, "mma") == 0) ctx->delta_engine = DC_DELTA_MMA_SYNC;
+        else if (strcmp(d, "tcgen05") == 0 || !*d) ctx->delta_engine = DC_DELTA_TCGEN05;
+        else bad = true;
+    }
     if (const char* a = getenv("DECIDE_ACT")) {
         if (strcmp(a, "bf16") == 0) ctx->act_dtype = DC_ACT_BF16;
         else if (strcmp(a, "f16") == 0 || !*a) ctx->act_dtype = DC_ACT_F16;
         else bad = true;
     }
     if (bad) {
-        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`, DECIDE_ACT `f16` or `bf16`", nullptr);
+        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`, DECIDE_ACT `f16` or `bf16`, DECIDE_DELTA_SPLIT 1 or 3, DECIDE_DELTA_ENGINE `tcgen05` or `mma`", nullptr);
         delete ctx;
         return nullptr;
     }
@@ -178,6 +183,13 @@ int dc_set_delta_split(dc_ctx* ctx, uint32_t split) {
     if (!ctx) return DC_INVALID_ARG;
     DC_REQUIRE(ctx, split == 1 || split == 3, "dc_set_delta_split: %u is neither 1 nor 3", split);
     ctx->delta_split = split;
+    return DC_OK;
+}
+
+int dc_set_delta_engine(dc_ctx* ctx, uint32_t engine) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, engine == DC_DELTA_MMA_SYNC || engine == DC_DELTA_TCGEN05, "dc_set_delta_engine: unknown engine %u", engine);
+    ctx->delta_engine = engine;
     return DC_OK;
 }
 

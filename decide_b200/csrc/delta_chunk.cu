@@ -15,6 +15,7 @@
 // ~1e-5 against fp32), because a single bf16/fp16 pass puts ~5e-4 relative error into o.
 #include "common.cuh"
 #include "mma.cuh"
+#include "ptx.cuh"
 
 namespace {
 
@@ -43,6 +44,50 @@ struct Slot {
     static constexpr size_t kDecay = kU + C * D * 4;
     static constexpr size_t kBytes = kDecay + 16;
 };
+
+// The same scratch for the tcgen05 form of kernel 2 (split 3 only). Every bf16 tile is K-major with
+// 128-byte rows of 64 elements and the 128-byte swizzle a tensor-map copy would produce (the 16-byte
+// chunk c of row r sits at chunk position c ^ (r & 7)), so tcgen05.mma reads it through a shared-
+// memory descriptor after one flat bulk copy:
+//   WQ  [hi|lo][k-atom 2][128 rows = W rows 0..63, Qg rows 64..127][64]   B operand of S W^T | S Qg^T
+//   AK  [hi|lo]{ A [64 i][64 j] ; Kd^T [128 dk][64 j] }                   B operands of v'^T A^T and v'^T Kd
+//   U, e^{G_last} as above
+struct SlotTC {
+    static constexpr size_t kAtom128 = 128 * 128;             // bytes of one k-atom of a 128-row tile
+    static constexpr size_t kWQ = 0;
+    static constexpr size_t kWQPart = 2 * kAtom128;           // hi or lo
+    static constexpr size_t kAK = kWQ + 2 * kWQPart;
+    static constexpr size_t kAKPart = 64 * 128 + kAtom128;    // hi or lo: A then Kd^T
+    static constexpr size_t kU = kAK + 2 * kAKPart;
+    static constexpr size_t kDecay = kU + C * D * 4;
+    static constexpr size_t kBytes = kDecay + 16;
+};
+static_assert(SlotTC::kBytes == Slot<3>::kBytes && SlotTC::kU == Slot<3>::kU, "both scratch layouts share slot size and the U offset");
+
+// Element offset of (row, k) in a K-major tile of ROWS rows made of 64-element k-atoms, 128-byte swizzle.
+template <int ROWS>
+__device__ __forceinline__ int umma_off(int row, int k) {
+    return (k >> 6) * ROWS * 64 + row * 64 + ((((k & 63) >> 3) ^ (row & 7)) << 3) + (k & 7);
+}
+// hi/lo bf16 pair stores at an element offset of a tile pair in global memory (lo tile `lo_bytes` after hi)
+__device__ __forceinline__ void tc_put2(uint8_t* hi_base, size_t lo_bytes, int off, float x0, float x1) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+    const float2 hf = __bfloat1622float2(h);
+    *reinterpret_cast<__nv_bfloat162*>(hi_base + 2 * off) = h;
+    *reinterpret_cast<__nv_bfloat162*>(hi_base + lo_bytes + 2 * off) = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
+}
+__device__ __forceinline__ void tc_put4(uint8_t* hi_base, size_t lo_bytes, int off, const float4& v) {
+    const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+    const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+    const __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&h0);
+    w.y = *reinterpret_cast<const uint32_t*>(&h1);
+    *reinterpret_cast<uint2*>(hi_base + 2 * off) = w;
+    w.x = *reinterpret_cast<const uint32_t*>(&l0);
+    w.y = *reinterpret_cast<const uint32_t*>(&l1);
+    *reinterpret_cast<uint2*>(hi_base + lo_bytes + 2 * off) = w;
+}
 
 struct ChunkArgs {
     const float *q, *k, *v, *a, *b, *a_log, *dt_bias;
@@ -157,8 +202,9 @@ __device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const flo
 // onto L.
 constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 5 * C * 4;
 
-template <int SPLIT>
+template <int SPLIT, bool TC>
 __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const ChunkArgs p) {
+    static_assert(!TC || SPLIT == 3, "the tcgen05 scratch layout exists for split 3 only");
     using SL = Slot<SPLIT>;
     extern __shared__ __align__(16) uint8_t smem[];
     __nv_bfloat16* kh = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -234,11 +280,45 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             put4<D, SPLIT>(kh, kl, r, c4, kv[i]);
             put4<D, SPLIT>(qh, ql, r, c4, qv[i]);
             const float eq = Eq[r], ek = Ek[r];
-            gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq));
-            gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
+            const float4 qe = make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq);
+            if constexpr (TC) {
+                tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(64 + r, c4), qe);
+            } else {
+                gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, qe);
+                gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
+            }
         }
     }
     __syncthreads();
+    if constexpr (TC) {
+        // Kd^T [dk][j] = k_j[dk] e^{G_last - G_j}, token index contiguous: read the K tiles column-wise
+        // (k as hi + lo carries 16 mantissa bits, which is what the products use anyway)
+        const int dk = tid & 127, jh = tid >> 7;
+        uint8_t* kt = slot + SlotTC::kAK + 64 * 128;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            const int chunk = 4 * jh + cc;
+            uint32_t wh[4], wl[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+                float x[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = 8 * chunk + 2 * e2 + e;
+                    const int off = tile_off<D>(j, dk);
+                    x[e] = (__bfloat162float(kh[off]) + __bfloat162float(kl[off])) * Ek[j];
+                }
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(x[0], x[1]);
+                const float2 hf = __bfloat1622float2(h2);
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(x[0] - hf.x, x[1] - hf.y);
+                wh[e2] = *reinterpret_cast<const uint32_t*>(&h2);
+                wl[e2] = *reinterpret_cast<const uint32_t*>(&l2);
+            }
+            const int off = dk * 64 + ((chunk ^ (dk & 7)) << 3);
+            *reinterpret_cast<uint4*>(kt + 2 * off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+            *reinterpret_cast<uint4*>(kt + SlotTC::kAKPart + 2 * off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+        }
+    }
 
     const int m0 = 16 * wr;
     {   // k.k^T and q.k^T: 16 rows x 32 columns per warp
@@ -281,8 +361,13 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
                 aqk[nt][e] *= d0;
                 aqk[nt][2 + e] *= d1;
             }
-            gput2<C, C, SPLIT>(slot + SL::kA, i0, jb, aqk[nt][0], aqk[nt][1]);
-            gput2<C, C, SPLIT>(slot + SL::kA, i1, jb, aqk[nt][2], aqk[nt][3]);
+            if constexpr (TC) {
+                tc_put2(slot + SlotTC::kAK, SlotTC::kAKPart, umma_off<64>(i0, jb), aqk[nt][0], aqk[nt][1]);
+                tc_put2(slot + SlotTC::kAK, SlotTC::kAKPart, umma_off<64>(i1, jb), aqk[nt][2], aqk[nt][3]);
+            } else {
+                gput2<C, C, SPLIT>(slot + SL::kA, i0, jb, aqk[nt][0], aqk[nt][1]);
+                gput2<C, C, SPLIT>(slot + SL::kA, i1, jb, aqk[nt][2], aqk[nt][3]);
+            }
         }
     }
     __syncthreads();
@@ -350,8 +435,13 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         for (int nt = 0; nt < 8; ++nt) {
             const int j = 64 * wc + nt * 8 + 2 * (lane & 3);
             if (which == 0) {
-                gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
-                gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
+                if constexpr (TC) {
+                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(i0, j), acc[nt][0], acc[nt][1]);
+                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(i1, j), acc[nt][2], acc[nt][3]);
+                } else {
+                    gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
+                    gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
+                }
             } else {
                 float* sU = reinterpret_cast<float*>(slot + SL::kU);
                 *reinterpret_cast<float2*>(sU + i0 * D + j) = make_float2(acc[nt][0], acc[nt][1]);
@@ -538,6 +628,313 @@ __global__ void __launch_bounds__(256, 1) delta_chunk_apply_kernel(const ChunkAr
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Kernel 2 on tcgen05: one CTA (8 warps) per (sequence, head) walks the chunks in order. Everything is
+// transposed so that the 128 value columns are the M dimension (= TMEM lanes) of every product:
+//   acc_v [dv][64]      = S W^T                  (then v'^T = U^T - acc_v)
+//   acc_o [dv][64] x 2  = S Qg^T + v'^T A^T      (= o^T; two buffers, alternating by chunk)
+//   acc_ds[dv][128]     = v'^T Kd                (the state increment)
+// The A operands, S [dv][dk] and v'^T [dv][j], are written by the threads (thread = one dv row = one
+// TMEM lane) as packed bf16 hi and lo parts straight into tensor memory, so the MMAs fetch only their B
+// operands (W|Qg, A, Kd^T: K-major swizzled tiles, one flat 112 KB bulk copy per chunk, double-
+// buffered) from shared memory; with both operands in shared memory these small products are bound by
+// shared-memory bandwidth. Each product runs as lo*hi + hi*lo + hi*hi into one fp32 accumulator. The
+// fp32 state stays in registers: warp w owns TMEM lanes 32(w%4).. (value columns) and the dk half w/4.
+// All 512 TMEM columns are used: 320 of accumulators, 128 of S, 64 of v'.
+// The serial chain of a chunk is: S -> S W^T -> v' -> v'^T Kd -> state. The two products that only feed
+// o (S Qg^T, v'^T A^T) are issued behind the chain's products; o of chunk c is read out and stored
+// while S W^T of chunk c+1 runs.
+// Thread 0 issues the bulk copies and the MMAs. Every wait, the block-wide ones included, is a bounded
+// mbarrier wait; when one gives up the CTA raises the status word, waits for its copies and MMAs in
+// flight, frees its tensor memory and returns.
+struct TcSmem {
+    static constexpr size_t kOps = SlotTC::kU;                // W|Qg then A|Kd^T, hi and lo: the head of a scratch slot
+    static constexpr size_t kBars = 2 * kOps;
+    static constexpr size_t kBytes = kBars + 128 + 1024;      // barriers and flags; slack to align the base to 1 KB
+};
+static_assert(SlotTC::kWQ == 0 && SlotTC::kAK == 2 * SlotTC::kWQPart && SlotTC::kU == SlotTC::kAK + 2 * SlotTC::kAKPart, "operands are contiguous");
+constexpr uint32_t kTcTmemCols = 512;
+// accumulator columns (o: + 64 per buffer) and the packed-bf16 A operands (two K elements per column)
+constexpr uint32_t kTcColV = 0, kTcColO = 64, kTcColDs = 192, kTcColSHi = 320, kTcColSLo = 384, kTcColVHi = 448, kTcColVLo = 480;
+constexpr uint32_t kABytes = 64 * 128;   // one (hi or lo) A tile; the Kd^T tile follows it
+
+// Block-wide barrier on an mbarrier with one arrival per warp.
+__device__ __forceinline__ bool tc_block_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag, int* status, int code) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    const bool ok = mbar_wait(bar, phase, abort_flag, status, code);
+    phase ^= 1u;
+    return ok;
+}
+// 2n fp32 values -> n columns of packed bf16 hi parts and n of lo parts
+template <int N>
+__device__ __forceinline__ void tc_split_pack(const float* x, uint32_t (&hi)[N], uint32_t (&lo)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+        const float2 hf = __bfloat1622float2(h2);
+        const __nv_bfloat162 l2 = __floats2bfloat162_rn(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
+        hi[i] = *reinterpret_cast<const uint32_t*>(&h2);
+        lo[i] = *reinterpret_cast<const uint32_t*>(&l2);
+    }
+}
+// D[tmem] (+)= A B^T with split operands over KSTEPS steps of 16 along K: A parts in tensor memory (8 columns
+// per step), B parts K-major in shared memory with 128-byte rows (2 descriptor units of 16 bytes per step).
+template <int KSTEPS>
+__device__ __forceinline__ void tc_mma_split(uint32_t d_tmem, uint32_t a_hi, uint32_t a_lo, uint64_t b_hi, uint64_t b_lo, uint32_t idesc, bool accumulate) {
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        if (accumulate || ks > 0) umma_bf16_ts<true>(d_tmem, a_lo + 8 * ks, b_hi + 2 * ks, idesc);
+        else umma_bf16_ts<false>(d_tmem, a_lo + 8 * ks, b_hi + 2 * ks, idesc);
+        umma_bf16_ts<true>(d_tmem, a_hi + 8 * ks, b_lo + 2 * ks, idesc);
+        umma_bf16_ts<true>(d_tmem, a_hi + 8 * ks, b_hi + 2 * ks, idesc);
+    }
+}
+
+#ifdef DC_TC_TIMELINE
+// Debug build only: cycle stamps of the first chunks of CTA (0, 0), threads 0 and 128.
+__device__ long long g_tc_timeline[2 * 16 * 16];
+#define TL(k) do { if (tl_who >= 0 && c < 16) g_tc_timeline[(c * 2 + tl_who) * 16 + (k)] = clock64(); } while (0)
+#else
+#define TL(k) do { } while (0)
+#endif
+
+constexpr int kTcThreads = 288;   // warps 0..7 work on the rows, warp 8 issues the copies and the MMAs
+
+__global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(const ChunkArgs p, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + TcSmem::kBars);
+    uint64_t* full = bars + 0;       // [2] bulk copy of a chunk's operands landed in buffer b
+    uint64_t* m1_done = bars + 2;    // S W^T finished
+    uint64_t* ds_done = bars + 3;    // v'^T Kd finished (and S Qg^T before it)
+    uint64_t* o_done = bars + 4;     // v'^T A^T finished: o^T complete, the chunk's operand buffer is free
+    uint64_t* all_bar = bars + 5;    // block-wide barrier (9 arrivals, one per warp)
+    uint64_t* drain_bar = bars + 6;  // teardown: MMAs still in flight
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* never_flag = tmem_slot + 2;   // stays 0: the teardown waits do not give up early
+
+    const uint32_t seq = blockIdx.y, h = blockIdx.x;
+    uint32_t row_lo, len;
+    seq_bounds(p, seq, row_lo, len);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n_chunks = (len + C - 1) / C;
+
+    if (tid == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        mbar_init(m1_done, 1);
+        mbar_init(ds_done, 1);
+        mbar_init(o_done, 1);
+        mbar_init(all_bar, 9);
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0u;
+        *never_flag = 0u;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_slot, kTcTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ issuer (one thread)
+        if (lane == 0 && n_chunks) {
+            uint32_t loads_issued = 0, loads_waited = 0, sync_ph = 0;
+            auto load_ops = [&](uint32_t c) {   // the bulk copy of chunk c's operands into buffer c & 1
+                mbar_arrive_expect_tx(&full[c & 1u], static_cast<uint32_t>(TcSmem::kOps));
+                bulk_load(smem + (c & 1u) * TcSmem::kOps, slot_ptr<3>(p, row_lo, seq, c, h), static_cast<uint32_t>(TcSmem::kOps), &full[c & 1u]);
+                loads_issued = c + 1;
+            };
+            auto sync_all = [&](int code) {
+                mbar_arrive(all_bar);
+                const bool ok = mbar_wait(all_bar, sync_ph, abort_flag, status, code);
+                sync_ph ^= 1u;
+                return ok;
+            };
+            load_ops(0);
+            if (n_chunks > 1) load_ops(1);
+            constexpr uint32_t idesc128 = umma_idesc(1, 1, 128, 128), idesc64 = umma_idesc(1, 1, 128, 64);
+            const uint32_t t_shi = tmem_base + kTcColSHi, t_slo = tmem_base + kTcColSLo, t_vhi = tmem_base + kTcColVHi, t_vlo = tmem_base + kTcColVLo;
+            // descriptors of the B tiles of operand buffer 0; buffer 1 lies kOps bytes (in 16-byte units) further
+            const uint64_t d_wq_hi = umma_desc_k128(smem_u32(smem + SlotTC::kWQ)), d_wq_lo = umma_desc_k128(smem_u32(smem + SlotTC::kWQ + SlotTC::kWQPart));
+            const uint64_t d_ak_hi = umma_desc_k128(smem_u32(smem + SlotTC::kAK)), d_ak_lo = umma_desc_k128(smem_u32(smem + SlotTC::kAK + SlotTC::kAKPart));
+            constexpr uint64_t kBufStep = TcSmem::kOps >> 4, kAtomStep = SlotTC::kAtom128 >> 4, kQgStep = (64 * 128) >> 4, kKdStep = kABytes >> 4;
+            for (uint32_t c = 0; c < n_chunks; ++c) {
+                const uint32_t ph = c & 1u;
+                const uint64_t boff = ph * kBufStep;
+                if (!sync_all(21)) break;                                 // S is in tensor memory
+                if (!mbar_wait(&full[ph], (c >> 1) & 1u, abort_flag, status, 22)) break;
+                loads_waited = c + 1;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int ka = 0; ka < 2; ++ka)                            // S W^T
+                    tc_mma_split<4>(tmem_base + kTcColV, t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep, d_wq_lo + boff + ka * kAtomStep, idesc64,
+                                    ka != 0);
+                umma_commit(m1_done);
+#pragma unroll
+                for (int ka = 0; ka < 2; ++ka)                            // S Qg^T into o buffer ph
+                    tc_mma_split<4>(tmem_base + kTcColO + 64 * ph, t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep + kQgStep,
+                                    d_wq_lo + boff + ka * kAtomStep + kQgStep, idesc64, ka != 0);
+                if (c > 0 && c + 1 < n_chunks) {
+                    // every product of the previous chunk is finished: its operand buffer takes the next chunk's
+                    if (!mbar_wait(o_done, ph ^ 1u, abort_flag, status, 26)) break;
+                    load_ops(c + 1);
+                }
+                if (!sync_all(24)) break;                                 // v' is in tensor memory
+                tc_fence_after_sync();
+                tc_mma_split<4>(tmem_base + kTcColDs, t_vhi, t_vlo, d_ak_hi + boff + kKdStep, d_ak_lo + boff + kKdStep, idesc128, false);
+                umma_commit(ds_done);
+                tc_mma_split<4>(tmem_base + kTcColO + 64 * ph, t_vhi, t_vlo, d_ak_hi + boff, d_ak_lo + boff, idesc64, true);
+                umma_commit(o_done);
+            }
+            if (*abort_flag) {
+                // nothing may still be writing this CTA's shared or tensor memory when it exits
+                for (uint32_t i = loads_waited; i < loads_issued; ++i) mbar_wait(&full[i & 1u], (i >> 1) & 1u, never_flag, status, 31);
+                umma_commit(drain_bar);
+                mbar_wait(drain_bar, 0u, never_flag, status, 32);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ row workers
+        const int q = warp & 3, hh = warp >> 2;
+        const int dv = 32 * q + lane;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(32 * q) << 16);
+        // state row dv, dk half hh
+        float Sreg[64];
+        const size_t sbase = (static_cast<size_t>(seq) * p.nv + h) * D * D + static_cast<size_t>(dv) * D + 64 * hh;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.state_in) v4 = *reinterpret_cast<const float4*>(p.state_in + sbase + 4 * i);
+            Sreg[4 * i] = v4.x; Sreg[4 * i + 1] = v4.y; Sreg[4 * i + 2] = v4.z; Sreg[4 * i + 3] = v4.w;
+        }
+        // the thread's 64 state values as 32 hi and 32 lo columns of TMEM lane dv
+        auto write_s = [&]() {
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                uint32_t hi[16], lo[16];
+                tc_split_pack<16>(Sreg + 32 * part, hi, lo);
+                tmem_st_32x32_x16(tlane + kTcColSHi + 32 * hh + 16 * part, hi);
+                tmem_st_32x32_x16(tlane + kTcColSLo + 32 * hh + 16 * part, lo);
+            }
+            tmem_st_wait();
+        };
+        // o rows j = 32 hh .. + 31 (of `n` valid), column dv, from o buffer `buf`
+        auto store_o = [&](uint32_t buf, size_t row_base, int n) {
+            uint32_t r[32];
+            tmem_ld_32x32(tlane + kTcColO + 64 * buf + 32 * hh, r);
+            tmem_ld_wait();
+            float* op = p.o + ((row_base + 32 * hh) * p.nv + h) * D + dv;
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+                if (32 * hh + e < n) op[static_cast<size_t>(e) * p.nv * D] = __uint_as_float(r[e]);
+        };
+        uint32_t sync_ph = 0;
+        if (n_chunks) write_s();
+#ifdef DC_TC_TIMELINE
+        const int tl_who = (blockIdx.x == 0 && blockIdx.y == 0) ? (tid == 0 ? 0 : (tid == 128 ? 1 : -1)) : -1;
+#endif
+        uint32_t c = 0;
+        for (; c < n_chunks; ++c) {
+            const uint32_t ph = c & 1u;
+            const uint8_t* slot = slot_ptr<3>(p, row_lo, seq, c, h);
+            const bool more = c + 1 < n_chunks;
+
+            // S is in tensor memory; acc_v, acc_ds and o buffer `ph` have been read
+            TL(0);
+            tc_fence_before_sync();
+            if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 21)) break;
+            TL(1);
+            // while S W^T runs: U^T values of this thread (row j = 32 hh + e, column dv), the chunk's decay, o of the previous chunk
+            float u[32];
+            const float* sU = reinterpret_cast<const float*>(slot + SlotTC::kU) + (32 * hh) * D + dv;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) u[e] = sU[e * D];
+            const float dl = *reinterpret_cast<const float*>(slot + SlotTC::kDecay);
+            TL(3);
+            if (c > 0) {
+                if (!mbar_wait(o_done, ph ^ 1u, abort_flag, status, 26)) break;
+                __syncwarp();
+                tc_fence_after_sync();
+                store_o(ph ^ 1u, static_cast<size_t>(row_lo) + (c - 1) * C, C);
+            }
+            TL(4);
+            if (!mbar_wait(m1_done, ph, abort_flag, status, 23)) break;
+            TL(5);
+            __syncwarp();
+            tc_fence_after_sync();
+            {   // v'^T = U^T - S W^T for rows j = 32 hh .. + 31 -> 16 hi and 16 lo columns of lane dv
+                uint32_t r[32];
+                tmem_ld_32x32(tlane + kTcColV + 32 * hh, r);
+                tmem_ld_wait();
+                float x[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) x[e] = u[e] - __uint_as_float(r[e]);
+                uint32_t hi[16], lo[16];
+                tc_split_pack<16>(x, hi, lo);
+                tmem_st_32x32_x16(tlane + kTcColVHi + 16 * hh, hi);
+                tmem_st_32x32_x16(tlane + kTcColVLo + 16 * hh, lo);
+                tmem_st_wait();
+            }
+            TL(6);
+            tc_fence_before_sync();
+            if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 24)) break;
+            TL(7);
+            if (!mbar_wait(ds_done, ph, abort_flag, status, 29)) break;
+            TL(9);
+            __syncwarp();
+            tc_fence_after_sync();
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {   // S <- e^{G_last} S + increment, dk = 64 hh + 32 half ..
+                uint32_t r[32];
+                tmem_ld_32x32(tlane + kTcColDs + 64 * hh + 32 * half, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) Sreg[32 * half + e] = fmaf(dl, Sreg[32 * half + e], __uint_as_float(r[e]));
+            }
+            TL(10);
+            if (more) write_s();
+            TL(11);
+        }
+        if (c == n_chunks && n_chunks) {   // o of the last chunk
+            const uint32_t last = n_chunks - 1;
+            if (mbar_wait(o_done, last & 1u, abort_flag, status, 30)) {
+                __syncwarp();
+                tc_fence_after_sync();
+                store_o(last & 1u, static_cast<size_t>(row_lo) + last * C, static_cast<int>(len - last * C));
+            }
+        }
+        __syncwarp();
+        tmem_ld_wait();
+        if (c == n_chunks && p.write_state) {
+            float* so = p.state_out + sbase;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                *reinterpret_cast<float4*>(so + 4 * i) = make_float4(Sreg[4 * i], Sreg[4 * i + 1], Sreg[4 * i + 2], Sreg[4 * i + 3]);
+        }
+    }
+
+    // ------------------------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after_sync();
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTcTmemCols);
+    }
+}
+#ifdef DC_TC_TIMELINE
+}  // namespace
+extern "C" int dc_debug_tc_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(g_tc_timeline))); }
+namespace {
+#endif
+
 template <int DVB, int SPLIT>
 int launch_apply(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq) {
     constexpr size_t smem = apply_smem<DVB, SPLIT>();
@@ -552,10 +949,27 @@ int launch_apply(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq
     return dc_check_launch(ctx, "gated_delta (chunk apply)");
 }
 
+int launch_chunked_tc(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq, uint32_t max_chunks) {
+    static bool attr_set[16] = {};
+    auto prep = delta_chunk_prepare_kernel<3, true>;
+    auto apply = delta_chunk_apply_tc_kernel;
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(apply, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(TcSmem::kBytes));
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", TcSmem::kBytes, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    prep<<<dim3(max_chunks, a.nv, n_seq), 256, kPrepSmem, s>>>(a);
+    int rc = dc_check_launch(ctx, "gated_delta (chunk prepare)");
+    if (rc != DC_OK) return rc;
+    apply<<<dim3(a.nv, n_seq), kTcThreads, TcSmem::kBytes, s>>>(a, ctx->status_dev);
+    return dc_check_launch(ctx, "gated_delta (chunk apply, tcgen05)");
+}
+
 template <int SPLIT>
 int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq, uint32_t max_chunks) {
     static bool attr_set[16] = {};
-    auto prep = delta_chunk_prepare_kernel<SPLIT>;
+    auto prep = delta_chunk_prepare_kernel<SPLIT, false>;
     if (!attr_set[ctx->device & 15]) {
         cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem));
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", kPrepSmem, cudaGetErrorString(e));
@@ -585,5 +999,6 @@ int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const fl
     if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);
     const uint32_t max_chunks = (max_len + C - 1) / C;
     if (split == 1) return launch_chunked<1>(ctx, s, args, n_seq, max_chunks);
+    if (ctx->delta_engine == DC_DELTA_TCGEN05) return launch_chunked_tc(ctx, s, args, n_seq, max_chunks);
     return launch_chunked<3>(ctx, s, args, n_seq, max_chunks);
 }

@@ -53,6 +53,12 @@ class Act(enum.IntEnum):
     F16 = 1
 
 
+class DeltaEngine(enum.IntEnum):
+    """Serial kernel of the chunked gated delta rule (DC_DELTA_*)."""
+    MmaSync = 0
+    Tcgen05 = 1
+
+
 class ConvertReport(ctypes.Structure):
     """dc_convert_report: the converter's fp16 precision-loss counters (convert.rs:64-71)."""
     _fields_ = [(n, ctypes.c_uint64) for n in ("values", "f16_subnormal", "f16_flushed_to_zero", "f16_overflow")]
@@ -129,6 +135,10 @@ class Device:
     def set_delta_split(self, split: int):
         """Operand precision of the chunked delta rule: 3 = hi/lo split (default), 1 = single bf16 pass."""
         self.call("dc_set_delta_split", split)
+
+    def set_delta_engine(self, engine: "DeltaEngine"):
+        """Tensor-core path of the chunked delta rule's serial kernel (split 3): tcgen05 (default) or mma.sync."""
+        self.call("dc_set_delta_engine", int(engine))
 
     @property
     def act(self) -> Act:

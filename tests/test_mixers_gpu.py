@@ -189,14 +189,18 @@ def test_conv_state_update(k, t):
 
 
 # ----------------------------------------------------------------- delta
-@pytest.fixture(params=["chunked", "sequential"])
+@pytest.fixture(params=["chunked", "chunked-mma", "sequential"])
 def delta_impl(request, k):
-    """Runs a delta-rule test on the chunk-64 tensor-core kernels (fast) and on the sequential kernel (baseline)."""
-    from decide_b200.kernels import Family, Impl
+    """Runs a delta-rule test on the chunk-64 tensor-core kernels (fast; serial kernel on tcgen05 or on
+    mma.sync) and on the sequential kernel (baseline)."""
+    from decide_b200.kernels import DeltaEngine, Family, Impl
 
-    k.dev.set_impl(Family.Delta, Impl.Fast if request.param == "chunked" else Impl.Baseline)
-    yield request.param
+    k.dev.set_impl(Family.Delta, Impl.Baseline if request.param == "sequential" else Impl.Fast)
+    k.dev.set_delta_engine(DeltaEngine.MmaSync if request.param == "chunked-mma" else DeltaEngine.Tcgen05)
+    yield "sequential" if request.param == "sequential" else "chunked"
     k.dev.set_impl(Family.Delta, Impl.Fast)
+    k.dev.set_delta_engine(DeltaEngine.Tcgen05)
+    k.dev.check_status()
 
 
 # fp32 sequential kernel vs the f64-accumulating oracle: ~1e-6; chunked kernel with hi/lo split operands: ~1e-5
