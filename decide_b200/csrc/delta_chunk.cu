@@ -49,7 +49,8 @@ struct Slot {
 // 128-byte rows of 64 elements and the 128-byte swizzle a tensor-map copy would produce (the 16-byte
 // chunk c of row r sits at chunk position c ^ (r & 7)), so tcgen05.mma reads it through a shared-
 // memory descriptor after one flat bulk copy:
-//   WQ  [hi|lo][k-atom 2][128 rows = W rows 0..63, Qg rows 64..127][64]   B operand of S W^T | S Qg^T
+//   WQ  [hi|lo][k-atom 2][128 rows][64]   B operand of S W^T | S Qg^T: W in rows 0..63 and Qg in rows
+//       64..127 for even chunks of a sequence, the other way round for odd chunks
 //   AK  [hi|lo]{ A [64 i][64 j] ; Kd^T [128 dk][64 j] }                   B operands of v'^T A^T and v'^T Kd
 //   U, e^{G_last} as above
 struct SlotTC {
@@ -200,6 +201,12 @@ __device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const flo
 // Kernel 1: one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
 // tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
 // onto L.
+#ifdef DC_TC_TIMELINE
+__device__ long long g_prep_timeline[2 * 16];
+#define TLP(k) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == 128)) g_prep_timeline[(threadIdx.x >> 7) * 16 + (k)] = clock64(); } while (0)
+#else
+#define TLP(k) do { } while (0)
+#endif
 constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 5 * C * 4;
 
 template <int SPLIT, bool TC>
@@ -231,6 +238,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
     const size_t row_base = static_cast<size_t>(row_lo) + r0;
     uint8_t* slot = slot_ptr<SPLIT>(p, row_lo, seq, c, h);
 
+    TLP(15);
     // gates; rows past the sequence end are padding: no decay, no write (g = 0, beta = 0, k = v = q = 0)
     if (tid < C) {
         float g = 0.f, be = 0.f;
@@ -242,12 +250,14 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         Nf[tid] = g;  // staging for the prefix sum
         Bs[tid] = be;
     }
+    TLP(0);
     __syncthreads();
     if (tid < C) {
         float acc = 0.f;
         for (int i = 0; i <= tid; ++i) acc += Nf[i];
         Gs[tid] = acc;
     }
+    TLP(1);
     __syncthreads();
     const float glast = Gs[C - 1];
     if (tid == 0) *reinterpret_cast<float*>(slot + SL::kDecay) = expf(glast);
@@ -261,6 +271,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         Ek[tid] = expf(glast - g);
         Es[tid] = Bs[tid] * expf(g);
     }
+    TLP(2);
     __syncthreads();
 
     {   // K and Q tiles into shared memory; q e^G and k e^{G_last - G} tiles straight to scratch
@@ -282,13 +293,14 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             const float eq = Eq[r], ek = Ek[r];
             const float4 qe = make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq);
             if constexpr (TC) {
-                tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(64 + r, c4), qe);
+                tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>((c & 1u ? 0 : 64) + r, c4), qe);
             } else {
                 gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, qe);
                 gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
             }
         }
     }
+    TLP(3);
     __syncthreads();
     if constexpr (TC) {
         // Kd^T [dk][j] = k_j[dk] e^{G_last - G_j}, token index contiguous: read the K tiles column-wise
@@ -320,6 +332,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         }
     }
 
+    TLP(14);
     const int m0 = 16 * wr;
     {   // k.k^T and q.k^T: 16 rows x 32 columns per warp
         float akk[4][4], aqk[4][4];
@@ -370,6 +383,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             }
         }
     }
+    TLP(4);
     __syncthreads();
     if (warp < 4) {
         // warps 0..3: T = (I + L)^-1, then its bf16 tiles (which reuse L's storage)
@@ -405,6 +419,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             }
         }
     }
+    TLP(5);
     __syncthreads();
 
     // W = T (beta k e^G), U = T (beta v): 16 rows x 64 columns per warp
@@ -436,8 +451,9 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             const int j = 64 * wc + nt * 8 + 2 * (lane & 3);
             if (which == 0) {
                 if constexpr (TC) {
-                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(i0, j), acc[nt][0], acc[nt][1]);
-                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(i1, j), acc[nt][2], acc[nt][3]);
+                    const int wrow = c & 1u ? 64 : 0;
+                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wrow + i0, j), acc[nt][0], acc[nt][1]);
+                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wrow + i1, j), acc[nt][2], acc[nt][3]);
                 } else {
                     gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
                     gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
@@ -449,6 +465,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             }
         }
     }
+    TLP(6);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -655,7 +672,9 @@ struct TcSmem {
 static_assert(SlotTC::kWQ == 0 && SlotTC::kAK == 2 * SlotTC::kWQPart && SlotTC::kU == SlotTC::kAK + 2 * SlotTC::kAKPart, "operands are contiguous");
 constexpr uint32_t kTcTmemCols = 512;
 // accumulator columns (o: + 64 per buffer) and the packed-bf16 A operands (two K elements per column)
-constexpr uint32_t kTcColV = 0, kTcColO = 64, kTcColDs = 192, kTcColSHi = 320, kTcColSLo = 384, kTcColVHi = 448, kTcColVLo = 480;
+// S W^T and S Qg^T come out of ONE N=128 product: its 128 output columns are [acc_v | o buffer 0] for even chunks and
+// [o buffer 1 | acc_v] for odd ones (kernel 1 swaps the row halves of the W|Qg tile accordingly), so acc_v sits between the two.
+constexpr uint32_t kTcColO1 = 0, kTcColV = 64, kTcColO0 = 128, kTcColDs = 192, kTcColSHi = 320, kTcColSLo = 384, kTcColVHi = 448, kTcColVLo = 480;
 constexpr uint32_t kABytes = 64 * 128;   // one (hi or lo) A tile; the Kd^T tile follows it
 
 // Block-wide barrier on an mbarrier with one arrival per warp.
@@ -693,8 +712,8 @@ __device__ __forceinline__ void tc_mma_split(uint32_t d_tmem, uint32_t a_hi, uin
 
 #ifdef DC_TC_TIMELINE
 // Debug build only: cycle stamps of the first chunks of CTA (0, 0), threads 0 and 128.
-__device__ long long g_tc_timeline[2 * 16 * 16];
-#define TL(k) do { if (tl_who >= 0 && c < 16) g_tc_timeline[(c * 2 + tl_who) * 16 + (k)] = clock64(); } while (0)
+__device__ long long g_tc_timeline[3 * 16 * 16];
+#define TL(k) do { if (tl_who >= 0 && c < 16) g_tc_timeline[(c * 3 + tl_who) * 16 + (k)] = clock64(); } while (0)
 #else
 #define TL(k) do { } while (0)
 #endif
@@ -764,34 +783,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             // descriptors of the B tiles of operand buffer 0; buffer 1 lies kOps bytes (in 16-byte units) further
             const uint64_t d_wq_hi = umma_desc_k128(smem_u32(smem + SlotTC::kWQ)), d_wq_lo = umma_desc_k128(smem_u32(smem + SlotTC::kWQ + SlotTC::kWQPart));
             const uint64_t d_ak_hi = umma_desc_k128(smem_u32(smem + SlotTC::kAK)), d_ak_lo = umma_desc_k128(smem_u32(smem + SlotTC::kAK + SlotTC::kAKPart));
-            constexpr uint64_t kBufStep = TcSmem::kOps >> 4, kAtomStep = SlotTC::kAtom128 >> 4, kQgStep = (64 * 128) >> 4, kKdStep = kABytes >> 4;
+            constexpr uint64_t kBufStep = TcSmem::kOps >> 4, kAtomStep = SlotTC::kAtom128 >> 4, kKdStep = kABytes >> 4;
+#ifdef DC_TC_TIMELINE
+            const int tl_who = (blockIdx.x == 0 && blockIdx.y == 0) ? 2 : -1;
+#endif
             for (uint32_t c = 0; c < n_chunks; ++c) {
                 const uint32_t ph = c & 1u;
                 const uint64_t boff = ph * kBufStep;
+                TL(0);
                 if (!sync_all(21)) break;                                 // S is in tensor memory
+                TL(1);
                 if (!mbar_wait(&full[ph], (c >> 1) & 1u, abort_flag, status, 22)) break;
                 loads_waited = c + 1;
                 tc_fence_after_sync();
+                TL(2);
 #pragma unroll
-                for (int ka = 0; ka < 2; ++ka)                            // S W^T
-                    tc_mma_split<4>(tmem_base + kTcColV, t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep, d_wq_lo + boff + ka * kAtomStep, idesc64,
-                                    ka != 0);
+                for (int ka = 0; ka < 2; ++ka)                            // [S W^T | S Qg^T] or [S Qg^T | S W^T]: acc_v and o buffer ph
+                    tc_mma_split<4>(tmem_base + (ph ? kTcColO1 : kTcColV), t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep,
+                                    d_wq_lo + boff + ka * kAtomStep, idesc128, ka != 0);
                 umma_commit(m1_done);
-#pragma unroll
-                for (int ka = 0; ka < 2; ++ka)                            // S Qg^T into o buffer ph
-                    tc_mma_split<4>(tmem_base + kTcColO + 64 * ph, t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep + kQgStep,
-                                    d_wq_lo + boff + ka * kAtomStep + kQgStep, idesc64, ka != 0);
+                TL(3);
                 if (c > 0 && c + 1 < n_chunks) {
                     // every product of the previous chunk is finished: its operand buffer takes the next chunk's
                     if (!mbar_wait(o_done, ph ^ 1u, abort_flag, status, 26)) break;
                     load_ops(c + 1);
                 }
+                TL(4);
                 if (!sync_all(24)) break;                                 // v' is in tensor memory
                 tc_fence_after_sync();
+                TL(5);
                 tc_mma_split<4>(tmem_base + kTcColDs, t_vhi, t_vlo, d_ak_hi + boff + kKdStep, d_ak_lo + boff + kKdStep, idesc128, false);
                 umma_commit(ds_done);
-                tc_mma_split<4>(tmem_base + kTcColO + 64 * ph, t_vhi, t_vlo, d_ak_hi + boff, d_ak_lo + boff, idesc64, true);
+                tc_mma_split<4>(tmem_base + (ph ? kTcColO1 : kTcColO0), t_vhi, t_vlo, d_ak_hi + boff, d_ak_lo + boff, idesc64, true);
                 umma_commit(o_done);
+                TL(6);
             }
             if (*abort_flag) {
                 // nothing may still be writing this CTA's shared or tensor memory when it exits
@@ -828,7 +853,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
         // o rows j = 32 hh .. + 31 (of `n` valid), column dv, from o buffer `buf`
         auto store_o = [&](uint32_t buf, size_t row_base, int n) {
             uint32_t r[32];
-            tmem_ld_32x32(tlane + kTcColO + 64 * buf + 32 * hh, r);
+            tmem_ld_32x32(tlane + (buf ? kTcColO1 : kTcColO0) + 32 * hh, r);
             tmem_ld_wait();
             float* op = p.o + ((row_base + 32 * hh) * p.nv + h) * D + dv;
 #pragma unroll
@@ -836,7 +861,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
                 if (32 * hh + e < n) op[static_cast<size_t>(e) * p.nv * D] = __uint_as_float(r[e]);
         };
         uint32_t sync_ph = 0;
-        if (n_chunks) write_s();
+        // U^T values of this thread for one chunk: rows j = 32 hh + e, column dv. Fetched one chunk ahead.
+        float u[32];
+        auto load_u = [&](uint32_t c) {
+            const float* sU = reinterpret_cast<const float*>(slot_ptr<3>(p, row_lo, seq, c, h) + SlotTC::kU) + (32 * hh) * D + dv;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) u[e] = sU[e * D];
+        };
+        if (n_chunks) {
+            load_u(0);
+            write_s();
+        }
 #ifdef DC_TC_TIMELINE
         const int tl_who = (blockIdx.x == 0 && blockIdx.y == 0) ? (tid == 0 ? 0 : (tid == 128 ? 1 : -1)) : -1;
 #endif
@@ -851,11 +886,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             tc_fence_before_sync();
             if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 21)) break;
             TL(1);
-            // while S W^T runs: U^T values of this thread (row j = 32 hh + e, column dv), the chunk's decay, o of the previous chunk
-            float u[32];
-            const float* sU = reinterpret_cast<const float*>(slot + SlotTC::kU) + (32 * hh) * D + dv;
-#pragma unroll
-            for (int e = 0; e < 32; ++e) u[e] = sU[e * D];
+            // while the first product runs: o of the previous chunk
             const float dl = *reinterpret_cast<const float*>(slot + SlotTC::kDecay);
             TL(3);
             if (c > 0) {
@@ -886,6 +917,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             tc_fence_before_sync();
             if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 24)) break;
             TL(7);
+            if (more) load_u(c + 1);   // lands while the state increment is computed
             if (!mbar_wait(ds_done, ph, abort_flag, status, 29)) break;
             TL(9);
             __syncwarp();
@@ -932,6 +964,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
 #ifdef DC_TC_TIMELINE
 }  // namespace
 extern "C" int dc_debug_tc_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(g_tc_timeline))); }
+extern "C" int dc_debug_prep_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_prep_timeline, sizeof(g_prep_timeline))); }
 namespace {
 #endif
 
