@@ -101,10 +101,10 @@ def conv(k, n_seq, tokens, nk, nv, iters, warmup):
 
 
 def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3, engine="tcgen05"):
-    from .kernels import DeltaEngine, Family, Impl
+    from .kernels import Engine, Family, Impl
     k.dev.set_impl(Family.Delta, Impl.Fast if impl == "fast" else Impl.Baseline)
     k.dev.set_delta_split(split)
-    k.dev.set_delta_engine(DeltaEngine.Tcgen05 if engine == "tcgen05" else DeltaEngine.MmaSync)
+    k.dev.set_engine(Family.Delta, Engine.Tcgen05 if engine == "tcgen05" else Engine.MmaSync)
     rows = n_seq * tokens
     q = torch.nn.functional.normalize(torch.randn(rows, nk, 128, device="cuda"), dim=-1) * 128 ** -0.5
     kk = torch.nn.functional.normalize(torch.randn(rows, nk, 128, device="cuda"), dim=-1)
@@ -118,7 +118,7 @@ def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3, engine=
     us = _time(fn, iters, warmup)
     k.dev.set_impl(Family.Delta, Impl.Fast)
     k.dev.set_delta_split(3)
-    k.dev.set_delta_engine(DeltaEngine.Tcgen05)
+    k.dev.set_engine(Family.Delta, Engine.Tcgen05)
     nbytes = rows * (2 * nk + 2 * nv) * 128 * 4.0
     flops = rows * nv * 128.0 * 128.0 * 7.0  # the sequential recurrence: decay, two dots, rank-1 update per state element
     return {"op": "gated_delta", "impl": impl if impl != "fast" else f"chunked split {split}" + (f" {engine}" if split == 3 else ""), "seqs": n_seq, "tokens": tokens, "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3, "flops": flops, "tflops_fp32": flops / us / 1e6,

@@ -352,6 +352,8 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
                                                  gate, qpos, static_cast<uint16_t*>(y), rows, ldg, nq, nkv, scale, seq_start, n_seq);
         return dc_check_launch(ctx, "attention (baseline)");
     }
+    if (seq_start && ctx->attn_engine == DC_ENGINE_TCGEN05)
+        return dc_attention_tc(ctx, s, q, kc, vc, gate, qpos, y, rows, ldg, nq, nkv, seq_start, n_seq, max_len);
     constexpr size_t smem = 4 * BKV * HD * 2 + BQ * sizeof(int);
     static bool attr_set[16] = {};
     auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;

@@ -1,0 +1,396 @@
+// Causal grouped-query attention on tcgen05 (head_dim 128, packed sequences): the fast path of
+// dc_attention for prefill batches. Same arithmetic contract as the mma.sync kernel of attn.cu
+// (spec cpu_ref.rs:167-188; reference kernels attn_fast.metal:289-411): fp32 scores and online softmax,
+// weights rounded once to the 16-bit operand type with the row sum taken over the ROUNDED weights,
+// optional sigmoid output gate in the store.
+//
+// One CTA per (128 query rows of a sequence, query head), two CTAs per SM. Per tile of 128 cache rows:
+//   S = Q K^T    tcgen05.mma, Q and K as K-major swizzled tiles loaded by TMA, S in tensor memory
+//   softmax      8 warps, one thread per (row, half of the 128 columns): scores out of tensor memory,
+//                mask, running maximum (the two halves of a row meet through shared memory), exp2,
+//                and the 16-bit weights written back INTO the columns the scores came from
+//   O += P V     tcgen05.mma with P as the tensor-memory A operand and V^T (value dim x cache row,
+//                cache rows contiguous) as the K-major B tile
+// V arrives as [cache row][head][128]; a small kernel first transposes it into scratch as
+// [head][128][column], each sequence starting on a column that is a multiple of 8 so that every TMA
+// tile starts on a 16-byte boundary; the gaps between sequences are zero-filled because a zero weight
+// times a stale NaN would still poison the sum.
+// The running maximum is lazy: O and the row sum are rescaled only when the maximum grows by more than
+// 2^8, so most tiles skip the read-modify-write of O in tensor memory; weights stay below 2^8.
+// Warp 8 issues the TMA copies and the MMAs. Every wait is a bounded mbarrier wait; when one gives up
+// the CTA raises the status word, waits for its copies and MMAs in flight, frees its tensor memory and
+// returns.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+using namespace dc;
+
+constexpr int HD = 128;
+constexpr int TQ = 128;    // query rows per CTA
+constexpr int TKV = 128;   // cache rows per tile
+constexpr int kThreads = 288;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColO = 128;
+constexpr float kMasked = -1e30f;
+constexpr float kRescaleStep = 8.0f;   // log2 units
+
+struct Smem {
+    static constexpr size_t kAtom = 128 * 128;          // [128 rows][64 x 16 bit]
+    static constexpr size_t kQ = 0;
+    static constexpr size_t kK = kQ + 2 * kAtom;
+    static constexpr size_t kV = kK + 2 * kAtom;
+    static constexpr size_t kBars = kV + 2 * kAtom;
+    static constexpr size_t kMx = kBars + 128;           // float [2 tiles][2 halves][128 rows]
+    static constexpr size_t kQp = kMx + 2 * 2 * 128 * 4;  // int [128] + the tile's maximum
+    static constexpr size_t kBytes = kQp + 129 * 4 + 12 + 1024;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Barrier between the two warps that share a row quadrant: an mbarrier with one arrival per warp, bounded like every wait here.
+__device__ __forceinline__ bool pair_sync(uint64_t* bar, uint32_t& phase, int lane, volatile uint32_t* abort_flag, int* status) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    const bool ok = mbar_wait(bar, phase, abort_flag, status, 53);
+    phase ^= 1u;
+    return ok;
+}
+
+// Column of the transposed V scratch where sequence `seq` (first row `row_lo`) starts.
+__host__ __device__ __forceinline__ uint32_t vt_col(uint32_t row_lo, uint32_t seq) { return ((row_lo + 7u) & ~7u) + 8u * seq; }
+
+// vt[(head * 128 + d) * ldt + vt_col(seq) + t] = vc[(row_lo + t) * nkv * 128 + head * 128 + d]; columns from the end of a
+// sequence to the start of the next one are zero-filled.
+__global__ void __launch_bounds__(256) v_transpose_kernel(const uint16_t* __restrict__ vc, uint16_t* __restrict__ vt, uint32_t rows, uint32_t nkv,
+                                                          uint32_t ldt, const uint32_t* __restrict__ seq_start, uint32_t n_seq) {
+    __shared__ uint16_t tile[64][HD + 8];
+    const uint32_t seq = blockIdx.z, head = blockIdx.y, t0 = blockIdx.x * 64;
+    const uint32_t row_lo = seq_start[seq], len = seq_start[seq + 1] - row_lo;
+    const uint32_t col0 = vt_col(row_lo, seq);
+    const uint32_t col_end = seq + 1 < n_seq ? vt_col(seq_start[seq + 1], seq + 1) : ldt;   // first column of the next sequence
+    if (col0 + t0 >= col_end) return;
+    for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+        const int r = e >> 4, c8 = (e & 15) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t0 + r < len) v = *reinterpret_cast<const uint4*>(vc + (static_cast<size_t>(row_lo) + t0 + r) * nkv * HD + head * HD + c8);
+        *reinterpret_cast<uint4*>(&tile[r][c8]) = v;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < HD * 8; e += 256) {
+        const int d = e >> 3, c = e & 7;   // 8 columns t0 + 8c .. of output row d
+        if (col0 + t0 + 8 * c >= col_end) continue;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = static_cast<uint32_t>(tile[8 * c + 2 * i][d]) | (static_cast<uint32_t>(tile[8 * c + 2 * i + 1][d]) << 16);
+        *reinterpret_cast<uint4*>(vt + (static_cast<size_t>(head) * HD + d) * ldt + col0 + t0 + 8 * c) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <typename Act>
+__global__ void __launch_bounds__(kThreads, 2)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t ldg, uint32_t nq, uint32_t nkv,
+               float scale_log2, const uint32_t* __restrict__ seq_start, int* __restrict__ status) {
+    const uint32_t seq = blockIdx.z, head = blockIdx.y;
+    const uint32_t row_lo = seq_start[seq], len = seq_start[seq + 1] - row_lo;
+    const uint32_t r0 = blockIdx.x * TQ;
+    if (r0 >= len) return;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sQ = smem + Smem::kQ;
+    uint8_t* sK = smem + Smem::kK;
+    uint8_t* sV = smem + Smem::kV;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
+    uint64_t* q_full = bars + 0;
+    uint64_t* k_full = bars + 1;
+    uint64_t* v_full = bars + 2;
+    uint64_t* s_done = bars + 3;     // S = Q K^T of a tile finished (and every product before it)
+    uint64_t* pv_done = bars + 4;    // O += P V of a tile finished
+    uint64_t* p_ready = bars + 5;    // the 8 softmax warps have written P (and rescaled O)
+    uint64_t* drain_bar = bars + 6;
+    uint64_t* pair_bar = bars + 8;   // [4] the two softmax warps of a row quadrant
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* never_flag = tmem_slot + 2;
+    float* mx = reinterpret_cast<float*>(smem + Smem::kMx);
+    int* qp = reinterpret_cast<int*>(smem + Smem::kQp);
+    int* qp_max = qp + 128;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(v_full, 1);
+        mbar_init(s_done, 1);
+        mbar_init(pv_done, 1);
+        mbar_init(p_ready, 8);
+        mbar_init(drain_bar, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+        *abort_flag = 0u;
+        *never_flag = 0u;
+        *qp_max = -1;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (tid < TQ) {
+        const int p = r0 + tid < len ? static_cast<int>(qpos[row_lo + r0 + tid]) : -1;
+        qp[tid] = p;
+        int m = p;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) atomicMax(qp_max, m);
+    }
+    __syncthreads();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t n_tiles = static_cast<uint32_t>(*qp_max + TKV) / TKV;   // cache rows 0..=max qpos; 0 only if no row is valid
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ issuer (one thread)
+        if (lane == 0 && n_tiles) {
+            const uint32_t hk = head / (nq / nkv);
+            const int32_t vcol0 = static_cast<int32_t>(vt_col(row_lo, seq));
+            uint32_t k_issued = 0, k_waited = 0, v_issued = 0, v_waited = 0;
+            bool q_pending = true;
+            auto load_k = [&](uint32_t j) {
+                mbar_arrive_expect_tx(k_full, 2 * Smem::kAtom);
+                tma_load_2d(sK, &tm_k, k_full, static_cast<int32_t>(hk * HD), static_cast<int32_t>(row_lo + j * TKV));
+                tma_load_2d(sK + Smem::kAtom, &tm_k, k_full, static_cast<int32_t>(hk * HD + 64), static_cast<int32_t>(row_lo + j * TKV));
+                k_issued = j + 1;
+            };
+            auto load_v = [&](uint32_t j) {
+                mbar_arrive_expect_tx(v_full, 2 * Smem::kAtom);
+                tma_load_2d(sV, &tm_v, v_full, vcol0 + static_cast<int32_t>(j * TKV), static_cast<int32_t>(hk * HD));
+                tma_load_2d(sV + Smem::kAtom, &tm_v, v_full, vcol0 + static_cast<int32_t>(j * TKV + 64), static_cast<int32_t>(hk * HD));
+                v_issued = j + 1;
+            };
+            mbar_arrive_expect_tx(q_full, 2 * Smem::kAtom);
+            tma_load_2d(sQ, &tm_q, q_full, static_cast<int32_t>(head * HD), static_cast<int32_t>(row_lo + r0));
+            tma_load_2d(sQ + Smem::kAtom, &tm_q, q_full, static_cast<int32_t>(head * HD + 64), static_cast<int32_t>(row_lo + r0));
+            load_k(0);
+            load_v(0);
+            constexpr uint32_t idesc = umma_idesc(Act::kUmmaFormat, Act::kUmmaFormat, TQ, TKV);
+            const uint64_t dq = umma_desc_k128(smem_u32(sQ)), dk = umma_desc_k128(smem_u32(sK)), dvt = umma_desc_k128(smem_u32(sV));
+            constexpr uint64_t kAtomStep = Smem::kAtom >> 4;
+            bool ok = mbar_wait(q_full, 0u, abort_flag, status, 41);
+            q_pending = !ok;
+            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                const uint32_t ph = j & 1u;
+                if (!(ok = mbar_wait(k_full, ph, abort_flag, status, 42))) break;
+                k_waited = j + 1;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint64_t off = (ks >> 2) * kAtomStep + 2 * (ks & 3);
+                    umma_bf16_ss(tmem_base + kColS, dq + off, dk + off, idesc, ks ? 1u : 0u);
+                }
+                umma_commit(s_done);
+                if (!(ok = mbar_wait(s_done, ph, abort_flag, status, 43))) break;
+                if (j + 1 < n_tiles) load_k(j + 1);
+                if (!(ok = mbar_wait(p_ready, ph, abort_flag, status, 44))) break;
+                if (!(ok = mbar_wait(v_full, ph, abort_flag, status, 45))) break;
+                v_waited = j + 1;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    // P of cache rows 16 ks .. sits in 8 columns of the half of S it was computed from
+                    const uint32_t pcol = tmem_base + kColS + (ks >> 2) * 64 + 8 * (ks & 3);
+                    const uint64_t off = (ks >> 2) * kAtomStep + 2 * (ks & 3);
+                    if (j == 0 && ks == 0) umma_bf16_ts<false>(tmem_base + kColO, pcol, dvt + off, idesc);
+                    else umma_bf16_ts<true>(tmem_base + kColO, pcol, dvt + off, idesc);
+                }
+                umma_commit(pv_done);
+                if (!(ok = mbar_wait(pv_done, ph, abort_flag, status, 46))) break;
+                if (j + 1 < n_tiles) load_v(j + 1);
+            }
+            if (*abort_flag) {
+                // nothing may still be writing this CTA's shared or tensor memory when it exits
+                if (q_pending) mbar_wait(q_full, 0u, never_flag, status, 47);
+                for (uint32_t i = k_waited; i < k_issued; ++i) mbar_wait(k_full, i & 1u, never_flag, status, 47);
+                for (uint32_t i = v_waited; i < v_issued; ++i) mbar_wait(v_full, i & 1u, never_flag, status, 47);
+                umma_commit(drain_bar);
+                mbar_wait(drain_bar, 0u, never_flag, status, 48);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax warps
+        const int q = warp & 3, hh = warp >> 2;
+        const int row = 32 * q + lane;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(32 * q) << 16);
+        const int qp_r = qp[row];
+        float m_used = kMasked, l = 0.f;
+        uint32_t pair_ph = 0;
+        uint32_t j = 0;
+        for (; j < n_tiles; ++j) {
+            const uint32_t ph = j & 1u;
+            if (!mbar_wait(s_done, ph, abort_flag, status, 51)) break;
+            __syncwarp();
+            tc_fence_after_sync();
+            float t[64];
+            {
+                uint32_t r[32];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld_32x32(tlane + kColS + 64 * hh + 32 * half, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) t[32 * half + e] = __uint_as_float(r[e]) * scale_log2;
+                }
+            }
+            const int kv0 = static_cast<int>(j * TKV) + 64 * hh;
+            const int visible = qp_r - kv0 + 1;    // columns e < visible may be attended
+            float lm = kMasked;
+            if (visible >= 64) {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) lm = fmaxf(lm, t[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 64; ++e) {
+                    t[e] = e < visible ? t[e] : kMasked;
+                    lm = fmaxf(lm, t[e]);
+                }
+            }
+            float* mxj = mx + ph * 256;
+            mxj[hh * 128 + row] = lm;
+            if (!pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status)) break;
+            const float m_tile = fmaxf(mxj[row], mxj[128 + row]);
+            const bool grow = m_tile - m_used > kRescaleStep;
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                // O and the row sum follow the new maximum (lanes whose maximum stays put scale by 1)
+                const float alpha = grow ? ex2(m_used - m_tile) : 1.0f;
+                l *= alpha;
+#pragma unroll
+                for (int part = 0; part < 4; ++part) {   // 16 columns at a time: load, scale, store
+                    uint32_t r[16];
+                    tmem_ld_32x32_x16(tlane + kColO + 64 * hh + 16 * part, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+                    tmem_st_32x32_x16(tlane + kColO + 64 * hh + 16 * part, r);
+                }
+                tmem_st_wait();
+            }
+            if (grow) m_used = m_tile;
+            // weights, rounded to the operand type; the row sum is taken over the rounded values
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = t[2 * i] > 0.5f * kMasked ? ex2(t[2 * i] - m_used) : 0.f;
+                const float p1 = t[2 * i + 1] > 0.5f * kMasked ? ex2(t[2 * i + 1] - m_used) : 0.f;
+                pk[i] = Act::pack(p0, p1);
+                l += Act::lo(pk[i]) + Act::hi(pk[i]);
+            }
+            {
+                uint32_t a[16], b[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    a[i] = pk[i];
+                    b[i] = pk[16 + i];
+                }
+                tmem_st_32x32_x16(tlane + kColS + 64 * hh, a);
+                tmem_st_32x32_x16(tlane + kColS + 64 * hh + 16, b);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+        }
+        if (j == n_tiles && n_tiles) {
+            if (mbar_wait(pv_done, (n_tiles - 1) & 1u, abort_flag, status, 52)) {
+                __syncwarp();
+                tc_fence_after_sync();
+                // the two halves of a row add their sums
+                float* ls = mx + ((n_tiles & 1u) ? 256 : 0);   // the half of the exchange buffer the last tile did not use
+                ls[hh * 128 + row] = l;
+                const bool ok = pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status);
+                const float l_tot = ok ? ls[row] + ls[128 + row] : 0.f;
+                const bool valid = qp_r >= 0 && l_tot > 0.f;
+                const float inv = valid ? 1.0f / l_tot : 0.f;
+                const size_t grow_ = static_cast<size_t>(row_lo) + r0 + row;
+                uint16_t* yp = y + grow_ * nq * HD + head * HD + 64 * hh;
+                const float* gp = gate ? gate + grow_ * ldg + head * HD + 64 * hh : nullptr;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tlane + kColO + 64 * hh + 32 * half, r);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float o[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[8 * c + e]) * inv;
+                            if (gp) {
+                                const float4 g0 = *reinterpret_cast<const float4*>(gp + 32 * half + 8 * c);
+                                const float4 g1 = *reinterpret_cast<const float4*>(gp + 32 * half + 8 * c + 4);
+                                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) o[e] *= 1.0f / (1.0f + __expf(-g[e]));
+                            }
+                            *reinterpret_cast<uint4*>(yp + 32 * half + 8 * c) =
+                                make_uint4(Act::pack(o[0], o[1]), Act::pack(o[2], o[3]), Act::pack(o[4], o[5]), Act::pack(o[6], o[7]));
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        tmem_ld_wait();
+    }
+
+    // ------------------------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after_sync();
+        __syncwarp();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace
+
+// Scratch the tcgen05 attention path needs for the transposed V of `rows` packed cache rows.
+size_t dc_attention_tc_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv) {
+    const size_t ldt = ((static_cast<size_t>(rows) + 7) & ~static_cast<size_t>(7)) + 8 * static_cast<size_t>(n_seq);
+    return static_cast<size_t>(nkv) * HD * ldt * 2;
+}
+
+int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,
+                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    const uint32_t ldt = ((rows + 7u) & ~7u) + 8u * n_seq;
+    uint16_t* vt = static_cast<uint16_t*>(dc_workspace(ctx, dc_attention_tc_scratch_bytes(rows, n_seq, nkv)));
+    if (!vt) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot get %zu bytes of scratch", dc_attention_tc_scratch_bytes(rows, n_seq, nkv));
+    CUtensorMap tq, tk, tv;
+    int rc = dc_make_tmap(ctx, q, rows, nq * HD, nq * HD, TQ, f16, &tq);
+    if (rc == DC_OK) rc = dc_make_tmap(ctx, kc, rows, nkv * HD, nkv * HD, TKV, f16, &tk);
+    if (rc == DC_OK) rc = dc_make_tmap(ctx, vt, nkv * HD, ldt, ldt, HD, f16, &tv);
+    if (rc != DC_OK) return rc;
+    v_transpose_kernel<<<dim3((max_len + 16 + 63) / 64, nkv, n_seq), 256, 0, s>>>(static_cast<const uint16_t*>(vc), vt, rows, nkv, ldt, seq_start, n_seq);
+    rc = dc_check_launch(ctx, "attention (V transpose)");
+    if (rc != DC_OK) return rc;
+    static bool attr_set[16] = {};
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<ActF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Smem::kBytes));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_tc_kernel<ActBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Smem::kBytes));
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot opt in to %zu bytes of shared memory: %s", Smem::kBytes, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
+    const dim3 grid((max_len + TQ - 1) / TQ, nq, n_seq);
+    auto kern = f16 ? attn_tc_kernel<ActF16> : attn_tc_kernel<ActBF16>;
+    kern<<<grid, kThreads, Smem::kBytes, s>>>(tq, tk, tv, gate, qpos, static_cast<uint16_t*>(y), ldg, nq, nkv, scale_log2, seq_start, ctx->status_dev);
+    return dc_check_launch(ctx, "attention (tcgen05)");
+}

@@ -36,7 +36,8 @@ struct dc_ctx {
     uint32_t gemm_impl = DC_IMPL_FAST;
     uint32_t attn_impl = DC_IMPL_FAST;
     uint32_t delta_impl = DC_IMPL_FAST;
-    uint32_t delta_engine = DC_DELTA_TCGEN05;  // serial kernel of the chunked delta rule (split 3)
+    uint32_t delta_engine = DC_ENGINE_TCGEN05;  // serial kernel of the chunked delta rule (split 3)
+    uint32_t attn_engine = DC_ENGINE_TCGEN05;   // fast attention for packed batches
     uint32_t delta_split = 3;         // chunked delta rule: 3 = hi/lo split operands (near fp32), 1 = single bf16 pass
     uint32_t act_dtype = DC_ACT_F16;  // type of every 16-bit GEMM operand: activations and weight matrices
     float* gemm_part_ws = nullptr;   // partial accumulators of K-split tail tiles: sm_count x 128 x 256 fp32
@@ -50,6 +51,13 @@ int dc_check_launch(dc_ctx* ctx, const char* what);
 // Returns a workspace of at least `bytes` (growing it is an allocation: callers that
 // must not allocate during a timed forward reserve it up front with dc_reserve_workspace).
 void* dc_workspace(dc_ctx* ctx, size_t bytes);
+// Cached 2-D tensor map over a 16-bit row-major matrix [rows][cols] (row stride ld elements): boxes of
+// box_rows x 64 elements, 128-byte swizzle, zero fill outside the matrix.
+int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16, CUtensorMap* out);
+// tcgen05 attention for packed prefill batches (attn_tc.cu) and the scratch it takes from the workspace.
+int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,
+                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
+size_t dc_attention_tc_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv);
 
 #define DC_REQUIRE(ctx, cond, ...)                                            \
     do {                                                                      \

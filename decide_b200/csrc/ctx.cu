@@ -85,9 +85,12 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         else if (strcmp(d, "3") == 0 || !*d) ctx->delta_split = 3;
         else bad = true;
     }
-    if (const char* d = getenv("DECIDE_DELTA_ENGINE")) {
-        if (strcmp(d, "mma") == 0) ctx->delta_engine = DC_DELTA_MMA_SYNC;
-        else if (strcmp(d, "tcgen05") == 0 || !*d) ctx->delta_engine = DC_DELTA_TCGEN05;
+    for (int f = 0; f < 2; ++f) {
+        const char* d = getenv(f ? "DECIDE_ATTN_ENGINE" : "DECIDE_DELTA_ENGINE");
+        if (!d) continue;
+        uint32_t& engine = f ? ctx->attn_engine : ctx->delta_engine;
+        if (strcmp(d, "mma") == 0) engine = DC_ENGINE_MMA_SYNC;
+        else if (strcmp(d, "tcgen05") == 0 || !*d) engine = DC_ENGINE_TCGEN05;
         else bad = true;
     }
     if (const char* a = getenv("DECIDE_ACT")) {
@@ -96,7 +99,7 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         else bad = true;
     }
     if (bad) {
-        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`, DECIDE_ACT `f16` or `bf16`, DECIDE_DELTA_SPLIT 1 or 3, DECIDE_DELTA_ENGINE `tcgen05` or `mma`", nullptr);
+        say("dc_open: DECIDE_GEMM / DECIDE_ATTN / DECIDE_DELTA must be `fast` or `baseline`, DECIDE_ACT `f16` or `bf16`, DECIDE_DELTA_SPLIT 1 or 3, DECIDE_ATTN_ENGINE / DECIDE_DELTA_ENGINE `tcgen05` or `mma`", nullptr);
         delete ctx;
         return nullptr;
     }
@@ -186,10 +189,17 @@ int dc_set_delta_split(dc_ctx* ctx, uint32_t split) {
     return DC_OK;
 }
 
-int dc_set_delta_engine(dc_ctx* ctx, uint32_t engine) {
+int dc_set_engine(dc_ctx* ctx, uint32_t family, uint32_t engine) {
     if (!ctx) return DC_INVALID_ARG;
-    DC_REQUIRE(ctx, engine == DC_DELTA_MMA_SYNC || engine == DC_DELTA_TCGEN05, "dc_set_delta_engine: unknown engine %u", engine);
-    ctx->delta_engine = engine;
+    DC_REQUIRE(ctx, engine == DC_ENGINE_MMA_SYNC || engine == DC_ENGINE_TCGEN05, "dc_set_engine: unknown engine %u", engine);
+    switch (family) {
+        case DC_FAMILY_ATTN: ctx->attn_engine = engine; break;
+        case DC_FAMILY_DELTA: ctx->delta_engine = engine; break;
+        case DC_FAMILY_GEMM:
+            DC_REQUIRE(ctx, engine == DC_ENGINE_TCGEN05, "dc_set_engine: the GEMM has no mma.sync engine (its baseline is DC_IMPL_BASELINE)");
+            break;
+        default: return dc_fail(ctx, DC_INVALID_ARG, "dc_set_engine: unknown family %u", family);
+    }
     return DC_OK;
 }
 

@@ -1032,6 +1032,6 @@ int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const fl
     if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);
     const uint32_t max_chunks = (max_len + C - 1) / C;
     if (split == 1) return launch_chunked<1>(ctx, s, args, n_seq, max_chunks);
-    if (ctx->delta_engine == DC_DELTA_TCGEN05) return launch_chunked_tc(ctx, s, args, n_seq, max_chunks);
+    if (ctx->delta_engine == DC_ENGINE_TCGEN05) return launch_chunked_tc(ctx, s, args, n_seq, max_chunks);
     return launch_chunked<3>(ctx, s, args, n_seq, max_chunks);
 }

@@ -236,11 +236,11 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         *wnt.ptr = m->arena + off;
         off += align_up(wnt.bytes, 1024);
     }
-    // scratch of the chunked delta rule for the largest batch, so that no forward allocates
-    if (!dc_workspace(ctx, dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv))) {
+    // scratch of the chunked delta rule and of the attention's transposed V for the largest batch, so that no forward allocates
+    if (!dc_workspace(ctx, std::max(dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv), dc_attention_tc_scratch_bytes(max_rows, max_seqs, d.nkv)))) {
         cudaFree(m->arena);
         delete m;
-        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate the delta-rule scratch");
+        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate the scratch workspace");
         return nullptr;
     }
     // RoPE inverse frequencies in fp32, as the reference and HF compute them (config.rs:44-46)

@@ -476,6 +476,10 @@ int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CU
 
 }  // namespace
 
+int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16, CUtensorMap* out) {
+    return make_tmap(ctx, base, rows, cols, ld, box_rows, f16, out);
+}
+
 // Tile plan: the analogue of gemm_configs::plan (crates/decide-metal/src/gemm_configs.rs:312).
 // Whole waves of 128 x BN tiles run as whole tiles; the tiles of the last, partial wave are cut along
 // K into up to 4 parts so that wave fills the SMs as well. BN = 256 unless the narrower tile is

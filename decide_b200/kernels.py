@@ -53,8 +53,8 @@ class Act(enum.IntEnum):
     F16 = 1
 
 
-class DeltaEngine(enum.IntEnum):
-    """Serial kernel of the chunked gated delta rule (DC_DELTA_*)."""
+class Engine(enum.IntEnum):
+    """Tensor-core engine of a family's fast kernels (DC_ENGINE_*)."""
     MmaSync = 0
     Tcgen05 = 1
 
@@ -136,9 +136,9 @@ class Device:
         """Operand precision of the chunked delta rule: 3 = hi/lo split (default), 1 = single bf16 pass."""
         self.call("dc_set_delta_split", split)
 
-    def set_delta_engine(self, engine: "DeltaEngine"):
-        """Tensor-core path of the chunked delta rule's serial kernel (split 3): tcgen05 (default) or mma.sync."""
-        self.call("dc_set_delta_engine", int(engine))
+    def set_engine(self, family: Family, engine: "Engine"):
+        """Tensor-core engine of the family's fast kernels (attention, delta rule): tcgen05 (default) or mma.sync."""
+        self.call("dc_set_engine", int(family), int(engine))
 
     @property
     def act(self) -> Act:

@@ -62,8 +62,8 @@ enum { DC_FAMILY_GEMM = 0, DC_FAMILY_ATTN = 1, DC_FAMILY_DELTA = 2 };
  * converts bf16 weights. Wherever this header says "bf16" for a GEMM operand or an activation
  * buffer, read "the context's 16-bit type". The tensor cores cannot mix the two in one MMA. */
 enum { DC_ACT_BF16 = 0, DC_ACT_F16 = 1 };
-/* Engines of the chunked delta rule's serial kernel: see dc_set_delta_engine. */
-enum { DC_DELTA_MMA_SYNC = 0, DC_DELTA_TCGEN05 = 1 };
+/* Tensor-core engines of the fast attention and delta-rule kernels: see dc_set_engine. */
+enum { DC_ENGINE_MMA_SYNC = 0, DC_ENGINE_TCGEN05 = 1 };
 
 /* ---- context: replaces DecideDevice::shared + Kernels::new (device.rs:125-130, mod.rs:54-66) ---- */
 dc_ctx* dc_open(int device, char* err, size_t err_len);
@@ -81,11 +81,15 @@ uint32_t dc_get_activation_dtype(dc_ctx* ctx);
  * DECIDE_DELTA_SPLIT=3) takes every fp32 operand as hi + lo bf16 parts, 3 MMAs per product, ~1e-5
  * relative error against fp32; 1 is a single bf16 pass, 3x fewer MMAs, ~3e-3 relative error in o. */
 int dc_set_delta_split(dc_ctx* ctx, uint32_t split);
-/* Tensor-core path of the chunked delta rule's serial kernel (split 3 only; split 1 always runs on
- * mma.sync): DC_DELTA_TCGEN05 (default; also DECIDE_DELTA_ENGINE=tcgen05) keeps the accumulators in
- * tensor memory, one CTA per (sequence, head); DC_DELTA_MMA_SYNC (DECIDE_DELTA_ENGINE=mma) is the
- * register-accumulator form, which also splits the value columns over CTAs. Same results to ~1e-6. */
-int dc_set_delta_engine(dc_ctx* ctx, uint32_t engine);
+/* Tensor-core engine of a family's FAST kernels: DC_ENGINE_TCGEN05 (default) or DC_ENGINE_MMA_SYNC, the
+ * register-accumulator forms on mma.sync. At open: DECIDE_ATTN_ENGINE / DECIDE_DELTA_ENGINE = tcgen05 | mma.
+ *  DC_FAMILY_DELTA: the serial kernel of the chunked delta rule with split 3 (split 1 always runs on
+ *    mma.sync); tcgen05 keeps the accumulators in tensor memory, one CTA per (sequence, head); mma.sync
+ *    also splits the value columns over CTAs. Same results to ~1e-6.
+ *  DC_FAMILY_ATTN: tcgen05 serves packed batches (seq_start given); calls without seq_start always run on
+ *    mma.sync. Same contract; results differ by fp32 rounding order only.
+ *  DC_FAMILY_GEMM has one engine (tcgen05). */
+int dc_set_engine(dc_ctx* ctx, uint32_t family, uint32_t engine);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
  * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
 int dc_check_status(dc_ctx* ctx, void* stream);

@@ -113,31 +113,54 @@ def test_attention_scattered_query_positions(k):
     assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
 
 
-@pytest.mark.parametrize("impl", ["fast", "baseline"])
-def test_attention_packed_sequences(k, impl):
-    from decide_b200.kernels import Family, Impl
+@pytest.fixture(params=["fast", "fast-mma", "baseline"])
+def attn_impl(request, k):
+    """Packed-batch attention on the tcgen05 kernel (fast), the mma.sync flash kernel (fast-mma) and the warp-per-row baseline."""
+    from decide_b200.kernels import Engine, Family, Impl
 
-    nq, nkv, hd = 8, 2, 128
-    lens = [70, 1, 130, 64]
+    k.dev.set_impl(Family.Attn, Impl.Baseline if request.param == "baseline" else Impl.Fast)
+    k.dev.set_engine(Family.Attn, Engine.MmaSync if request.param == "fast-mma" else Engine.Tcgen05)
+    yield request.param
+    k.dev.set_impl(Family.Attn, Impl.Fast)
+    k.dev.set_engine(Family.Attn, Engine.Tcgen05)
+    k.dev.check_status()
+
+
+def _packed_attention(k, seed, lens, nq, nkv, gated=True, k_growth=0.0):
+    hd = 128
     starts = np.concatenate([[0], np.cumsum(lens)])
     total = int(starts[-1])
-    q = randn(50, total, nq, hd).to(k.dev.act_torch)
-    kc = randn(51, total, nkv, hd).to(k.dev.act_torch)
-    vc = randn(52, total, nkv, hd).to(k.dev.act_torch)
-    gate = randn(53, total, nq * hd)
+    q = randn(seed, total, nq, hd).to(k.dev.act_torch)
+    kc = randn(seed + 1, total, nkv, hd)
+    if k_growth:   # later cache rows score higher and higher: the running maximum keeps growing
+        kc = kc * (1.0 + k_growth * torch.arange(total).float())[:, None, None]
+    kc = kc.to(k.dev.act_torch)
+    vc = randn(seed + 2, total, nkv, hd).to(k.dev.act_torch)
+    gate = randn(seed + 3, total, nq * hd) if gated else None
     qpos = np.concatenate([np.arange(n) for n in lens])
     y = torch.empty(total, nq * hd, dtype=k.dev.act_torch, device="cuda")
-    k.dev.set_impl(Family.Attn, Impl.Baseline if impl == "baseline" else Impl.Fast)
-    try:
-        k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda(), _u32(qpos), y, total, nq * hd, nq, nkv, hd,
-                         seq_start=_u32(starts), n_seq=len(lens), max_len=max(lens))
-    finally:
-        k.dev.set_impl(Family.Attn, Impl.Fast)
+    k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda() if gated else None, _u32(qpos), y, total, nq * hd if gated else 0, nq, nkv, hd,
+                     seq_start=_u32(starts), n_seq=len(lens), max_len=max(lens))
+    k.dev.check_status()
     got = np32(y)
     for s, n in enumerate(lens):
         a, b = starts[s], starts[s + 1]
-        want = cpu_ref.attention(np32(q)[a:b], np.arange(n), np32(kc)[a:b], np32(vc)[a:b], np32(gate)[a:b], nq, nkv, hd)
-        assert_close(got[a:b], want, atol=6e-3, rtol=2 ** -7, what=f"packed attention seq {s}")
+        want = cpu_ref.attention(np32(q)[a:b], np.arange(n), np32(kc)[a:b], np32(vc)[a:b], np32(gate)[a:b] if gated else None, nq, nkv, hd)
+        assert_close(got[a:b], want, atol=6e-3, rtol=2 ** -7, what=f"packed attention seq {s} (len {n})")
+
+
+def test_attention_packed_sequences(k, attn_impl):
+    _packed_attention(k, 50, [70, 1, 130, 64], 8, 2)
+
+
+def test_attention_packed_long_and_ragged(k, attn_impl):
+    """Several 128-row tiles per sequence, sequence starts that are not multiples of 8, an un-gated call."""
+    _packed_attention(k, 60, [603, 3, 257, 128, 129, 5], 4, 1, gated=False)
+
+
+def test_attention_packed_growing_scores(k, attn_impl):
+    """Scores that grow along the cache force the running maximum (and the rescaling of the output accumulator) to move in every tile."""
+    _packed_attention(k, 70, [400, 300], 4, 2, k_growth=0.02)
 
 
 # ------------------------------------------------------------------ conv
@@ -193,13 +216,13 @@ def test_conv_state_update(k, t):
 def delta_impl(request, k):
     """Runs a delta-rule test on the chunk-64 tensor-core kernels (fast; serial kernel on tcgen05 or on
     mma.sync) and on the sequential kernel (baseline)."""
-    from decide_b200.kernels import DeltaEngine, Family, Impl
+    from decide_b200.kernels import Engine, Family, Impl
 
     k.dev.set_impl(Family.Delta, Impl.Baseline if request.param == "sequential" else Impl.Fast)
-    k.dev.set_delta_engine(DeltaEngine.MmaSync if request.param == "chunked-mma" else DeltaEngine.Tcgen05)
+    k.dev.set_engine(Family.Delta, Engine.MmaSync if request.param == "chunked-mma" else Engine.Tcgen05)
     yield "sequential" if request.param == "sequential" else "chunked"
     k.dev.set_impl(Family.Delta, Impl.Fast)
-    k.dev.set_delta_engine(DeltaEngine.Tcgen05)
+    k.dev.set_engine(Family.Delta, Engine.Tcgen05)
     k.dev.check_status()
 
 
