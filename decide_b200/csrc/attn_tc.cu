@@ -1,8 +1,9 @@
 // Causal grouped-query attention on tcgen05 (head_dim 128, packed sequences): the fast path of
 // dc_attention for prefill batches. Same arithmetic contract as the mma.sync kernel of attn.cu
 // (spec cpu_ref.rs:167-188; reference kernels attn_fast.metal:289-411): fp32 scores and online softmax,
-// weights rounded once to the 16-bit operand type with the row sum taken over the ROUNDED weights,
-// optional sigmoid output gate in the store.
+// weights rounded once to the 16-bit operand type, optional sigmoid output gate in the store. The row
+// sum is taken in fp32 BEFORE that rounding (the mma.sync kernel sums the rounded weights; the two
+// differ by about 2^-12 of the sum, far inside the operand type's own rounding).
 //
 // One CTA per (128 query rows of a sequence, query head), two CTAs per SM. Per tile of 128 cache rows:
 //   S = Q K^T    tcgen05.mma, Q and K as K-major swizzled tiles loaded by TMA, S in tensor memory
@@ -91,6 +92,16 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const uint16_t* __rest
     }
 }
 
+#ifdef DC_TC_TIMELINE
+// Debug build only: cycle stamps of the first tiles of one CTA (issuer, softmax threads 0 and 128).
+__device__ long long g_attn_timeline[3 * 16 * 16];
+#define TLA(who, k) do { if (tl_on && j < 15) g_attn_timeline[(j * 3 + (who)) * 16 + (k)] = clock64(); } while (0)
+#define TLB(who, k) do { if (tl_on) g_attn_timeline[(15 * 3 + (who)) * 16 + (k)] = clock64(); } while (0)
+#else
+#define TLA(who, k) do { } while (0)
+#define TLB(who, k) do { } while (0)
+#endif
+
 template <typename Act>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -115,7 +126,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint64_t* p_ready = bars + 5;    // the 8 softmax warps have written P (and rescaled O)
     uint64_t* drain_bar = bars + 6;
     uint64_t* pair_bar = bars + 8;   // [4] the two softmax warps of a row quadrant
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    uint64_t* gate_bar = bars + 12;  // the 8 softmax warps have staged the gate tile
+    uint64_t* out_bar = bars + 13;   // the 8 softmax warps have staged the output tile
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* never_flag = tmem_slot + 2;
     float* mx = reinterpret_cast<float*>(smem + Smem::kMx);
@@ -123,6 +136,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     int* qp_max = qp + 128;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef DC_TC_TIMELINE
+    const bool tl_on = blockIdx.x == 4 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || tid == 256);
+#endif
+    TLB(tid >> 7, 0);
     if (tid == 0) {
         mbar_init(q_full, 1);
         mbar_init(k_full, 1);
@@ -132,18 +149,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_init(p_ready, 8);
         mbar_init(drain_bar, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 2);
+        mbar_init(gate_bar, 8);
+        mbar_init(out_bar, 8);
         *abort_flag = 0u;
         *never_flag = 0u;
         *qp_max = -1;
         fence_mbar_init();
     }
     if (warp == 8) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+        }
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    TLB(tid >> 7, 1);
     if (tid < TQ) {
         const int p = r0 + tid < len ? static_cast<int>(qpos[row_lo + r0 + tid]) : -1;
         qp[tid] = p;
@@ -153,6 +178,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (lane == 0) atomicMax(qp_max, m);
     }
     __syncthreads();
+    TLB(tid >> 7, 2);
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t n_tiles = static_cast<uint32_t>(*qp_max + TKV) / TKV;   // cache rows 0..=max qpos; 0 only if no row is valid
 
@@ -185,21 +211,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             constexpr uint64_t kAtomStep = Smem::kAtom >> 4;
             bool ok = mbar_wait(q_full, 0u, abort_flag, status, 41);
             q_pending = !ok;
+            TLB(2, 3);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 const uint32_t ph = j & 1u;
+                TLA(2, 0);
                 if (!(ok = mbar_wait(k_full, ph, abort_flag, status, 42))) break;
+                TLA(2, 1);
                 k_waited = j + 1;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint64_t off = (ks >> 2) * kAtomStep + 2 * (ks & 3);
-                    umma_bf16_ss(tmem_base + kColS, dq + off, dk + off, idesc, ks ? 1u : 0u);
+                    if (ks == 0) umma_bf16_ss<false>(tmem_base + kColS, dq + off, dk + off, idesc);
+                    else umma_bf16_ss<true>(tmem_base + kColS, dq + off, dk + off, idesc);
                 }
                 umma_commit(s_done);
+                TLA(2, 2);
                 if (!(ok = mbar_wait(s_done, ph, abort_flag, status, 43))) break;
+                TLA(2, 3);
                 if (j + 1 < n_tiles) load_k(j + 1);
                 if (!(ok = mbar_wait(p_ready, ph, abort_flag, status, 44))) break;
+                TLA(2, 4);
                 if (!(ok = mbar_wait(v_full, ph, abort_flag, status, 45))) break;
+                TLA(2, 5);
                 v_waited = j + 1;
                 tc_fence_after_sync();
 #pragma unroll
@@ -211,7 +245,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     else umma_bf16_ts<true>(tmem_base + kColO, pcol, dvt + off, idesc);
                 }
                 umma_commit(pv_done);
+                TLA(2, 6);
                 if (!(ok = mbar_wait(pv_done, ph, abort_flag, status, 46))) break;
+                TLA(2, 7);
                 if (j + 1 < n_tiles) load_v(j + 1);
             }
             if (*abort_flag) {
@@ -234,9 +270,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         uint32_t j = 0;
         for (; j < n_tiles; ++j) {
             const uint32_t ph = j & 1u;
+            TLA(hh, 0);
             if (!mbar_wait(s_done, ph, abort_flag, status, 51)) break;
+            TLA(hh, 1);
             __syncwarp();
             tc_fence_after_sync();
+            if (gate && j + 1 == n_tiles) {
+                // The last S = Q K^T is done, so the Q and K tiles (64 KB, contiguous) are free: stage the 128 x 128 fp32 gate
+                // tile there with row-wise (coalesced) asynchronous copies; it lands while this tile is being processed.
+                // Row r holds its 32 16-byte chunks at positions c ^ (r & 31), so that the per-row reads of the epilogue
+                // spread over the banks. Warp w stages rows 16 w .. 16 w + 15.
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int gr = 16 * warp + i;
+                    if (r0 + gr < len) {
+                        const float* src = gate + (static_cast<size_t>(row_lo) + r0 + gr) * ldg + head * HD + 4 * lane;
+                        const uint32_t dst = smem_u32(sQ + gr * 512 + ((lane ^ (gr & 31)) << 4));
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+            // raw scores of this thread's half row; the scale (with log2 e folded in) is applied inside the exp2
             float t[64];
             {
                 uint32_t r[32];
@@ -245,26 +300,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     tmem_ld_32x32(tlane + kColS + 64 * hh + 32 * half, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) t[32 * half + e] = __uint_as_float(r[e]) * scale_log2;
+                    for (int e = 0; e < 32; ++e) t[32 * half + e] = __uint_as_float(r[e]);
                 }
             }
             const int kv0 = static_cast<int>(j * TKV) + 64 * hh;
             const int visible = qp_r - kv0 + 1;    // columns e < visible may be attended
-            float lm = kMasked;
-            if (visible >= 64) {
+            if (visible < 64) {
 #pragma unroll
-                for (int e = 0; e < 64; ++e) lm = fmaxf(lm, t[e]);
-            } else {
+                for (int e = 0; e < 64; ++e) t[e] = e < visible ? t[e] : kMasked;
+            }
+            float lm0 = kMasked, lm1 = kMasked;
 #pragma unroll
-                for (int e = 0; e < 64; ++e) {
-                    t[e] = e < visible ? t[e] : kMasked;
-                    lm = fmaxf(lm, t[e]);
-                }
+            for (int e = 0; e < 64; e += 4) {
+                lm0 = fmaxf(lm0, fmaxf(t[e], t[e + 1]));
+                lm1 = fmaxf(lm1, fmaxf(t[e + 2], t[e + 3]));
             }
             float* mxj = mx + ph * 256;
-            mxj[hh * 128 + row] = lm;
+            mxj[hh * 128 + row] = fmaxf(lm0, lm1);
+            TLA(hh, 2);
             if (!pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status)) break;
-            const float m_tile = fmaxf(mxj[row], mxj[128 + row]);
+            TLA(hh, 3);
+            // maximum of the tile in exp2 units; a fully masked row keeps the sentinel
+            const float m_raw = fmaxf(mxj[row], mxj[128 + row]);
+            const float m_tile = m_raw > 0.5f * kMasked ? m_raw * scale_log2 : kMasked;
             const bool grow = m_tile - m_used > kRescaleStep;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
                 // O and the row sum follow the new maximum (lanes whose maximum stays put scale by 1)
@@ -282,14 +340,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_st_wait();
             }
             if (grow) m_used = m_tile;
-            // weights, rounded to the operand type; the row sum is taken over the rounded values
+            TLA(hh, 4);
+            // weights 2^(s * scale - m): a masked score (-1e30) gives exactly 0 as long as the row has a maximum; a row without
+            // one (nothing visible yet) gets zeros explicitly. The row sum adds the weights before they are rounded to 16 bits.
             uint32_t pk[32];
+            if (m_used > 0.5f * kMasked) {
+                float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = t[2 * i] > 0.5f * kMasked ? ex2(t[2 * i] - m_used) : 0.f;
-                const float p1 = t[2 * i + 1] > 0.5f * kMasked ? ex2(t[2 * i + 1] - m_used) : 0.f;
-                pk[i] = Act::pack(p0, p1);
-                l += Act::lo(pk[i]) + Act::hi(pk[i]);
+                for (int i = 0; i < 32; ++i) {
+                    const float p0 = ex2(fmaf(t[2 * i], scale_log2, -m_used));
+                    const float p1 = ex2(fmaf(t[2 * i + 1], scale_log2, -m_used));
+                    pk[i] = Act::pack(p0, p1);
+                    l0 += p0;
+                    l1 += p1;
+                }
+                l += l0 + l1;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) pk[i] = 0u;
             }
             {
                 uint32_t a[16], b[16];
@@ -301,50 +369,76 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_st_32x32_x16(tlane + kColS + 64 * hh, a);
                 tmem_st_32x32_x16(tlane + kColS + 64 * hh + 16, b);
             }
+            TLA(hh, 5);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
+            TLA(hh, 6);
         }
+        TLB(hh, 4);
         if (j == n_tiles && n_tiles) {
-            if (mbar_wait(pv_done, (n_tiles - 1) & 1u, abort_flag, status, 52)) {
+            const bool row_ok = qp_r >= 0;
+            asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's share of the gate tile has landed
+            float* ls = mx + ((n_tiles & 1u) ? 256 : 0);   // the half of the exchange buffer the last tile did not use
+            ls[hh * 128 + row] = l;
+            bool pair_ok = pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status);   // the two halves of a row add their sums
+            if (pair_ok && gate) {   // all 8 warps have staged their rows of the gate tile
+                __syncwarp();
+                if (lane == 0) mbar_arrive(gate_bar);
+                pair_ok = mbar_wait(gate_bar, 0u, abort_flag, status, 54);
+            }
+            if (pair_ok && mbar_wait(pv_done, (n_tiles - 1) & 1u, abort_flag, status, 52)) {
+                TLB(hh, 5);
                 __syncwarp();
                 tc_fence_after_sync();
-                // the two halves of a row add their sums
-                float* ls = mx + ((n_tiles & 1u) ? 256 : 0);   // the half of the exchange buffer the last tile did not use
-                ls[hh * 128 + row] = l;
-                const bool ok = pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status);
-                const float l_tot = ok ? ls[row] + ls[128 + row] : 0.f;
-                const bool valid = qp_r >= 0 && l_tot > 0.f;
-                const float inv = valid ? 1.0f / l_tot : 0.f;
-                const size_t grow_ = static_cast<size_t>(row_lo) + r0 + row;
-                uint16_t* yp = y + grow_ * nq * HD + head * HD + 64 * hh;
-                const float* gp = gate ? gate + grow_ * ldg + head * HD + 64 * hh : nullptr;
+                const float l_tot = ls[row] + ls[128 + row];
+                const float inv = row_ok && l_tot > 0.f ? 1.0f / l_tot : 0.f;
+                // The output tile goes through the V tile's shared memory (free after the last product) so that it leaves in
+                // whole 256-byte rows: thread-per-row stores would touch 32 different lines per instruction. Row r keeps its 16
+                // chunks of 16 bytes at positions c ^ (r & 15).
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t r[32];
                     tmem_ld_32x32(tlane + kColO + 64 * hh + 32 * half, r);
                     tmem_ld_wait();
-                    if (valid) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            float o[8];
+                    for (int c = 0; c < 4; ++c) {
+                        float o[8];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[8 * c + e]) * inv;
-                            if (gp) {
-                                const float4 g0 = *reinterpret_cast<const float4*>(gp + 32 * half + 8 * c);
-                                const float4 g1 = *reinterpret_cast<const float4*>(gp + 32 * half + 8 * c + 4);
-                                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                        for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[8 * c + e]) * inv;
+                        if (gate) {
+                            const int ch = 16 * hh + 8 * half + 2 * c;   // 16-byte chunk of this row's 128 gate values
+                            const float4 g0 = *reinterpret_cast<const float4*>(sQ + row * 512 + ((ch ^ (row & 31)) << 4));
+                            const float4 g1 = *reinterpret_cast<const float4*>(sQ + row * 512 + (((ch + 1) ^ (row & 31)) << 4));
+                            const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) o[e] *= 1.0f / (1.0f + __expf(-g[e]));
-                            }
-                            *reinterpret_cast<uint4*>(yp + 32 * half + 8 * c) =
-                                make_uint4(Act::pack(o[0], o[1]), Act::pack(o[2], o[3]), Act::pack(o[4], o[5]), Act::pack(o[6], o[7]));
+                            for (int e = 0; e < 8; ++e) o[e] = __fdividef(o[e], 1.0f + __expf(-gv[e]));
+                        }
+                        const int oc = 8 * hh + 4 * half + c;   // 16-byte chunk of this row's 128 outputs
+                        *reinterpret_cast<uint4*>(sV + row * 256 + ((oc ^ (row & 15)) << 4)) =
+                            make_uint4(Act::pack(o[0], o[1]), Act::pack(o[2], o[3]), Act::pack(o[4], o[5]), Act::pack(o[6], o[7]));
+                    }
+                }
+                TLB(hh, 8);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_bar);
+                if (mbar_wait(out_bar, 0u, abort_flag, status, 55)) {
+                    TLB(hh, 9);
+                    // warp w sends rows 16 w .. 16 w + 15, two rows per instruction
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int orow = 16 * warp + 2 * i + (lane >> 4), oc = lane & 15;
+                        if (r0 + orow < len && qp[orow] >= 0) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(sV + orow * 256 + ((oc ^ (orow & 15)) << 4));
+                            *reinterpret_cast<uint4*>(y + (static_cast<size_t>(row_lo) + r0 + orow) * nq * HD + head * HD + 8 * oc) = v;
                         }
                     }
                 }
             }
         }
+        TLB(hh, 6);
+        asm volatile("cp.async.wait_all;" ::: "memory");   // (only matters when the loop was left early)
         __syncwarp();
         tmem_ld_wait();
     }
@@ -352,6 +446,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // ------------------------------------------------------------------------------ teardown
     tc_fence_before_sync();
     __syncthreads();
+    TLB(tid >> 7, 7);
     if (warp == 8) {
         tc_fence_after_sync();
         __syncwarp();
@@ -360,6 +455,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 }
 
 }  // namespace
+
+#ifdef DC_TC_TIMELINE
+extern "C" int dc_debug_attn_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_timeline, sizeof(g_attn_timeline))); }
+#endif
 
 // Scratch the tcgen05 attention path needs for the transposed V of `rows` packed cache rows.
 size_t dc_attention_tc_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv) {

@@ -198,6 +198,17 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t adesc, ui
         : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem] with ACCUMULATE fixed at compile time: no predicate to compute per instruction.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACCUMULATE ? 1 : 0)
+        : "memory");
+}
+
 // The same with the A operand in tensor memory: 128 lanes (rows) x 8 columns per 16-element k-step,
 // each 32-bit column holding two consecutive 16-bit K elements (the lower index in the low half).
 // ACCUMULATE is a compile-time choice so that no predicate has to be computed per instruction.
