@@ -17,7 +17,7 @@ size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv);
 int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const float* k, const float* v, const float* a, const float* b,
                            const float* a_log, const float* dt_bias, const float* state_in, float* state_out, float* o, uint32_t t,
                            uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, const uint32_t* seq_start, uint32_t n_seq,
-                           uint32_t max_len, uint32_t split);
+                           uint32_t max_len, uint32_t split, const float* praw, uint32_t ldp, const float* conv_w, const float* conv_prev);
 
 namespace {
 
@@ -154,7 +154,7 @@ extern "C" int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const f
     if (ctx->delta_impl == DC_IMPL_FAST) {
         DC_REQUIRE(ctx, aligned16(v) && aligned16(o) && ldab >= nv, "gated_delta (chunked): v and o must be 16-byte aligned");
         return dc_gated_delta_chunked(ctx, s, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, write_state, nk, nv, seq_start, n_seq,
-                                      max_len, ctx->delta_split);
+                                      max_len, ctx->delta_split, nullptr, 0, nullptr, nullptr);
     }
     // Baseline: the sequential recurrence. Enough threads to fill the GPU: one lane per value column when there are many sequences,
     // up to 8 lanes per column for a single sequence.
@@ -167,6 +167,37 @@ extern "C" int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const f
     else
         launch_seq<8>(s, q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, t, ldab, nk, nv, write_state, seq_start, n_seq);
     return dc_check_launch(ctx, "gated_delta");
+}
+
+extern "C" int dc_conv_gated_delta_supported(dc_ctx* ctx) {
+    return ctx && ctx->delta_impl == DC_IMPL_FAST && ctx->delta_engine == DC_ENGINE_TCGEN05 && ctx->delta_split == 3;
+}
+
+extern "C" int dc_conv_gated_delta(dc_ctx* ctx, void* stream, const float* p, const float* prev, const float* w, const float* a, const float* b,
+                                   const float* a_log, const float* dt_bias, const float* state_in, float* state_out, float* o, uint32_t t,
+                                   uint32_t ldp, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk, uint32_t dv,
+                                   const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, p && w && a && b && a_log && dt_bias && o, "conv_gated_delta: null operand");
+    DC_REQUIRE(ctx, !write_state || state_out, "conv_gated_delta: write_state without a state_out buffer");
+    if (dk != 128 || dv != 128) return dc_fail(ctx, DC_UNSUPPORTED, "conv_gated_delta: head dims %u/%u (built for 128/128)", dk, dv);
+    DC_REQUIRE(ctx, nk >= 1 && nv % nk == 0, "conv_gated_delta: %u value heads over %u key heads", nv, nk);
+    DC_REQUIRE(ctx, ldp >= (2 * nk + nv) * 128 && ldp % 4 == 0, "conv_gated_delta: ldp = %u must cover the qkv columns and be a multiple of 4", ldp);
+    DC_REQUIRE(ctx, aligned16(p) && aligned16(w) && aligned16(o) && (!prev || aligned16(prev)) && (!state_in || aligned16(state_in)) &&
+                        (!state_out || aligned16(state_out)),
+               "conv_gated_delta: p, w, prev, o and the state must be 16-byte aligned");
+    if (!dc_conv_gated_delta_supported(ctx))
+        return dc_fail(ctx, DC_UNSUPPORTED, "conv_gated_delta: needs the fast delta rule on the tcgen05 engine with split 3");
+    if (!seq_start) {
+        DC_REQUIRE(ctx, t >= 1, "conv_gated_delta: T must be at least 1");
+        n_seq = 1;
+        max_len = t;
+    }
+    if (max_len == 0 || max_len > t) max_len = t;
+    DC_REQUIRE(ctx, n_seq >= 1 && n_seq <= 65535, "conv_gated_delta: %u sequences", n_seq);
+    // a, b are columns of the same rows as p: their row stride is ldp
+    return dc_gated_delta_chunked(ctx, static_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, a, b, a_log, dt_bias, state_in, state_out, o, t, ldp,
+                                  write_state, nk, nv, seq_start, n_seq, max_len, 3, p, ldp, w, prev);
 }
 
 extern "C" size_t dc_gated_delta_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) { return dc_delta_chunk_scratch_bytes(t, n_seq ? n_seq : 1, nv); }

@@ -98,6 +98,12 @@ struct ChunkArgs {
     uint8_t* scratch;
     const uint32_t* seq_start;
     uint32_t t, ldab, nk, nv, write_state;
+    // fused conv (tcgen05 kernel 1 only): raw projection rows (stride ldp: q | k | v channels), taps [channels][4],
+    // the 3 raw rows before each sequence (or null); q, k, v above are then unused
+    const float* praw;
+    const float* conv_w;
+    const float* conv_prev;
+    uint32_t ldp;
 };
 
 __device__ __forceinline__ void seq_bounds(const ChunkArgs& p, uint32_t seq, uint32_t& row_lo, uint32_t& len) {
@@ -202,10 +208,10 @@ __device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const flo
 // tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
 // onto L.
 #ifdef DC_TC_TIMELINE
-__device__ long long g_prep_timeline[2 * 16];
-#define TLP(k) do { if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == 128)) g_prep_timeline[(threadIdx.x >> 7) * 16 + (k)] = clock64(); } while (0)
+__device__ long long g_prep_timeline[8 * 16];
+#define TLP(k) do { if (blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) g_prep_timeline[(threadIdx.x >> 5) * 16 + (k)] = clock64(); } while (0)
 #else
-#define TLP(k) do { } while (0)
+#define TLP(k) do { long long t_ = clock64(); asm volatile("" ::"l"(t_)); } while (0)
 #endif
 constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 5 * C * 4;
 
@@ -982,18 +988,445 @@ int launch_apply(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq
     return dc_check_launch(ctx, "gated_delta (chunk apply)");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Kernel 1 on tcgen05 (split 3, the scratch layout of the tcgen05 kernel 2): one CTA (8 warps) per
+// (chunk, head, sequence), two CTAs per SM, 256 TMEM columns.
+//   X = [k rows ; q rows] (128 x 128, bf16 hi/lo K-major tiles in shared memory, written row-wise by the
+//       threads that loaded the rows)            acc1 = X k^T  ->  k.k^T (lanes 0..63) and q.k^T (lanes 64..127)
+//   L, A out of acc1 (thread = row); the 64 x 64 inverse T on warps 0..3 in fp32 as in the mma.sync kernel,
+//   while warps 4..7 (thread = feature column d) read k and v column-wise from global memory (coalesced
+//   across the warp) and write (beta k e^G)^T and (beta v)^T as packed hi/lo A operands into tensor memory,
+//   and Kd^T to scratch.
+//   acc1 = (beta k e^G)^T T^T = W^T,  acc2 = (beta v)^T T^T = U^T    (T as the K-major B tile)
+//   W^T goes back through shared memory into the row-major tile kernel 2 wants; U^T is stored as it is.
+// Thread 0 issues the MMAs; the two waits on their completion are bounded, and a wait that gives up
+// makes the whole CTA skip to the teardown (the decision is taken block-wide).
+struct PrepTcSmem {
+    static constexpr size_t kX = 0;                           // X tiles [hi|lo][2 k-atoms][128][64]; later the W staging tiles
+    static constexpr size_t kL = kX + 4 * SlotTC::kAtom128;   // fp32 L [64][65]; later the T tiles [hi|lo][64][64]
+    static constexpr size_t kN = kL + C * LD * 4;             // fp32 inverse
+    static constexpr size_t kP = kN + C * LD * 4;             // scratch of the block inverse
+    static constexpr size_t kG = kP + 4 * 16 * 17 * 4;        // G, beta, e^G, e^{G_last - G}, beta e^G, 1/|k|
+    static constexpr size_t kBars = kG + 6 * C * 4;
+    static constexpr size_t kBytes = kBars + 64 + 1024;
+};
+static_assert(2 * 64 * 128 <= C * LD * 4, "the T tiles fit where L was");
+constexpr uint32_t kPrepTmemCols = 256;
+constexpr uint32_t kPColAcc1 = 0, kPColAcc2 = 64, kPColKHi = 128, kPColKLo = 160, kPColVHi = 192, kPColVLo = 224;
+
+__device__ __forceinline__ void split8_store(uint8_t* hi_dst, uint8_t* lo_dst, const float (&x)[8]) {
+    uint32_t h[4], l[4];
+    tc_split_pack<4>(x, h, l);
+    *reinterpret_cast<uint4*>(hi_dst) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(lo_dst) = make_uint4(l[0], l[1], l[2], l[3]);
+}
+
+// SiLU with the fast reciprocal (2 ulp): inside the fused conv, where an IEEE division per element would cost more than the conv.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <bool CONV>
+__global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const ChunkArgs p, int* __restrict__ status) {
+    // heads fastest: CTAs that run at the same time read neighbouring 512-byte pieces of the same rows
+    const uint32_t seq = blockIdx.z, h = blockIdx.x, c = blockIdx.y;
+    uint32_t row_lo, len;
+    seq_bounds(p, seq, row_lo, len);
+    const uint32_t r0 = c * C;
+    if (r0 >= len) return;
+    const int n = static_cast<int>(min(static_cast<uint32_t>(C), len - r0));
+    const uint32_t hk = h / (p.nv / p.nk);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t row_base = static_cast<size_t>(row_lo) + r0;
+    uint8_t* slot = slot_ptr<3>(p, row_lo, seq, c, h);
+
+    TLP(15);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sX = smem + PrepTcSmem::kX;
+    float* Lf = reinterpret_cast<float*>(smem + PrepTcSmem::kL);
+    uint8_t* sT = smem + PrepTcSmem::kL;
+    float* Nf = reinterpret_cast<float*>(smem + PrepTcSmem::kN);
+    float* Pf = reinterpret_cast<float*>(smem + PrepTcSmem::kP);
+    float* Gs = reinterpret_cast<float*>(smem + PrepTcSmem::kG);
+    float* Bs = Gs + C;
+    float* Eq = Bs + C;
+    float* Ek = Eq + C;
+    float* Es = Ek + C;
+    float* Kinv = Es + C;   // fused conv: 1 / |k row| so that the column-wise pass can normalise what it recomputes
+    uint64_t* mma_bar = reinterpret_cast<uint64_t*>(smem + PrepTcSmem::kBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_bar + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    if (tid == 0) {
+        mbar_init(mma_bar, 1);
+        *abort_flag = 0u;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, kPrepTmemCols);
+        tmem_relinquish();
+    }
+    // Fused conv: channels of this head's q, k, v in the raw projection rows; raw row s of the sequence (s may be -3..-1:
+    // the rows before it, from conv_prev or zero)
+    const uint32_t conv_dim = (2 * p.nk + p.nv) * D;
+    const uint32_t ch_q = hk * D, ch_k = (p.nk + hk) * D, ch_v = (2 * p.nk + h) * D;
+    auto raw4 = [&](int s, uint32_t ch) -> float4 {
+        if (s >= static_cast<int>(len)) return make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s >= 0) return *reinterpret_cast<const float4*>(p.praw + (static_cast<size_t>(row_lo) + s) * p.ldp + ch);
+        if (p.conv_prev) return *reinterpret_cast<const float4*>(p.conv_prev + (static_cast<size_t>(seq) * 3 + (3 + s)) * conv_dim + ch);
+        return make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    auto raw1 = [&](int s, uint32_t ch) -> float {   // callers keep s below the sequence length
+        if (s >= 0) return p.praw[(static_cast<size_t>(row_lo) + s) * p.ldp + ch];
+        return p.conv_prev ? p.conv_prev[(static_cast<size_t>(seq) * 3 + (3 + s)) * conv_dim + ch] : 0.f;
+    };
+    // The chunk's v rows are wanted much later and column-wise: pull their 256 lines into L2 now.
+    {
+        const int r = tid >> 2;
+        if (r < n) {
+            const float* vrow = CONV ? p.praw + (row_base + r) * p.ldp + ch_v : p.v + ((row_base + r) * p.nv + h) * D;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vrow + 32 * (tid & 3)));
+        }
+    }
+    // gates of the 64 rows on threads 0..63, cumulative log decay by warp scans; rows past the sequence end are
+    // padding: no decay, no write (g = 0, beta = 0, k = v = q = 0). Warps 0..1 do this before they request their
+    // share of the rows below, so that nothing has to stay in registers across the transcendental code.
+    float g_row = 0.f, be_row = 0.f;
+    if (tid < C) {
+        if (tid < n) {
+            const size_t row = row_base + tid;
+            g_row = -expf(p.a_log[h]) * softplus_precise(p.a[row * p.ldab + h] + p.dt_bias[h]);
+            be_row = 1.0f / (1.0f + expf(-p.b[row * p.ldab + h]));
+        }
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, g_row, o);
+            if (lane >= o) g_row += up;
+        }
+        if (lane == 31) Es[warp] = g_row;   // the warp's total, parked where beta e^G will go
+    }
+    // K and Q rows, a warp per row and instruction (coalesced; a float4 per lane). Plain: element e = tid + 256 i is row
+    // e >> 5. Fused conv: warp w owns rows 8 w .. 8 w + 7 (slot i = row 8 w + i) and slides the 4-tap window down them.
+    float4 kv[8], qv[8];
+    if constexpr (!CONV) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + 256 * i, r = e >> 5, c4 = (e & 31) * 4;
+            kv[i] = qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < n) {
+                kv[i] = *reinterpret_cast<const float4*>(p.k + ((row_base + r) * p.nk + hk) * D + c4);
+                qv[i] = *reinterpret_cast<const float4*>(p.q + ((row_base + r) * p.nk + hk) * D + c4);
+            }
+        }
+    } else {
+        // depthwise causal conv (4 taps) + SiLU, then the L2 norm over the head's 128 channels (eps inside the square
+        // root; q also times 128^-1/2): conv.metal:5-35, cpu_ref.rs:55-81
+        const int s0 = static_cast<int>(r0) + 8 * warp;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {   // 0: k rows, 1: q rows (one copy of the code: the kernel must stay inside the instruction cache)
+            const uint32_t ch = (which == 0 ? ch_k : ch_q) + 4 * lane;
+            const float4 w0 = reinterpret_cast<const float4*>(p.conv_w)[ch + 0], w1 = reinterpret_cast<const float4*>(p.conv_w)[ch + 1];
+            const float4 w2 = reinterpret_cast<const float4*>(p.conv_w)[ch + 2], w3 = reinterpret_cast<const float4*>(p.conv_w)[ch + 3];
+            float4 x[11];
+#pragma unroll
+            for (int i = 0; i < 11; ++i) x[i] = raw4(s0 - 3 + i, ch);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float4 y;
+                y.x = silu_fast(fmaf(w0.w, x[i + 3].x, fmaf(w0.z, x[i + 2].x, fmaf(w0.y, x[i + 1].x, w0.x * x[i].x))));
+                y.y = silu_fast(fmaf(w1.w, x[i + 3].y, fmaf(w1.z, x[i + 2].y, fmaf(w1.y, x[i + 1].y, w1.x * x[i].y))));
+                y.z = silu_fast(fmaf(w2.w, x[i + 3].z, fmaf(w2.z, x[i + 2].z, fmaf(w2.y, x[i + 1].z, w2.x * x[i].z))));
+                y.w = silu_fast(fmaf(w3.w, x[i + 3].w, fmaf(w3.z, x[i + 2].w, fmaf(w3.y, x[i + 1].w, w3.x * x[i].w))));
+                const float ss = warp_sum(y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w);
+                const bool live = 8 * warp + i < n;
+                const float rn = live ? rsqrtf(ss + 1e-6f) : 0.f;
+                const float inv = which == 0 ? rn : rn * 0.08838834764831845f;
+                y.x *= inv; y.y *= inv; y.z *= inv; y.w *= inv;
+                qv[i] = y;
+                if (which == 0 && lane == 0) Kinv[8 * warp + i] = rn;
+            }
+            if (which == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) kv[i] = qv[i];
+            }
+        }
+    }
+    TLP(0);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    TLP(1);
+    const uint32_t tmem_base = *tmem_slot;
+    {
+        const float tot0 = Es[0], glast = tot0 + Es[1];
+        __syncthreads();   // both totals are read before Es is overwritten
+        if (tid < C) {
+            const float g = g_row + (warp == 1 ? tot0 : 0.f);
+            Gs[tid] = g;
+            Bs[tid] = be_row;
+            Eq[tid] = expf(g);
+            Ek[tid] = tid < n ? expf(glast - g) : 0.f;   // a padded row contributes nothing to the state
+            Es[tid] = be_row * expf(g);
+            if (tid == 0) *reinterpret_cast<float*>(slot + SlotTC::kDecay) = expf(glast);
+        }
+        __syncthreads();
+    }
+
+    {   // X tiles: k rows 0..63, q rows 64..127 (K-major, 8 bytes of hi and of lo per thread and row); q e^G to scratch
+        const size_t lo_bytes = 2 * SlotTC::kAtom128;
+        const int wq0 = c & 1u ? 0 : 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = CONV ? 8 * warp + i : (tid + 256 * i) >> 5, c4 = 4 * lane;
+            tc_put4(sX, lo_bytes, umma_off<128>(r, c4), kv[i]);
+            tc_put4(sX, lo_bytes, umma_off<128>(64 + r, c4), qv[i]);
+            const float eq = Eq[r];
+            tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wq0 + r, c4), make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq));
+        }
+    }
+    TLP(2);
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+    constexpr uint32_t idesc64 = umma_idesc(1, 1, 128, 64);
+    if (tid == 0) {   // acc1 = X k^T: 2 k-atoms x 4 steps, hi/lo terms
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t off = (ks >> 2) * (SlotTC::kAtom128 >> 4) + 2 * (ks & 3);
+            const uint64_t dh = umma_desc_k128(smem_u32(sX)) + off, dl = umma_desc_k128(smem_u32(sX + 2 * SlotTC::kAtom128)) + off;
+            if (ks == 0) umma_bf16_ss<false>(tmem_base + kPColAcc1, dl, dh, idesc64);
+            else umma_bf16_ss<true>(tmem_base + kPColAcc1, dl, dh, idesc64);
+            umma_bf16_ss<true>(tmem_base + kPColAcc1, dh, dl, idesc64);
+            umma_bf16_ss<true>(tmem_base + kPColAcc1, dh, dh, idesc64);
+        }
+        umma_commit(mma_bar);
+    }
+    bool ok = mbar_wait(mma_bar, 0u, abort_flag, status, 61);
+    TLP(3);
+    ok = __syncthreads_and(ok);
+    if (ok) {
+        tc_fence_after_sync();
+        const int q4 = warp & 3, hh = warp >> 2;
+        const int lrow = 32 * q4 + lane;                    // TMEM lane = X row
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(32 * q4) << 16);
+        {   // L (lanes 0..63) into shared memory, A (lanes 64..127) to scratch; columns j = 32 hh ..
+            uint32_t r[32];
+            tmem_ld_32x32(tlane + kPColAcc1 + 32 * hh, r);
+            tmem_ld_wait();
+            const int i = lrow & 63;
+            const float gi = Gs[i], bi = Bs[i];
+            if (lrow < 64) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int j = 32 * hh + e;
+                    const float w = bi * __uint_as_float(r[e]) * __expf(gi - Gs[j]);
+                    Lf[i * LD + j] = j < i ? w : 0.f;
+                }
+            } else {
+                uint8_t* ah = sX + i * 128;   // staging mirrors the scratch layout of A | Kd^T, hi then lo
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    float x[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int j = 32 * hh + 8 * cc + e;
+                        const float w = __uint_as_float(r[8 * cc + e]) * __expf(gi - Gs[j]);
+                        x[e] = j <= i ? w : 0.f;
+                    }
+                    const int pos = ((4 * hh + cc) ^ (i & 7)) << 4;
+                    split8_store(ah + pos, ah + SlotTC::kAKPart + pos, x);
+                }
+            }
+        }
+        TLP(4);
+        tc_fence_before_sync();
+        __syncthreads();
+        TLP(5);
+        if (warp < 4) {
+            // warps 0..3: T = (I + L)^-1, then its K-major hi/lo tiles (which reuse L's storage)
+            invert_unit_lower(Lf, Nf, Pf, warp, lane);
+            const int trw = tid & 63, th = tid >> 6;   // row, 32-column half
+            float tv[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) tv[e] = Nf[trw * LD + 32 * th + e];
+            bar4();                                    // every row of L has been consumed before the tiles overwrite it
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                float x[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = tv[8 * cc + e];
+                const int pos = ((4 * th + cc) ^ (trw & 7)) << 4;
+                split8_store(sT + trw * 128 + pos, sT + 64 * 128 + trw * 128 + pos, x);
+            }
+        } else {
+            // warps 4..7: thread = feature column d. (beta k e^G)^T and (beta v)^T into tensor memory, Kd^T to scratch
+            const int d = tid - 128;
+            const uint32_t tl4 = tmem_base + (static_cast<uint32_t>(32 * (warp - 4)) << 16);
+            const float* kp = CONV ? nullptr : p.k + (row_base * p.nk + hk) * D + d;
+            const float* vp = CONV ? nullptr : p.v + (row_base * p.nv + h) * D + d;
+            uint8_t* kdh = sX + kABytes + d * 128;   // staged like A
+            // rows past the end are read from the last valid row and scaled by zero (beta, and e^{G_last - G}, are 0 there)
+            // Fused conv: the column's raw values slide through the 4 taps; k is divided by its row norms from above.
+            float4 tw = make_float4(0.f, 0.f, 0.f, 0.f);
+            float x0 = 0.f, x1 = 0.f, x2 = 0.f;
+            if constexpr (CONV) {
+                tw = reinterpret_cast<const float4*>(p.conv_w)[ch_k + d];
+                x0 = raw1(static_cast<int>(r0) - 3, ch_k + d);
+                x1 = raw1(static_cast<int>(r0) - 2, ch_k + d);
+                x2 = raw1(static_cast<int>(r0) - 1, ch_k + d);
+            }
+#pragma unroll 1
+            for (int b = 0; b < 2; ++b) {   // 32 chunk rows at a time
+                float kc[32];
+                if constexpr (!CONV) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) kc[e] = kp[static_cast<size_t>(min(32 * b + e, n - 1)) * p.nk * D];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) kc[e] = p.praw[(row_base + min(32 * b + e, n - 1)) * p.ldp + ch_k + d];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float x3 = kc[e];
+                        kc[e] = silu_fast(fmaf(tw.w, x3, fmaf(tw.z, x2, fmaf(tw.y, x1, tw.x * x0)))) * Kinv[32 * b + e];
+                        x0 = x1; x1 = x2; x2 = x3;
+                    }
+                }
+                float x[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) x[e] = kc[e] * Es[32 * b + e];
+                uint32_t hi[16], lo[16];
+                tc_split_pack<16>(x, hi, lo);
+                tmem_st_32x32_x16(tl4 + kPColKHi + 16 * b, hi);
+                tmem_st_32x32_x16(tl4 + kPColKLo + 16 * b, lo);
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    float y[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) y[e] = kc[8 * cc + e] * Ek[32 * b + 8 * cc + e];
+                    const int pos = ((4 * b + cc) ^ (d & 7)) << 4;
+                    split8_store(kdh + pos, kdh + SlotTC::kAKPart + pos, y);
+                }
+            }
+            TLP(12);
+            if constexpr (CONV) {
+                tw = reinterpret_cast<const float4*>(p.conv_w)[ch_v + d];
+                x0 = raw1(static_cast<int>(r0) - 3, ch_v + d);
+                x1 = raw1(static_cast<int>(r0) - 2, ch_v + d);
+                x2 = raw1(static_cast<int>(r0) - 1, ch_v + d);
+            }
+#pragma unroll 1
+            for (int b = 0; b < 2; ++b) {
+                float x[32];
+                if constexpr (!CONV) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) x[e] = vp[static_cast<size_t>(min(32 * b + e, n - 1)) * p.nv * D];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) x[e] = p.praw[(row_base + min(32 * b + e, n - 1)) * p.ldp + ch_v + d];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float x3 = x[e];
+                        x[e] = silu_fast(fmaf(tw.w, x3, fmaf(tw.z, x2, fmaf(tw.y, x1, tw.x * x0))));
+                        x0 = x1; x1 = x2; x2 = x3;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) x[e] *= Bs[32 * b + e];
+                uint32_t hi[16], lo[16];
+                tc_split_pack<16>(x, hi, lo);
+                tmem_st_32x32_x16(tl4 + kPColVHi + 16 * b, hi);
+                tmem_st_32x32_x16(tl4 + kPColVLo + 16 * b, lo);
+            }
+            TLP(13);
+            tmem_st_wait();
+        }
+        TLP(6);
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncthreads();
+        TLP(7);
+        if (tid == 0) {   // W^T = (beta k e^G)^T T^T, U^T = (beta v)^T T^T
+            tc_fence_after_sync();
+            const uint64_t th_d = umma_desc_k128(smem_u32(sT)), tl_d = umma_desc_k128(smem_u32(sT + 64 * 128));
+            tc_mma_split<4>(tmem_base + kPColAcc1, tmem_base + kPColKHi, tmem_base + kPColKLo, th_d, tl_d, idesc64, false);
+            tc_mma_split<4>(tmem_base + kPColAcc2, tmem_base + kPColVHi, tmem_base + kPColVLo, th_d, tl_d, idesc64, false);
+            umma_commit(mma_bar);
+        }
+        {   // while those run: the staged A | Kd^T tiles (48 KB, laid out as in scratch) leave in whole lines
+            const uint4* src = reinterpret_cast<const uint4*>(sX);
+            uint4* dst = reinterpret_cast<uint4*>(slot + SlotTC::kAK);
+#pragma unroll
+            for (int i = 0; i < 12; ++i) dst[tid + 256 * i] = src[tid + 256 * i];
+        }
+        TLP(8);
+        ok = mbar_wait(mma_bar, 1u, abort_flag, status, 62);
+        TLP(9);
+        ok = __syncthreads_and(ok);
+        if (ok) {
+            tc_fence_after_sync();
+            const int d = lrow;   // TMEM lane = feature column; columns i = 32 hh ..
+            {   // W^T -> the row-major staging tiles [hi|lo][2 k-atoms][64 rows][64] where X was
+                uint32_t r[32];
+                tmem_ld_32x32(tlane + kPColAcc1 + 32 * hh, r);
+                tmem_ld_wait();
+                uint8_t* wh = sX + (d >> 6) * (64 * 128) + (d & 7) * 2;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int i = 32 * hh + e;
+                    const float w = __uint_as_float(r[e]);
+                    const __nv_bfloat16 whi = __float2bfloat16_rn(w);
+                    const __nv_bfloat16 wlo = __float2bfloat16_rn(w - __bfloat162float(whi));
+                    const int off = i * 128 + ((((d & 63) >> 3) ^ (i & 7)) << 4);
+                    *reinterpret_cast<__nv_bfloat16*>(wh + off) = whi;
+                    *reinterpret_cast<__nv_bfloat16*>(wh + 2 * (64 * 128) + off) = wlo;
+                }
+            }
+            {   // U [64 rows][128 dv] fp32: a warp writes 128 contiguous bytes of a row per instruction
+                uint32_t r[32];
+                tmem_ld_32x32(tlane + kPColAcc2 + 32 * hh, r);
+                tmem_ld_wait();
+                float* up = reinterpret_cast<float*>(slot + SlotTC::kU) + (32 * hh) * D + d;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) up[e * D] = __uint_as_float(r[e]);
+            }
+            TLP(10);
+            __syncthreads();
+            // staging -> scratch: W occupies rows 0..63 (even chunks) or 64..127 (odd chunks) of each k-atom of the W|Qg tiles
+            const int wrow0 = c & 1u ? 64 : 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = tid + 256 * i;             // 16-byte chunk of the 32 KB
+                const int seg = e >> 9, o = (e & 511) * 16;   // segment = part * 2 + k-atom, 8 KB each
+                const uint4 v = *reinterpret_cast<const uint4*>(sX + seg * (64 * 128) + o);
+                *reinterpret_cast<uint4*>(slot + SlotTC::kWQ + (seg >> 1) * SlotTC::kWQPart + (seg & 1) * SlotTC::kAtom128 + wrow0 * 128 + o) = v;
+            }
+        }
+    }
+    TLP(11);
+    // ------------------------------------------------------------------------------ teardown
+    tmem_ld_wait();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after_sync();
+        __syncwarp();
+        tmem_dealloc(tmem_base, kPrepTmemCols);
+    }
+}
+
 int launch_chunked_tc(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq, uint32_t max_chunks) {
     static bool attr_set[16] = {};
-    auto prep = delta_chunk_prepare_kernel<3, true>;
+    auto prep = a.praw ? delta_chunk_prepare_tc_kernel<true> : delta_chunk_prepare_tc_kernel<false>;
     auto apply = delta_chunk_apply_tc_kernel;
     if (!attr_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem));
+        cudaError_t e = cudaFuncSetAttribute(delta_chunk_prepare_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PrepTcSmem::kBytes));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(delta_chunk_prepare_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(PrepTcSmem::kBytes));
         if (e == cudaSuccess) e = cudaFuncSetAttribute(apply, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(TcSmem::kBytes));
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", TcSmem::kBytes, cudaGetErrorString(e));
         attr_set[ctx->device & 15] = true;
     }
-    prep<<<dim3(max_chunks, a.nv, n_seq), 256, kPrepSmem, s>>>(a);
-    int rc = dc_check_launch(ctx, "gated_delta (chunk prepare)");
+    prep<<<dim3(a.nv, max_chunks, n_seq), 256, PrepTcSmem::kBytes, s>>>(a, ctx->status_dev);
+    int rc = dc_check_launch(ctx, "gated_delta (chunk prepare, tcgen05)");
     if (rc != DC_OK) return rc;
     apply<<<dim3(a.nv, n_seq), kTcThreads, TcSmem::kBytes, s>>>(a, ctx->status_dev);
     return dc_check_launch(ctx, "gated_delta (chunk apply, tcgen05)");
@@ -1025,8 +1458,10 @@ size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) {
 int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const float* k, const float* v, const float* a, const float* b,
                            const float* a_log, const float* dt_bias, const float* state_in, float* state_out, float* o, uint32_t t,
                            uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, const uint32_t* seq_start, uint32_t n_seq,
-                           uint32_t max_len, uint32_t split) {
-    ChunkArgs args{q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, nullptr, seq_start, t, ldab, nk, nv, write_state};
+                           uint32_t max_len, uint32_t split, const float* praw, uint32_t ldp, const float* conv_w, const float* conv_prev) {
+    ChunkArgs args{q, k, v, a, b, a_log, dt_bias, state_in, state_out, o, nullptr, seq_start, t, ldab, nk, nv, write_state, praw, conv_w, conv_prev, ldp};
+    if (praw && !(split == 3 && ctx->delta_engine == DC_ENGINE_TCGEN05))
+        return dc_fail(ctx, DC_UNSUPPORTED, "conv_gated_delta: the fused form exists for the tcgen05 engine with split 3 only");
     const size_t bytes = dc_delta_chunk_scratch_bytes(t, n_seq, nv);
     args.scratch = static_cast<uint8_t*>(dc_workspace(ctx, bytes));
     if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);

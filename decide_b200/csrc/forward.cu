@@ -99,12 +99,18 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
         if (!is_attention_layer(d, l)) {
             const uint32_t ld = m->lin_in_n;
             RUN("gemm_gdn_in", dc_gemm(c, st, m->h, w.w_in, m->p, rows, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
-            RUN("conv_silu_l2", dc_conv_silu_l2(c, st, m->p, nullptr, w.conv_w, m->q, m->k, m->v, rows, ld, d.gdn_nk, d.gdn_nv,
-                                                d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
             const float* b = m->p + m->conv_dim + m->value_dim;  // fused order qkv|z|b|a (config.rs:14-17)
             const float* a = b + d.gdn_nv;
-            RUN("gated_delta", dc_gated_delta(c, st, m->q, m->k, m->v, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
-                                              d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
+            if (dc_conv_gated_delta_supported(c)) {
+                // conv + SiLU + L2 norm inside the delta rule's first kernel: q, k, v never reach memory
+                RUN("gated_delta", dc_conv_gated_delta(c, st, m->p, nullptr, w.conv_w, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
+                                                       d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
+            } else {
+                RUN("conv_silu_l2", dc_conv_silu_l2(c, st, m->p, nullptr, w.conv_w, m->q, m->k, m->v, rows, ld, d.gdn_nk, d.gdn_nv,
+                                                    d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
+                RUN("gated_delta", dc_gated_delta(c, st, m->q, m->k, m->v, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
+                                                  d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, m->seq_start, n_seq, max_len));
+            }
             RUN("gated_rmsnorm_silu", dc_gated_rmsnorm_silu(c, st, m->o, m->p + m->conv_dim, w.gnorm, m->g, rows, d.gdn_nv, d.gdn_dv, ld, d.eps));
             out_k = m->value_dim;
         } else {

@@ -268,6 +268,15 @@ class Delta(_Family):
         self.dev.call("dc_gated_delta", _stream(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias),
                       _ptr(state_in), _ptr(state_out), _ptr(o), t, ldab, int(write_state), nk, nv, dk, dv, _ptr(seq_start), n_seq, max_len)
 
+    def conv_gated_delta_supported(self) -> bool:
+        return bool(self.dev.lib.dc_conv_gated_delta_supported(self.dev.handle))
+
+    def conv_gated_delta(self, stream, p, prev, w, a, b, a_log, dt_bias, state_in, state_out, o, t, ldp, write_state: bool,
+                         nk: int, nv: int, dk: int = 128, dv: int = 128, seq_start=None, n_seq: int = 1, max_len: int = 0):
+        """conv_silu_l2 + gated_delta in one call: q, k, v never reach memory (no single counterpart in the reference)."""
+        self.dev.call("dc_conv_gated_delta", _stream(stream), _ptr(p), _ptr(prev), _ptr(w), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias),
+                      _ptr(state_in), _ptr(state_out), _ptr(o), t, ldp, int(write_state), nk, nv, dk, dv, _ptr(seq_start), n_seq, max_len)
+
 
 class Kernels:
     """Every kernel family, as `Kernels::new(dev)` of the reference (kernels/mod.rs:54-66)."""

@@ -237,6 +237,19 @@ int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, co
                    uint32_t dv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
 size_t dc_gated_delta_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv);
 
+/* ---- Conv::conv_silu_l2 + Delta::gated_delta in one call (no single counterpart in the reference, which
+ * encodes the two back to back: forward.rs:1214-1234) ----
+ * Same arguments and results as dc_conv_silu_l2 followed by dc_gated_delta, but q, k, v never reach
+ * memory: the chunked delta rule's first kernel applies the conv, SiLU and L2 norm to the raw rows of p
+ * as it loads them. a and b are the gate columns of the same rows (row stride ldp). Available when
+ * dc_conv_gated_delta_supported(ctx) (fast delta rule, tcgen05 engine, split 3); DC_UNSUPPORTED otherwise,
+ * and the caller uses the two-call form. */
+int dc_conv_gated_delta(dc_ctx* ctx, void* stream, const float* p, const float* prev, const float* w, const float* a,
+                        const float* b, const float* a_log, const float* dt_bias, const float* state_in, float* state_out,
+                        float* o, uint32_t t, uint32_t ldp, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk,
+                        uint32_t dv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
+int dc_conv_gated_delta_supported(dc_ctx* ctx);
+
 /* ======================================================================================
  * Whole-model prefill: the host loop of Forward (crates/decide-engine/src/forward.rs:1129-1328)
  * in C++ over the entry points above, for a batch of packed requests.

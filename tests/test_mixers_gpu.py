@@ -319,6 +319,40 @@ def test_gated_delta_packed_sequences(k, delta_impl):
         assert_close(np32(states[s]), st, what=f"packed delta state {s}", **DELTA_TOL)
 
 
+@pytest.mark.parametrize("lens,nk,nv,with_prev", [([1], 16, 16, False), ([70], 16, 16, True), ([130, 5, 64, 200], 16, 16, True), ([90, 33], 8, 16, False)])
+def test_conv_gated_delta_fused_equals_the_two_calls(k, lens, nk, nv, with_prev):
+    """conv + SiLU + L2 norm inside the delta rule's first kernel (dc_conv_gated_delta) against the oracle's conv followed by
+    its sequential delta rule, per sequence, with carried conv rows and two value heads per key head among the cases."""
+    if not k.delta.conv_gated_delta_supported():
+        pytest.skip("the fused form needs the tcgen05 engine with split 3")
+    conv_dim = (2 * nk + nv) * 128
+    ldp = conv_dim + nv * 128 + 2 * nv           # qkv | z | b | a, as the fused projection lays them out
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total, n_seq = int(starts[-1]), len(lens)
+    p = randn(200, total, ldp)
+    w = randn(201, conv_dim, 4, std=0.3)
+    prev = randn(202, n_seq, 3, conv_dim) if with_prev else None
+    a_log = torch.rand(nv, generator=torch.Generator().manual_seed(203)) * 2.7
+    dt_bias = 1.0 + randn(204, nv, std=0.02)
+    states = torch.zeros(n_seq, nv, 128, 128, device="cuda")
+    o = torch.empty(total, nv, 128, device="cuda")
+    pd = p.cuda()
+    b_col, a_col = conv_dim + nv * 128, conv_dim + nv * 128 + nv
+    k.delta.conv_gated_delta(None, pd, prev.cuda() if with_prev else None, w.cuda(), (pd, a_col * 4), (pd, b_col * 4), a_log.cuda(), dt_bias.cuda(),
+                             None, states, o, total, ldp, True, nk, nv, seq_start=_u32(starts), n_seq=n_seq, max_len=max(lens))
+    k.dev.check_status()
+    pn = np32(p)
+    for s, n in enumerate(lens):
+        lo, hi = int(starts[s]), int(starts[s + 1])
+        pv = np32(prev[s]) if with_prev else np.zeros((3, conv_dim), np.float32)
+        wq, wk, wv = cpu_ref.conv_silu_l2(pn[lo:hi], ldp, n, pv, np32(w), nk, nv, 128, 128)
+        st = np.zeros((nv, 128, 128), np.float32)
+        want = cpu_ref.gated_delta(wq, wk, wv, np.ascontiguousarray(pn[lo:hi, a_col:a_col + nv]), np.ascontiguousarray(pn[lo:hi, b_col:b_col + nv]), nv,
+                                   np32(a_log), np32(dt_bias), st, n, nk, nv, 128, 128)
+        assert_close(np32(o)[lo:hi], want, what=f"fused conv+delta o, seq {s}", **DELTA_TOL)
+        assert_close(np32(states[s]), st, what=f"fused conv+delta state, seq {s}", **DELTA_TOL)
+
+
 @pytest.mark.parametrize("n_seq", [10, 40])
 def test_gated_delta_many_sequences_use_wider_lanes(k, n_seq, delta_impl):
     """With many sequences the sequential kernel gives each value column fewer lanes (4, then 1) than for a
