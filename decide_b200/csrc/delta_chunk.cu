@@ -70,13 +70,7 @@ template <int ROWS>
 __device__ __forceinline__ int umma_off(int row, int k) {
     return (k >> 6) * ROWS * 64 + row * 64 + ((((k & 63) >> 3) ^ (row & 7)) << 3) + (k & 7);
 }
-// hi/lo bf16 pair stores at an element offset of a tile pair in global memory (lo tile `lo_bytes` after hi)
-__device__ __forceinline__ void tc_put2(uint8_t* hi_base, size_t lo_bytes, int off, float x0, float x1) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-    const float2 hf = __bfloat1622float2(h);
-    *reinterpret_cast<__nv_bfloat162*>(hi_base + 2 * off) = h;
-    *reinterpret_cast<__nv_bfloat162*>(hi_base + lo_bytes + 2 * off) = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
-}
+// hi/lo bf16 stores (four values, 8 bytes per part) at an element offset of a tile pair; the lo tile lies `lo_bytes` after the hi tile
 __device__ __forceinline__ void tc_put4(uint8_t* hi_base, size_t lo_bytes, int off, const float4& v) {
     const __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
     const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
@@ -203,21 +197,21 @@ __device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const flo
     put4<CW, SPLIT>(hi, hi + ROWS * CW, row, col, v);
 }
 
-// ---------------------------------------------------------------------------------------------
-// Kernel 1: one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
-// tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
-// onto L.
 #ifdef DC_TC_TIMELINE
+// Debug build only (-DDC_TC_TIMELINE): cycle stamps per phase, lane 0 of each warp of one CTA of kernel 1.
 __device__ long long g_prep_timeline[8 * 16];
 #define TLP(k) do { if (blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) g_prep_timeline[(threadIdx.x >> 5) * 16 + (k)] = clock64(); } while (0)
 #else
-#define TLP(k) do { long long t_ = clock64(); asm volatile("" ::"l"(t_)); } while (0)
+#define TLP(k) do { } while (0)
 #endif
+// ---------------------------------------------------------------------------------------------
+// Kernel 1 on mma.sync (DC_ENGINE_MMA_SYNC, and split 1): one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
+// tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
+// onto L.
 constexpr size_t kPrepSmem = 4 * C * D * 2 + 2 * C * LD * 4 + 4 * 16 * 17 * 4 + 5 * C * 4;
 
-template <int SPLIT, bool TC>
+template <int SPLIT>
 __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const ChunkArgs p) {
-    static_assert(!TC || SPLIT == 3, "the tcgen05 scratch layout exists for split 3 only");
     using SL = Slot<SPLIT>;
     extern __shared__ __align__(16) uint8_t smem[];
     __nv_bfloat16* kh = reinterpret_cast<__nv_bfloat16*>(smem);
@@ -243,8 +237,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
     const int wr = warp & 3, wc = warp >> 2;
     const size_t row_base = static_cast<size_t>(row_lo) + r0;
     uint8_t* slot = slot_ptr<SPLIT>(p, row_lo, seq, c, h);
-
-    TLP(15);
     // gates; rows past the sequence end are padding: no decay, no write (g = 0, beta = 0, k = v = q = 0)
     if (tid < C) {
         float g = 0.f, be = 0.f;
@@ -256,14 +248,12 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         Nf[tid] = g;  // staging for the prefix sum
         Bs[tid] = be;
     }
-    TLP(0);
     __syncthreads();
     if (tid < C) {
         float acc = 0.f;
         for (int i = 0; i <= tid; ++i) acc += Nf[i];
         Gs[tid] = acc;
     }
-    TLP(1);
     __syncthreads();
     const float glast = Gs[C - 1];
     if (tid == 0) *reinterpret_cast<float*>(slot + SL::kDecay) = expf(glast);
@@ -277,7 +267,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         Ek[tid] = expf(glast - g);
         Es[tid] = Bs[tid] * expf(g);
     }
-    TLP(2);
     __syncthreads();
 
     {   // K and Q tiles into shared memory; q e^G and k e^{G_last - G} tiles straight to scratch
@@ -297,48 +286,11 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             put4<D, SPLIT>(kh, kl, r, c4, kv[i]);
             put4<D, SPLIT>(qh, ql, r, c4, qv[i]);
             const float eq = Eq[r], ek = Ek[r];
-            const float4 qe = make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq);
-            if constexpr (TC) {
-                tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>((c & 1u ? 0 : 64) + r, c4), qe);
-            } else {
-                gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, qe);
-                gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
-            }
+            gput4<D, C, SPLIT>(slot + SL::kQg, r, c4, make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq));
+            gput4<D, C, SPLIT>(slot + SL::kKd, r, c4, make_float4(kv[i].x * ek, kv[i].y * ek, kv[i].z * ek, kv[i].w * ek));
         }
     }
-    TLP(3);
     __syncthreads();
-    if constexpr (TC) {
-        // Kd^T [dk][j] = k_j[dk] e^{G_last - G_j}, token index contiguous: read the K tiles column-wise
-        // (k as hi + lo carries 16 mantissa bits, which is what the products use anyway)
-        const int dk = tid & 127, jh = tid >> 7;
-        uint8_t* kt = slot + SlotTC::kAK + 64 * 128;
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-            const int chunk = 4 * jh + cc;
-            uint32_t wh[4], wl[4];
-#pragma unroll
-            for (int e2 = 0; e2 < 4; ++e2) {
-                float x[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int j = 8 * chunk + 2 * e2 + e;
-                    const int off = tile_off<D>(j, dk);
-                    x[e] = (__bfloat162float(kh[off]) + __bfloat162float(kl[off])) * Ek[j];
-                }
-                const __nv_bfloat162 h2 = __floats2bfloat162_rn(x[0], x[1]);
-                const float2 hf = __bfloat1622float2(h2);
-                const __nv_bfloat162 l2 = __floats2bfloat162_rn(x[0] - hf.x, x[1] - hf.y);
-                wh[e2] = *reinterpret_cast<const uint32_t*>(&h2);
-                wl[e2] = *reinterpret_cast<const uint32_t*>(&l2);
-            }
-            const int off = dk * 64 + ((chunk ^ (dk & 7)) << 3);
-            *reinterpret_cast<uint4*>(kt + 2 * off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-            *reinterpret_cast<uint4*>(kt + SlotTC::kAKPart + 2 * off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
-        }
-    }
-
-    TLP(14);
     const int m0 = 16 * wr;
     {   // k.k^T and q.k^T: 16 rows x 32 columns per warp
         float akk[4][4], aqk[4][4];
@@ -380,16 +332,10 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
                 aqk[nt][e] *= d0;
                 aqk[nt][2 + e] *= d1;
             }
-            if constexpr (TC) {
-                tc_put2(slot + SlotTC::kAK, SlotTC::kAKPart, umma_off<64>(i0, jb), aqk[nt][0], aqk[nt][1]);
-                tc_put2(slot + SlotTC::kAK, SlotTC::kAKPart, umma_off<64>(i1, jb), aqk[nt][2], aqk[nt][3]);
-            } else {
-                gput2<C, C, SPLIT>(slot + SL::kA, i0, jb, aqk[nt][0], aqk[nt][1]);
-                gput2<C, C, SPLIT>(slot + SL::kA, i1, jb, aqk[nt][2], aqk[nt][3]);
-            }
+            gput2<C, C, SPLIT>(slot + SL::kA, i0, jb, aqk[nt][0], aqk[nt][1]);
+            gput2<C, C, SPLIT>(slot + SL::kA, i1, jb, aqk[nt][2], aqk[nt][3]);
         }
     }
-    TLP(4);
     __syncthreads();
     if (warp < 4) {
         // warps 0..3: T = (I + L)^-1, then its bf16 tiles (which reuse L's storage)
@@ -425,7 +371,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             }
         }
     }
-    TLP(5);
     __syncthreads();
 
     // W = T (beta k e^G), U = T (beta v): 16 rows x 64 columns per warp
@@ -456,14 +401,8 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
         for (int nt = 0; nt < 8; ++nt) {
             const int j = 64 * wc + nt * 8 + 2 * (lane & 3);
             if (which == 0) {
-                if constexpr (TC) {
-                    const int wrow = c & 1u ? 64 : 0;
-                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wrow + i0, j), acc[nt][0], acc[nt][1]);
-                    tc_put2(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wrow + i1, j), acc[nt][2], acc[nt][3]);
-                } else {
-                    gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
-                    gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
-                }
+                gput2<D, C, SPLIT>(slot + SL::kW, i0, j, acc[nt][0], acc[nt][1]);
+                gput2<D, C, SPLIT>(slot + SL::kW, i1, j, acc[nt][2], acc[nt][3]);
             } else {
                 float* sU = reinterpret_cast<float*>(slot + SL::kU);
                 *reinterpret_cast<float2*>(sU + i0 * D + j) = make_float2(acc[nt][0], acc[nt][1]);
@@ -471,7 +410,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_kernel(const Chunk
             }
         }
     }
-    TLP(6);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1079,11 +1017,16 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
         if (s >= 0) return p.praw[(static_cast<size_t>(row_lo) + s) * p.ldp + ch];
         return p.conv_prev ? p.conv_prev[(static_cast<size_t>(seq) * 3 + (3 + s)) * conv_dim + ch] : 0.f;
     };
-    // The chunk's v rows are wanted much later and column-wise: pull their 256 lines into L2 now.
+    // Pull the chunk's rows into L2 before anything else: each thread one 128-byte line of a k, a q and a v row (v is
+    // wanted much later and column-wise; k and q a little later row-wise, after the gates).
     {
         const int r = tid >> 2;
         if (r < n) {
+            const float* krow = CONV ? p.praw + (row_base + r) * p.ldp + ch_k : p.k + ((row_base + r) * p.nk + hk) * D;
+            const float* qrow = CONV ? p.praw + (row_base + r) * p.ldp + ch_q : p.q + ((row_base + r) * p.nk + hk) * D;
             const float* vrow = CONV ? p.praw + (row_base + r) * p.ldp + ch_v : p.v + ((row_base + r) * p.nv + h) * D;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(krow + 32 * (tid & 3)));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(qrow + 32 * (tid & 3)));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(vrow + 32 * (tid & 3)));
         }
     }
@@ -1258,12 +1201,47 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
                 const int pos = ((4 * th + cc) ^ (trw & 7)) << 4;
                 split8_store(sT + trw * 128 + pos, sT + 64 * 128 + trw * 128 + pos, x);
             }
+            // ... then (beta v)^T into tensor memory, thread = value column d (the other four warps are busy with k)
+            const int d = tid;
+            const uint32_t tl4 = tmem_base + (static_cast<uint32_t>(32 * warp) << 16);
+            const float* vp = CONV ? nullptr : p.v + (row_base * p.nv + h) * D + d;
+            float4 tw = make_float4(0.f, 0.f, 0.f, 0.f);
+            float x0 = 0.f, x1 = 0.f, x2 = 0.f;
+            if constexpr (CONV) {
+                tw = reinterpret_cast<const float4*>(p.conv_w)[ch_v + d];
+                x0 = raw1(static_cast<int>(r0) - 3, ch_v + d);
+                x1 = raw1(static_cast<int>(r0) - 2, ch_v + d);
+                x2 = raw1(static_cast<int>(r0) - 1, ch_v + d);
+            }
+#pragma unroll 1
+            for (int b = 0; b < 2; ++b) {
+                float x[32];
+                if constexpr (!CONV) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) x[e] = vp[static_cast<size_t>(min(32 * b + e, n - 1)) * p.nv * D];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) x[e] = p.praw[(row_base + min(32 * b + e, n - 1)) * p.ldp + ch_v + d];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const float x3 = x[e];
+                        x[e] = silu_fast(fmaf(tw.w, x3, fmaf(tw.z, x2, fmaf(tw.y, x1, tw.x * x0))));
+                        x0 = x1; x1 = x2; x2 = x3;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 32; ++e) x[e] *= Bs[32 * b + e];
+                uint32_t hi[16], lo[16];
+                tc_split_pack<16>(x, hi, lo);
+                tmem_st_32x32_x16(tl4 + kPColVHi + 16 * b, hi);
+                tmem_st_32x32_x16(tl4 + kPColVLo + 16 * b, lo);
+            }
+            tmem_st_wait();
         } else {
-            // warps 4..7: thread = feature column d. (beta k e^G)^T and (beta v)^T into tensor memory, Kd^T to scratch
+            // warps 4..7: thread = key column d. (beta k e^G)^T into tensor memory, Kd^T to the staging tiles
             const int d = tid - 128;
             const uint32_t tl4 = tmem_base + (static_cast<uint32_t>(32 * (warp - 4)) << 16);
             const float* kp = CONV ? nullptr : p.k + (row_base * p.nk + hk) * D + d;
-            const float* vp = CONV ? nullptr : p.v + (row_base * p.nv + h) * D + d;
             uint8_t* kdh = sX + kABytes + d * 128;   // staged like A
             // rows past the end are read from the last valid row and scaled by zero (beta, and e^{G_last - G}, are 0 there)
             // Fused conv: the column's raw values slide through the 4 taps; k is divided by its row norms from above.
@@ -1308,35 +1286,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
                 }
             }
             TLP(12);
-            if constexpr (CONV) {
-                tw = reinterpret_cast<const float4*>(p.conv_w)[ch_v + d];
-                x0 = raw1(static_cast<int>(r0) - 3, ch_v + d);
-                x1 = raw1(static_cast<int>(r0) - 2, ch_v + d);
-                x2 = raw1(static_cast<int>(r0) - 1, ch_v + d);
-            }
-#pragma unroll 1
-            for (int b = 0; b < 2; ++b) {
-                float x[32];
-                if constexpr (!CONV) {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) x[e] = vp[static_cast<size_t>(min(32 * b + e, n - 1)) * p.nv * D];
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) x[e] = p.praw[(row_base + min(32 * b + e, n - 1)) * p.ldp + ch_v + d];
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const float x3 = x[e];
-                        x[e] = silu_fast(fmaf(tw.w, x3, fmaf(tw.z, x2, fmaf(tw.y, x1, tw.x * x0))));
-                        x0 = x1; x1 = x2; x2 = x3;
-                    }
-                }
-#pragma unroll
-                for (int e = 0; e < 32; ++e) x[e] *= Bs[32 * b + e];
-                uint32_t hi[16], lo[16];
-                tc_split_pack<16>(x, hi, lo);
-                tmem_st_32x32_x16(tl4 + kPColVHi + 16 * b, hi);
-                tmem_st_32x32_x16(tl4 + kPColVLo + 16 * b, lo);
-            }
             TLP(13);
             tmem_st_wait();
         }
@@ -1435,7 +1384,7 @@ int launch_chunked_tc(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t 
 template <int SPLIT>
 int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq, uint32_t max_chunks) {
     static bool attr_set[16] = {};
-    auto prep = delta_chunk_prepare_kernel<SPLIT, false>;
+    auto prep = delta_chunk_prepare_kernel<SPLIT>;
     if (!attr_set[ctx->device & 15]) {
         cudaError_t e = cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem));
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to %zu bytes of shared memory: %s", kPrepSmem, cudaGetErrorString(e));
