@@ -125,6 +125,35 @@ def delta(k, n_seq, tokens, nk, nv, iters, warmup, impl="fast", split=3, engine=
             "us_per_token_step": us / tokens}
 
 
+def conv_delta(k, n_seq, tokens, nk, nv, iters, warmup, fused=True):
+    """conv + SiLU + L2 norm and the gated delta rule over a random fused projection buffer [rows, qkv|z|b|a]:
+    in one call (dc_conv_gated_delta) or as the two calls."""
+    rows = n_seq * tokens
+    conv_dim = (2 * nk + nv) * 128
+    ldp = conv_dim + nv * 128 + 2 * nv
+    p = torch.randn(rows, ldp, device="cuda")
+    w = torch.randn(conv_dim, 4, device="cuda") * 0.3
+    a_log = torch.rand(nv, device="cuda") * math.log(16.0)
+    dt = torch.ones(nv, device="cuda")
+    o = torch.empty(rows, nv, 128, device="cuda")
+    starts, _ = _seqs(n_seq, tokens)
+    b_col, a_col = conv_dim + nv * 128, conv_dim + nv * 128 + nv
+    if fused:
+        fn = lambda: k.delta.conv_gated_delta(None, p, None, w, (p, a_col * 4), (p, b_col * 4), a_log, dt, None, None, o, rows, ldp, False, nk, nv,
+                                              seq_start=starts, n_seq=n_seq, max_len=tokens)
+    else:
+        q = torch.empty(rows, nk, 128, device="cuda")
+        kk = torch.empty_like(q)
+        v = torch.empty(rows, nv, 128, device="cuda")
+
+        def fn():
+            k.conv.conv_silu_l2(None, p, None, w, q, kk, v, rows, ldp, nk, nv, seq_start=starts, n_seq=n_seq, max_len=tokens)
+            k.delta.gated_delta(None, q, kk, v, (p, a_col * 4), (p, b_col * 4), a_log, dt, None, None, o, rows, ldp, False, nk, nv,
+                                seq_start=starts, n_seq=n_seq, max_len=tokens)
+    us = _time(fn, iters, warmup)
+    return {"op": "conv+gated_delta", "impl": "one call" if fused else "two calls", "seqs": n_seq, "tokens": tokens, "us": us}
+
+
 def rope(k, rows, nq, nkv, gated, iters, warmup):
     hd = 128
     ld = (2 if gated else 1) * nq * hd + 2 * nkv * hd
@@ -164,7 +193,7 @@ def attention(k, n_seq, tokens, nq, nkv, gated, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "rmsnorm", "gnorm", "conv", "delta", "rope", "attention", "all"])
+    ap.add_argument("op", choices=["gemm", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "all"])
     ap.add_argument("--m", type=int, default=38592)
     ap.add_argument("--n", type=int, default=19456)
     ap.add_argument("--k", type=int, default=2560)
@@ -190,6 +219,9 @@ def main():
     elif a.op == "delta":
         out.append(delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup))
         out.append(delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup, engine="mma"))
+    elif a.op == "conv_delta":
+        out.append(conv_delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup))
+        out.append(conv_delta(k, a.seqs, a.tokens, 16, 16, a.iters, a.warmup, fused=False))
     elif a.op == "rope":
         out.append(rope(k, a.rows, 32, 8, True, a.iters, a.warmup))
     elif a.op == "attention":
@@ -203,7 +235,8 @@ def main():
             out += [rmsnorm(k, rows, 2560, a.iters, a.warmup), gnorm(k, rows, 16, a.iters, a.warmup), conv(k, seqs, tokens, 16, 16, a.iters, a.warmup),
                     delta(k, seqs, tokens, 16, 16, a.iters, a.warmup), delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, engine="mma"),
                     delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, split=1),
-                    delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, impl="baseline"), rope(k, rows, 32, 8, True, a.iters, a.warmup),
+                    delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, impl="baseline"), conv_delta(k, seqs, tokens, 16, 16, a.iters, a.warmup),
+                    conv_delta(k, seqs, tokens, 16, 16, a.iters, a.warmup, fused=False), rope(k, rows, 32, 8, True, a.iters, a.warmup),
                     attention(k, seqs, tokens, 32, 8, True, a.iters, a.warmup)]
     dev.check_status()
     for r in out:
