@@ -75,6 +75,27 @@ def test_request_alone_equals_request_in_a_batch(dev):
     eng.close()
 
 
+def test_engines_agree_on_the_whole_model(dev):
+    """The same batch through the tcgen05 kernels (delta rule with the conv fused in, attention) and through
+    the mma.sync kernels (separate conv): identical decisions, logits within a fraction of the gold tolerance."""
+    from decide_b200.kernels import Engine as Eng, Family
+
+    sd, eng = make(SMALL, dev, 21, max_rows=1024, max_seqs=4, max_answers=16, max_cand=8)
+    batch = synth_batch(SMALL, 3, 200, seed=22, n_answers=3, n_cand=8, max_cand=8)
+    try:
+        tc = eng.logits(batch)
+        for fam in (Family.Attn, Family.Delta):
+            dev.set_engine(fam, Eng.MmaSync)
+        legacy = eng.logits(batch)
+    finally:
+        for fam in (Family.Attn, Family.Delta):
+            dev.set_engine(fam, Eng.Tcgen05)
+    dev.check_status()
+    assert np.abs(tc - legacy).max() < 2e-3, f"engines differ by {np.abs(tc - legacy).max():.2e}"
+    assert np.isfinite(tc).all()
+    eng.close()
+
+
 def test_baseline_dims_four_layers(dev):
     """3 Gated DeltaNet layers + 1 attention layer at the benchmark's widths, two 603-token requests."""
     dims = Dims(**{**BASELINE_DIMS.__dict__, "n_layers": 4})
