@@ -109,7 +109,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                float scale_log2, const uint32_t* __restrict__ seq_start, int* __restrict__ status) {
     const uint32_t seq = blockIdx.z, head = blockIdx.y;
     const uint32_t row_lo = seq_start[seq], len = seq_start[seq + 1] - row_lo;
-    const uint32_t r0 = blockIdx.x * TQ;
+    // query tiles are handed out last-first: the tiles with the most cache rows to visit start first
+    const uint32_t r0 = (gridDim.x - 1 - blockIdx.x) * TQ;
     if (r0 >= len) return;
 
     extern __shared__ uint8_t smem_raw[];
@@ -137,7 +138,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef DC_TC_TIMELINE
-    const bool tl_on = blockIdx.x == 4 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || tid == 256);
+    const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || tid == 256);
 #endif
     TLB(tid >> 7, 0);
     if (tid == 0) {
