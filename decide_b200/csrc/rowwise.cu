@@ -41,6 +41,38 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_
     }
 }
 
+// The same for rows of exactly NV4 * 128 values: the row stays in registers between the two passes and all of its
+// loads are in flight at once.
+template <typename Act, int NV4>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_t* __restrict__ y,
+                   const uint32_t* __restrict__ rowmap, uint32_t rows, uint32_t ld_in, uint32_t ld_out, float eps, uint32_t add_one) {
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const uint32_t src = rowmap ? rowmap[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(src) * ld_in);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    float4 v[NV4];
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) v[i] = xr[lane + 32 * i];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(NV4 * 128) + eps);
+    const float one = add_one ? 1.0f : 0.0f;
+    uint2* yr = reinterpret_cast<uint2*>(y + static_cast<size_t>(r) * ld_out);
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) {
+        const float4 g = wr[lane + 32 * i];
+        uint2 o;
+        o.x = Act::pack(v[i].x * inv * (one + g.x), v[i].y * inv * (one + g.y));
+        o.y = Act::pack(v[i].z * inv * (one + g.z), v[i].w * inv * (one + g.w));
+        yr[lane + 32 * i] = o;
+    }
+}
+
 // out[t] = float(table[ids[t]]); embed.metal:4-13.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 embed_kernel(const uint32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ out, uint32_t t,
@@ -255,7 +287,14 @@ int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* 
     DC_REQUIRE(ctx, h % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && h > 0, "rmsnorm: H and the row strides must be multiples of 4");
     DC_REQUIRE(ctx, aligned16(x) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "rmsnorm: misaligned operand");
     if (rows == 0) return DC_OK;
-    if (ctx->act_dtype == DC_ACT_F16)
+    if (h == 2560) {   // the benchmark model's hidden size: the register-resident form
+        if (ctx->act_dtype == DC_ACT_F16)
+            rmsnorm_reg_kernel<ActF16, 20><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+                x, w, static_cast<uint16_t*>(y), rowmap, rows, ld_in, ld_out, eps, add_one);
+        else
+            rmsnorm_reg_kernel<ActBF16, 20><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+                x, w, static_cast<uint16_t*>(y), rowmap, rows, ld_in, ld_out, eps, add_one);
+    } else if (ctx->act_dtype == DC_ACT_F16)
         rmsnorm_kernel<ActF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
             x, w, static_cast<uint16_t*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
     else
