@@ -139,23 +139,33 @@ final_head_kernel(const float* __restrict__ x, const float* __restrict__ w, cons
 
 // Per (row, value head): RMSNorm over dv = 128 with fp32 weight (no +1), times silu(z);
 // gnorm.metal:6-25, spec cpu_ref.rs:132-145. One warp per (row, head), one float4 per lane.
-template <typename Act>
+// One warp per (row, group of G consecutive heads): all of the group's loads are in flight together.
+template <typename Act, int G>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 gated_rmsnorm_silu_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ w,
                           uint16_t* __restrict__ y, uint32_t t, uint32_t nv_heads, uint32_t ldz, float eps) {
+    const uint32_t groups = nv_heads / G;
     const uint32_t idx = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (idx >= t * nv_heads) return;
-    const uint32_t s = idx / nv_heads, hd = idx - s * nv_heads;
+    if (idx >= t * groups) return;
+    const uint32_t s = idx / groups, h0 = (idx - s * groups) * G;
     const int lane = threadIdx.x & 31;
-    const float4 v = reinterpret_cast<const float4*>(o + static_cast<size_t>(idx) * 128)[lane];
-    const float4 zz = reinterpret_cast<const float4*>(z + static_cast<size_t>(s) * ldz + hd * 128)[lane];
-    const float4 g = reinterpret_cast<const float4*>(w)[lane];
-    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-    const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
-    uint2 out;
-    out.x = Act::pack(v.x * inv * g.x * silu_f(zz.x), v.y * inv * g.y * silu_f(zz.y));
-    out.y = Act::pack(v.z * inv * g.z * silu_f(zz.z), v.w * inv * g.w * silu_f(zz.w));
-    reinterpret_cast<uint2*>(y + static_cast<size_t>(idx) * 128)[lane] = out;
+    const size_t head0 = static_cast<size_t>(s) * nv_heads + h0;
+    float4 v[G], zz[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        v[g] = reinterpret_cast<const float4*>(o + (head0 + g) * 128)[lane];
+        zz[g] = reinterpret_cast<const float4*>(z + static_cast<size_t>(s) * ldz + (h0 + g) * 128)[lane];
+    }
+    const float4 gw = reinterpret_cast<const float4*>(w)[lane];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const float ss = warp_sum(v[g].x * v[g].x + v[g].y * v[g].y + v[g].z * v[g].z + v[g].w * v[g].w);
+        const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+        uint2 out;
+        out.x = Act::pack(v[g].x * inv * gw.x * silu_f(zz[g].x), v[g].y * inv * gw.y * silu_f(zz[g].y));
+        out.y = Act::pack(v[g].z * inv * gw.z * silu_f(zz[g].z), v[g].w * inv * gw.w * silu_f(zz[g].w));
+        reinterpret_cast<uint2*>(y + (head0 + g) * 128)[lane] = out;
+    }
 }
 
 // bf16 -> fp16 with the converter's precision-loss counters (convert.rs:73-90): [1] subnormal results,
@@ -354,12 +364,16 @@ int dc_gated_rmsnorm_silu(dc_ctx* ctx, void* stream, const float* o, const float
     DC_REQUIRE(ctx, ldz >= nv * dv && ldz % 4 == 0, "gated_rmsnorm_silu: ldz = %u must cover %u columns and be a multiple of 4", ldz, nv * dv);
     DC_REQUIRE(ctx, aligned16(o) && aligned16(z) && aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "gated_rmsnorm_silu: misaligned operand");
     if (t == 0) return DC_OK;
-    if (ctx->act_dtype == DC_ACT_F16)
-        gated_rmsnorm_silu_kernel<ActF16><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-            o, z, w, static_cast<uint16_t*>(y), t, nv, ldz, eps);
-    else
-        gated_rmsnorm_silu_kernel<ActBF16><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-            o, z, w, static_cast<uint16_t*>(y), t, nv, ldz, eps);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    uint16_t* out = static_cast<uint16_t*>(y);
+    if (nv % 4 == 0) {   // four heads per warp
+        if (f16) gated_rmsnorm_silu_kernel<ActF16, 4><<<blocks_for(t * (nv / 4)), kWarpsPerBlock * 32, 0, st>>>(o, z, w, out, t, nv, ldz, eps);
+        else gated_rmsnorm_silu_kernel<ActBF16, 4><<<blocks_for(t * (nv / 4)), kWarpsPerBlock * 32, 0, st>>>(o, z, w, out, t, nv, ldz, eps);
+    } else {
+        if (f16) gated_rmsnorm_silu_kernel<ActF16, 1><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, st>>>(o, z, w, out, t, nv, ldz, eps);
+        else gated_rmsnorm_silu_kernel<ActBF16, 1><<<blocks_for(t * nv), kWarpsPerBlock * 32, 0, st>>>(o, z, w, out, t, nv, ldz, eps);
+    }
     return dc_check_launch(ctx, "gated_rmsnorm_silu");
 }
 
