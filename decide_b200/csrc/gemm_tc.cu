@@ -476,6 +476,28 @@ int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CU
 
 }  // namespace
 
+namespace {
+// One warp; lane 0 waits on a barrier that never completes, with the same bounded wait every kernel here uses.
+__global__ void wait_timeout_selftest_kernel(int* __restrict__ status) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        dc::mbar_init(&bar, 1);
+        abort_flag = 0u;
+        dc::fence_mbar_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) dc::mbar_wait(&bar, 0u, &abort_flag, status, 99);
+    __syncwarp();
+}
+}  // namespace
+
+extern "C" int dc_selftest_wait_timeout(dc_ctx* ctx, void* stream) {
+    if (!ctx) return DC_INVALID_ARG;
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->status_dev);
+    return dc_check_launch(ctx, "selftest (wait timeout)");
+}
+
 int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16, CUtensorMap* out) {
     return make_tmap(ctx, base, rows, cols, ld, box_rows, f16, out);
 }

@@ -123,6 +123,10 @@ class Device:
         """Synchronises the stream and raises if a kernel's bounded wait ran out."""
         self.call("dc_check_status", _stream(stream))
 
+    def selftest_wait_timeout(self, stream=None):
+        """Enqueues a kernel whose bounded wait must run out (400 ms); the next check_status raises a DC_TIMEOUT KernelError."""
+        self.call("dc_selftest_wait_timeout", _stream(stream))
+
     def set_impl(self, family: Family, impl: Impl):
         self.call("dc_set_impl", int(family), int(impl))
 

@@ -93,6 +93,11 @@ int dc_set_engine(dc_ctx* ctx, uint32_t family, uint32_t engine);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
  * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
 int dc_check_status(dc_ctx* ctx, void* stream);
+/* Self-test of that path (no counterpart in the reference): enqueues one tiny kernel whose only
+ * wait is on an mbarrier that nothing ever arrives at. The wait gives up at the library's limit
+ * (400 ms), raises the status word with wait id 99 and the kernel returns normally; the next
+ * dc_check_status must report DC_TIMEOUT and the context stays usable. */
+int dc_selftest_wait_timeout(dc_ctx* ctx, void* stream);
 /* Kernels enqueued through this context so far. */
 uint64_t dc_launch_count(dc_ctx* ctx);
 /* Grows the context's scratch workspace to at least `bytes` now, so that later calls do not

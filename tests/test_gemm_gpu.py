@@ -162,3 +162,25 @@ def test_contract_violations_are_errors(k):
         k.gemm.gemm(None, x, w, y, 4, 64, 64, 64, 64, 32, Epilogue.SwigluBF16, 32)
     assert e.value.code in (1, 3)
     assert k.dev.launches == before
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(k):
+    """Failure detection without a fault: a kernel whose only wait is on a barrier nothing arrives at gives up at the
+    library's limit, raises the device status word and returns; dc_check_status reports DC_TIMEOUT once (with the wait's
+    id), clears the word, and the same context then runs a GEMM correctly."""
+    from decide_b200.kernels import Epilogue, KernelError
+
+    k.dev.check_status()                       # clean to start with
+    k.dev.selftest_wait_timeout()
+    with pytest.raises(KernelError) as err:
+        k.dev.check_status()
+    assert err.value.code == 4 and "wait id 99" in str(err.value)
+    k.dev.check_status()                       # latched once, cleared by the report
+    m, n, kk = 130, 256, 128
+    x = randn(5, m, kk).to(k.dev.act_torch).cuda()
+    w = randn(6, n, kk, std=0.05).to(k.dev.act_torch).cuda()
+    y = torch.empty(m, n, device="cuda")
+    k.gemm.gemm(None, x, w, y, m, n, kk, kk, kk, n, Epilogue.StoreF32)
+    k.dev.check_status()
+    want = x.float() @ w.float().T
+    assert torch.allclose(y, want, atol=1e-2, rtol=1e-2)
