@@ -26,6 +26,10 @@ from .kernels import Device, Epilogue, Kernels
 EPI = {"f32": Epilogue.StoreF32, "store16": Epilogue.StoreBF16, "add": Epilogue.AddF32, "swiglu": Epilogue.SwigluBF16}
 
 
+# (N, K, epilogue) of gate_up, down, the Gated-DeltaNet in- and out-projection, the attention in-projection and o-proj
+PROJECTIONS = [(19456, 2560, "swiglu"), (2560, 9728, "add"), (8224, 2560, "f32"), (2560, 2048, "add"), (10240, 2560, "f32"), (2560, 4096, "add")]
+
+
 def _time(fn, iters: int, warmup: int) -> float:
     for _ in range(warmup):
         fn()
@@ -193,7 +197,7 @@ def attention(k, n_seq, tokens, nq, nkv, gated, iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "all"])
+    ap.add_argument("op", choices=["gemm", "gemms", "rowwise", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "all"])
     ap.add_argument("--m", type=int, default=38592)
     ap.add_argument("--n", type=int, default=19456)
     ap.add_argument("--k", type=int, default=2560)
@@ -210,6 +214,11 @@ def main():
     out = []
     if a.op == "gemm":
         out.append(gemm(k, a.m, a.n, a.k, a.epi, a.iters, a.warmup, a.bn))
+    elif a.op == "gemms":   # the six projection shapes of the model at --m rows
+        for (n, kk, epi) in PROJECTIONS:
+            out.append(gemm(k, a.m, n, kk, epi, a.iters, a.warmup))
+    elif a.op == "rowwise":  # the memory-bound kernels at --rows rows
+        out += [rmsnorm(k, a.rows, 2560, a.iters, a.warmup), gnorm(k, a.rows, 16, a.iters, a.warmup), rope(k, a.rows, 32, 8, True, a.iters, a.warmup)]
     elif a.op == "rmsnorm":
         out.append(rmsnorm(k, a.rows, 2560, a.iters, a.warmup))
     elif a.op == "gnorm":
@@ -228,7 +237,7 @@ def main():
         out.append(attention(k, a.seqs, a.tokens, 32, 8, True, a.iters, a.warmup))
     else:
         for m in (603, 2307, 38592):
-            for (n, kk, epi) in [(19456, 2560, "swiglu"), (2560, 9728, "add"), (8224, 2560, "f32"), (2560, 2048, "add"), (10240, 2560, "f32"), (2560, 4096, "add")]:
+            for (n, kk, epi) in PROJECTIONS:
                 out.append(gemm(k, m, n, kk, epi, a.iters, a.warmup))
         for seqs, tokens in ((64, 603), (1, 2307)):
             rows = seqs * tokens
