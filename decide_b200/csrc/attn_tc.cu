@@ -213,11 +213,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bool ok = mbar_wait(q_full, 0u, abort_flag, status, 41);
             q_pending = !ok;
             TLB(2, 3);
-            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
-                const uint32_t ph = j & 1u;
-                TLA(2, 0);
-                if (!(ok = mbar_wait(k_full, ph, abort_flag, status, 42))) break;
-                TLA(2, 1);
+            // S = Q K^T of tile j: queued as soon as K has landed. For j > 0 that is right behind O += P V of tile j - 1:
+            // the products execute in issue order, so the scores overwrite the weights only after they have been consumed.
+            auto issue_s = [&](uint32_t j) {
+                if (!mbar_wait(k_full, j & 1u, abort_flag, status, 42)) return false;
                 k_waited = j + 1;
                 tc_fence_after_sync();
 #pragma unroll
@@ -227,8 +226,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     else umma_bf16_ss<true>(tmem_base + kColS, dq + off, dk + off, idesc);
                 }
                 umma_commit(s_done);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (uint32_t j = 0; ok && j < n_tiles; ++j) {
+                const uint32_t ph = j & 1u;
                 TLA(2, 2);
-                if (!(ok = mbar_wait(s_done, ph, abort_flag, status, 43))) break;
+                if (!(ok = mbar_wait(s_done, ph, abort_flag, status, 43))) break;   // the K tile is free again
                 TLA(2, 3);
                 if (j + 1 < n_tiles) load_k(j + 1);
                 if (!(ok = mbar_wait(p_ready, ph, abort_flag, status, 44))) break;
@@ -247,7 +251,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
                 umma_commit(pv_done);
                 TLA(2, 6);
-                if (!(ok = mbar_wait(pv_done, ph, abort_flag, status, 46))) break;
+                if (j + 1 < n_tiles && !(ok = issue_s(j + 1))) break;
+                if (!(ok = mbar_wait(pv_done, ph, abort_flag, status, 46))) break;   // the V tile is free again
                 TLA(2, 7);
                 if (j + 1 < n_tiles) load_v(j + 1);
             }
