@@ -304,6 +304,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             uint32_t tm, tn;
             tile_coords(w.tile, a, tm, tn);
             const uint32_t acc = lt & 1u, acc_ph = (lt >> 1) & 1u;
+            if constexpr (EPI == DC_EPI_ADD_F32) {
+                // The residual block this warp will read-modify-write is pulled into L2 while the tile's main loop still
+                // runs (for a K-split tile: by every part, long before the last one to arrive needs it): a lane asks for
+                // the 128-byte lines of its own row.
+                const size_t prow = static_cast<size_t>(tm) * BM + q * 32u + lane;
+                if (prow < a.m) {
+                    const float* yrow = static_cast<const float*>(y) + prow * a.ldy + tn * BN;
+#pragma unroll
+                    for (uint32_t c = 0; c < BN / 32; ++c)
+                        if (tn * BN + c * 32u < a.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(yrow + c * 32u));
+                }
+            }
             bool ok = mbar_wait(&acc_full[acc], acc_ph, abort_flag, status, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
