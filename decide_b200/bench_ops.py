@@ -66,7 +66,9 @@ def gemm(k: Kernels, m, n, kk, epi: str, iters, warmup, bn=0):
         fn = lambda: k.gemm.gemm(None, x, w, y, m, n, kk, kk, kk, n_out, e)
     us = _time(fn, iters, warmup)
     flops = 2.0 * m * n * kk
-    return {"op": "gemm", "m": m, "n": n, "k": kk, "epilogue": epi, "tile_n": bn or k.gemm.plan(m, n), "us": us, "flops": flops, "tflops": flops / us / 1e6}
+    plan_bn, tail_split = k.gemm.plan_k(m, n, kk)
+    return {"op": "gemm", "m": m, "n": n, "k": kk, "epilogue": epi, "tile_n": bn or plan_bn, "tail_k_split": 1 if bn else tail_split, "us": us, "flops": flops,
+            "tflops": flops / us / 1e6}
 
 
 def rmsnorm(k, rows, h, iters, warmup):

@@ -378,6 +378,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 if (prev == static_cast<int>(a.split) - 1) {
                     __threadfence();
                     const float* base = a.part_ws + static_cast<size_t>(rt * a.split) * kPartFloats + q * 32u * 32u;
+                    if constexpr (EPI == DC_EPI_ADD_F32 || EPI == DC_EPI_STORE_F32) {
+                        // fp32 outputs: the parts already sit in the layout the stores want (a warp instruction covers 4 whole
+                        // rows of the chunk), so they are summed and written straight out; the residual values of `+=` are
+                        // requested together with the parts, one round trip to L2 per chunk instead of two.
+                        float* yf = static_cast<float*>(y);
+#pragma unroll 1
+                        for (uint32_t c = 0; c < BN / 32; ++c) {
+                            const uint32_t col0 = tn * BN + c * 32u;
+                            if (col0 >= a.n) break;
+                            float4 sum[8];
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) {
+                                const size_t row = row0 + it * 4 + sub;
+                                sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (EPI == DC_EPI_ADD_F32 && row < a.m) sum[it] = *reinterpret_cast<const float4*>(yf + row * a.ldy + col0 + 4 * l8);
+                            }
+                            float4 acc4[8];
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) acc4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (uint32_t pt = 0; pt < 4; ++pt) {
+                                if (pt < a.split) {
+                                    const float* src = base + pt * kPartFloats + c * kChunkFloats;
+#pragma unroll
+                                    for (int it = 0; it < 8; ++it) {
+                                        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (it * 4 + sub) * 32 + 4 * l8));
+                                        acc4[it].x += v.x;
+                                        acc4[it].y += v.y;
+                                        acc4[it].z += v.z;
+                                        acc4[it].w += v.w;
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) {
+                                const size_t row = row0 + it * 4 + sub;
+                                if (row < a.m)
+                                    *reinterpret_cast<float4*>(yf + row * a.ldy + col0 + 4 * l8) =
+                                        make_float4(sum[it].x + acc4[it].x, sum[it].y + acc4[it].y, sum[it].z + acc4[it].z, sum[it].w + acc4[it].w);
+                            }
+                        }
+                    } else
 #pragma unroll 1
                     for (uint32_t c = 0; c < BN / 32; ++c) {
                         const uint32_t col0 = tn * BN + c * 32u;
@@ -554,6 +596,12 @@ Plan best_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t bn_ove
 }  // namespace
 
 uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count) { return best_plan(m, n, k ? k : 2560, sm_count, 0).bn; }
+
+extern "C" uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split) {
+    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, 0);
+    if (tail_split) *tail_split = pl.split;
+    return pl.bn;
+}
 
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override) {

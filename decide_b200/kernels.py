@@ -193,6 +193,12 @@ class Gemm(_Family):
     def plan(self, m: int, n: int) -> int:
         return int(self.dev.lib.dc_gemm_plan(self.dev.handle, m, n))
 
+    def plan_k(self, m: int, n: int, k: int) -> tuple[int, int]:
+        """(tile width, K split of the tail wave's tiles) the fast GEMM uses for this shape."""
+        split = ctypes.c_uint32(0)
+        bn = int(self.dev.lib.dc_gemm_plan_k(self.dev.handle, m, n, k, ctypes.byref(split)))
+        return bn, int(split.value)
+
 
 class Norm(_Family):
     def rmsnorm(self, stream, x, w, y, rowmap, rows, h, ld_in, ld_out, add_one: bool, eps: float = EPS):

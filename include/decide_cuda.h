@@ -152,6 +152,9 @@ int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, ui
 int dc_gemm_tile(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
                  uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t bn);
 uint32_t dc_gemm_plan(dc_ctx* ctx, uint32_t m, uint32_t n);
+/* The same for a given K (dc_gemm_plan assumes K = 2560): the tile width, and into *tail_split (may be NULL) the number of
+ * parts the tiles of the last, partial wave are cut into along K (1 = whole tiles). */
+uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split);
 
 /* ---- Norm::rmsnorm (kernels/norm.rs:23-33; spec cpu_ref.rs:11-22) ----
  * y[r] = x[rowmap[r]] * rsqrt(mean(x^2)+eps) * (add_one ? 1+w : w); x fp32, w fp32 [h], y bf16.
