@@ -8,7 +8,10 @@ One step = one batched prefill of 64 requests x 603 seeded token ids through the
 embedding, random-init weights) ending in the candidate-row head over 6 answer rows x 16 candidate
 ids per request. With N GPUs every rank runs its own 64 requests (requests share nothing: no
 collective on the data path), so per-GPU work is fixed ("weak" scaling); `value` is the tokens all
-ranks prefilled divided by the slowest rank's device time.
+ranks prefilled divided by the slowest rank's device time. At N > 1 the line also carries
+`strong_scaling`: ONE set of 64 requests sharded 64/N over the ranks (every rank holds the same
+weights), timed the same way, its logits gathered on rank 0 and compared bit for bit with rank 0's
+own pass over the same shards.
 
 `value` is timed with the batch resident in HBM; `e2e` is the same batch through the public
 host-buffer call (`Engine.logits`: ids, offsets, answer rows and candidates copied in from host
@@ -87,6 +90,14 @@ class ClockSampler:
                 "samples": len(rows), "reasons": reasons}
 
 
+def sub_batch(batch, reqs: range):
+    """The requests `reqs` of a batch of equal-length requests, as a batch of their own."""
+    lo, hi = reqs.start, reqs.stop
+    return type(batch)(batch.ids[lo * TOKENS:hi * TOKENS].copy(), (np.arange(hi - lo + 1) * TOKENS).astype(np.uint32),
+                       (batch.ans_rows[lo * ANSWERS:hi * ANSWERS] - np.uint32(lo * TOKENS)).astype(np.uint32),
+                       batch.cand[lo * ANSWERS:hi * ANSWERS].copy(), batch.ncand[lo * ANSWERS:hi * ANSWERS].copy())
+
+
 def cpu_gold_setup(dims, seed):
     import torch
 
@@ -162,7 +173,7 @@ def run_engine(args):
         embed, final_norm = sd["embed_tokens.weight"].to(cuda), sd["norm.weight"].to(cuda)
         cpu = {"setup_s": time.perf_counter() - t0}
     else:
-        fused, embed, final_norm = synth_fused_on_device(dims, 1 + rank, cuda)
+        fused, embed, final_norm = synth_fused_on_device(dims, 1, cuda)   # the same weights on every rank
     rows = REQUESTS * TOKENS
     eng = Engine(dims, dev=dev, max_rows=rows, max_seqs=REQUESTS, max_answers=REQUESTS * ANSWERS, max_cand=CANDS,
                  fused_layers=fused, embed=embed, final_norm=final_norm)
@@ -211,6 +222,7 @@ def run_engine(args):
     clocks = sampler.stop()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     dev.check_status()
+    rows_run_batch = eng.resident_rows
 
     # ---- single-request latency (p50 forward ms of the metric): one 2,307-token and one 603-token request,
     # host buffers in, logits out, 3 warm-up + 10 timed calls each; linear-interpolated median as the
@@ -230,6 +242,35 @@ def run_engine(args):
                 samples.append(e0.elapsed_time(e1))
             latency[f"tokens_{toks}"] = {"p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)), "runs": len(samples)}
 
+    # ---- strong scaling (N > 1): the same 64 requests on every N, sharded by request; results checked across ranks
+    strong = None
+    if world > 1:
+        whole = synth_batch(dims, REQUESTS, TOKENS, seed=100, n_answers=ANSWERS, n_cand=CANDS, max_cand=CANDS)
+        mine = sub_batch(whole, ddist.shard(REQUESTS, world, rank))
+        for _ in range(max(2, args.warmup)):
+            local_logits = eng.logits(mine)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            eng.forward_resident(mine)
+        e1.record(stream)
+        barrier()
+        ms_strong = max_over_ranks(e0.elapsed_time(e1))
+        gathered = ddist.gather_rows(local_logits, cuda)
+        if rank == 0:
+            # rank 0 alone over the same shards, one after the other: same batches, same kernels, another GPU
+            alone = np.concatenate([eng.logits(sub_batch(whole, ddist.shard(REQUESTS, world, r))) for r in range(world)], axis=0)
+            together = eng.logits(whole)
+            strong = {"tokens_per_s": REQUESTS * TOKENS * args.steps / (ms_strong / 1e3), "ms_per_step": ms_strong / args.steps,
+                      "requests_per_gpu": REQUESTS // world, "rows_per_gpu": mine.rows,
+                      "logits_bit_identical_to_one_gpu": bool(np.array_equal(gathered, alone)),
+                      "max_abs_dlogit_vs_one_gpu": float(np.abs(gathered - alone).max()),
+                      "max_abs_dlogit_vs_one_batch_of_64": float(np.abs(gathered - together).max()),
+                      "note": "the one-GPU pass runs the same shard-sized batches; one batch of 64 differs in which rows fall into K-split tail tiles (fp32 summation order)"}
+            if not strong["logits_bit_identical_to_one_gpu"]:
+                raise SystemExit(f"request sharding changed the logits: {strong}")
+        barrier()
+
     tokens = world * rows * args.steps
     value = tokens / (ms_value / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
@@ -238,10 +279,11 @@ def run_engine(args):
 
     peaks = measured_peaks()
     gu_ms, gu_calls = prof.get("gemm_gate_up", (0.0, 0))
-    flops_per_launch = 2.0 * rows * (2 * dims.inter) * dims.hidden
+    rows_run = rows_run_batch   # rows per step after tail truncation
+    flops_per_launch = 2.0 * rows_run * (2 * dims.inter) * dims.hidden
     achieved = flops_per_launch / (gu_ms / gu_calls * 1e-3) / 1e12 if gu_calls else None
     gemm_ms = sum(ms for n, (ms, _) in prof.items() if n.startswith("gemm_"))
-    gemm_tflops = dims.gemm_flops_per_row() * rows * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+    gemm_tflops = dims.gemm_flops(rows_run, REQUESTS * ANSWERS, pruned=True) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
     traffic = None
     tf = ROOT / "profiles" / "gemm_gate_up_traffic.json"
     if tf.exists():
@@ -251,12 +293,13 @@ def run_engine(args):
     if with_cpu and rank == 0:
         from oracle import gold_synth
 
-        one = type(batch)(batch.ids[:TOKENS], np.array([0, TOKENS], np.uint32), batch.ans_rows[:ANSWERS], batch.cand[:ANSWERS], batch.ncand[:ANSWERS])
+        # the LAST request of the batch: its rows sit in the tiles of the GEMMs' partial last wave, which run K-split
+        one = sub_batch(batch, range(REQUESTS - 1, REQUESTS))
         want, sec = gold_synth.gold_batch_logits(gold, one, CANDS)
-        got = logits[:ANSWERS]
+        got = logits[-ANSWERS:]
         table = check.compare(got, want, one.ncand)
         cpu_baseline = {"value": TOKENS / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                        "sample": f"1 request of {TOKENS} tokens (request 0 of the batch), all 36 layers, fp32 CPU forward: {sec:.1f} s",
+                        "sample": f"1 request of {TOKENS} tokens (the last request of the batch), all 36 layers, fp32 CPU forward: {sec:.1f} s",
                         "parity_on_sample": {"max_abs_dlogit": table["max_dlogit"], "max_abs_dp": table["max_dp"],
                                              "decisions_agree": f"{table['agree']}/{table['fields']}", "near_tie_flips": len(table["small_flips"]),
                                              "failures": table["failures"]}}
@@ -267,6 +310,8 @@ def run_engine(args):
             "ms_per_step": ms_value / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16" if dev.act.name == "F16" else "bf16",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "requests_per_gpu": REQUESTS, "tokens_per_request": TOKENS,
+                       "work_skipping": f"as the reference: each request runs to its last answer row ({rows_run_batch} of {rows} rows per step, forward.rs:830-831) and the "
+                                        "last layer runs q/attention/out-projection/MLP for the answer rows only (forward.rs:1150-1186); tokens/s counts the request's tokens",
                        "l2": "inputs larger than L2: 8.2 GB of weights stream through every step", "sharding": "by request, no collectives",
                        "sixteen_bit_type": "fp16 weights and activations, fp32 accumulate/residual/state (bf16 activations miss the 0.02 logit bar; DECIDE_ACT=bf16 selects them)"
                        if dev.act.name == "F16" else "bf16 weights and activations (misses the 0.02 logit bar over 36 layers)"},
@@ -281,6 +326,7 @@ def run_engine(args):
             "gemm_frac_of_peak": gemm_tflops / peaks["bf16_tflops_sustained"] if gemm_tflops else None,
             "per_op_ms_per_step": {n: ms / args.steps for n, (ms, _) in sorted(prof.items(), key=lambda kv: -kv[1][0])},
             "single_request_latency": latency,
+            "strong_scaling": strong,
             "cpu_baseline": cpu_baseline,
         }))
     eng.close()

@@ -37,6 +37,7 @@ def header_prototypes(text: str | None = None) -> dict[str, tuple]:
     """{name: (restype, [argtypes], [argnames])} for every function the header declares."""
     text = HEADER.read_text() if text is None else text
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"^[ \t]*#.*$", " ", text, flags=re.M)   # preprocessor lines are not declarations
     protos = {}
     for m in re.finditer(r"([A-Za-z_][\w\s\*]*?)\b(dc_\w+)\s*\(([^;{}]*?)\)\s*;", text):
         ret, name, params = m.group(1).strip(), m.group(2), m.group(3).strip()

@@ -329,6 +329,20 @@ inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 1
 
 }  // namespace
 
+namespace {
+constexpr size_t kFastSmem = 4 * BKV * HD * 2 + BQ * sizeof(int);
+}
+int dc_attention_warm(dc_ctx* ctx) {
+    static bool attr_set[16] = {};
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_fast_kernel<ActF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kFastSmem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fast_kernel<ActBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kFastSmem));
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot opt in to %zu bytes of shared memory: %s", kFastSmem, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
+    return DC_OK;
+}
+
 extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void* kc, const void* vc, const float* gate,
                             const uint32_t* qpos, void* y, uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, uint32_t hd,
                             const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
@@ -354,14 +368,11 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
     }
     if (seq_start && ctx->attn_engine == DC_ENGINE_TCGEN05)
         return dc_attention_tc(ctx, s, q, kc, vc, gate, qpos, y, rows, ldg, nq, nkv, seq_start, n_seq, max_len);
-    constexpr size_t smem = 4 * BKV * HD * 2 + BQ * sizeof(int);
-    static bool attr_set[16] = {};
+    constexpr size_t smem = kFastSmem;
     auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;
-    if (!attr_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_fast_kernel<ActF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fast_kernel<ActBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot opt in to %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        attr_set[ctx->device & 15] = true;
+    {
+        const int rc = dc_attention_warm(ctx);
+        if (rc != DC_OK) return rc;
     }
     dim3 grid((max_len + BQ - 1) / BQ, nq, n_seq);
     fast<<<grid, kThreads, smem, s>>>(static_cast<const uint16_t*>(q), static_cast<const uint16_t*>(kc),

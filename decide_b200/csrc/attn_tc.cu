@@ -92,15 +92,6 @@ __global__ void __launch_bounds__(256) v_transpose_kernel(const uint16_t* __rest
     }
 }
 
-#ifdef DC_TC_TIMELINE
-// Debug build only: cycle stamps of the first tiles of one CTA (issuer, softmax threads 0 and 128).
-__device__ long long g_attn_timeline[3 * 16 * 16];
-#define TLA(who, k) do { if (tl_on && j < 15) g_attn_timeline[(j * 3 + (who)) * 16 + (k)] = clock64(); } while (0)
-#define TLB(who, k) do { if (tl_on) g_attn_timeline[(15 * 3 + (who)) * 16 + (k)] = clock64(); } while (0)
-#else
-#define TLA(who, k) do { } while (0)
-#define TLB(who, k) do { } while (0)
-#endif
 
 template <typename Act>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -137,10 +128,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     int* qp_max = qp + 128;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef DC_TC_TIMELINE
-    const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || tid == 256);
-#endif
-    TLB(tid >> 7, 0);
     if (tid == 0) {
         mbar_init(q_full, 1);
         mbar_init(k_full, 1);
@@ -169,7 +156,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    TLB(tid >> 7, 1);
     if (tid < TQ) {
         const int p = r0 + tid < len ? static_cast<int>(qpos[row_lo + r0 + tid]) : -1;
         qp[tid] = p;
@@ -179,7 +165,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (lane == 0) atomicMax(qp_max, m);
     }
     __syncthreads();
-    TLB(tid >> 7, 2);
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t n_tiles = static_cast<uint32_t>(*qp_max + TKV) / TKV;   // cache rows 0..=max qpos; 0 only if no row is valid
 
@@ -212,7 +197,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             constexpr uint64_t kAtomStep = Smem::kAtom >> 4;
             bool ok = mbar_wait(q_full, 0u, abort_flag, status, 41);
             q_pending = !ok;
-            TLB(2, 3);
             // S = Q K^T of tile j: queued as soon as K has landed. For j > 0 that is right behind O += P V of tile j - 1:
             // the products execute in issue order, so the scores overwrite the weights only after they have been consumed.
             auto issue_s = [&](uint32_t j) {
@@ -231,14 +215,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (ok) ok = issue_s(0);
             for (uint32_t j = 0; ok && j < n_tiles; ++j) {
                 const uint32_t ph = j & 1u;
-                TLA(2, 2);
                 if (!(ok = mbar_wait(s_done, ph, abort_flag, status, 43))) break;   // the K tile is free again
-                TLA(2, 3);
                 if (j + 1 < n_tiles) load_k(j + 1);
                 if (!(ok = mbar_wait(p_ready, ph, abort_flag, status, 44))) break;
-                TLA(2, 4);
                 if (!(ok = mbar_wait(v_full, ph, abort_flag, status, 45))) break;
-                TLA(2, 5);
                 v_waited = j + 1;
                 tc_fence_after_sync();
 #pragma unroll
@@ -250,10 +230,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                     else umma_bf16_ts<true>(tmem_base + kColO, pcol, dvt + off, idesc);
                 }
                 umma_commit(pv_done);
-                TLA(2, 6);
                 if (j + 1 < n_tiles && !(ok = issue_s(j + 1))) break;
                 if (!(ok = mbar_wait(pv_done, ph, abort_flag, status, 46))) break;   // the V tile is free again
-                TLA(2, 7);
                 if (j + 1 < n_tiles) load_v(j + 1);
             }
             if (*abort_flag) {
@@ -276,9 +254,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         uint32_t j = 0;
         for (; j < n_tiles; ++j) {
             const uint32_t ph = j & 1u;
-            TLA(hh, 0);
             if (!mbar_wait(s_done, ph, abort_flag, status, 51)) break;
-            TLA(hh, 1);
             __syncwarp();
             tc_fence_after_sync();
             if (gate && j + 1 == n_tiles) {
@@ -323,9 +299,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
             float* mxj = mx + ph * 256;
             mxj[hh * 128 + row] = fmaxf(lm0, lm1);
-            TLA(hh, 2);
             if (!pair_sync(&pair_bar[q], pair_ph, lane, abort_flag, status)) break;
-            TLA(hh, 3);
             // maximum of the tile in exp2 units; a fully masked row keeps the sentinel
             const float m_raw = fmaxf(mxj[row], mxj[128 + row]);
             const float m_tile = m_raw > 0.5f * kMasked ? m_raw * scale_log2 : kMasked;
@@ -346,7 +320,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_st_wait();
             }
             if (grow) m_used = m_tile;
-            TLA(hh, 4);
             // weights 2^(s * scale - m): a masked score (-1e30) gives exactly 0 as long as the row has a maximum; a row without
             // one (nothing visible yet) gets zeros explicitly. The row sum adds the weights before they are rounded to 16 bits.
             uint32_t pk[32];
@@ -375,14 +348,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 tmem_st_32x32_x16(tlane + kColS + 64 * hh, a);
                 tmem_st_32x32_x16(tlane + kColS + 64 * hh + 16, b);
             }
-            TLA(hh, 5);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
-            TLA(hh, 6);
         }
-        TLB(hh, 4);
         if (j == n_tiles && n_tiles) {
             const bool row_ok = qp_r >= 0;
             asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's share of the gate tile has landed
@@ -395,7 +365,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 pair_ok = mbar_wait(gate_bar, 0u, abort_flag, status, 54);
             }
             if (pair_ok && mbar_wait(pv_done, (n_tiles - 1) & 1u, abort_flag, status, 52)) {
-                TLB(hh, 5);
                 __syncwarp();
                 tc_fence_after_sync();
                 const float l_tot = ls[row] + ls[128 + row];
@@ -426,11 +395,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             make_uint4(Act::pack(o[0], o[1]), Act::pack(o[2], o[3]), Act::pack(o[4], o[5]), Act::pack(o[6], o[7]));
                     }
                 }
-                TLB(hh, 8);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(out_bar);
                 if (mbar_wait(out_bar, 0u, abort_flag, status, 55)) {
-                    TLB(hh, 9);
                     // warp w sends rows 16 w .. 16 w + 15, two rows per instruction
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -443,7 +410,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 }
             }
         }
-        TLB(hh, 6);
         asm volatile("cp.async.wait_all;" ::: "memory");   // (only matters when the loop was left early)
         __syncwarp();
         tmem_ld_wait();
@@ -452,7 +418,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // ------------------------------------------------------------------------------ teardown
     tc_fence_before_sync();
     __syncthreads();
-    TLB(tid >> 7, 7);
     if (warp == 8) {
         tc_fence_after_sync();
         __syncwarp();
@@ -462,9 +427,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 }  // namespace
 
-#ifdef DC_TC_TIMELINE
-extern "C" int dc_debug_attn_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_attn_timeline, sizeof(g_attn_timeline))); }
-#endif
 
 // Scratch the tcgen05 attention path needs for the transposed V of `rows` packed cache rows.
 size_t dc_attention_tc_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv) {
@@ -472,20 +434,9 @@ size_t dc_attention_tc_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv
     return static_cast<size_t>(nkv) * HD * ldt * 2;
 }
 
-int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,
-                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
-    const bool f16 = ctx->act_dtype == DC_ACT_F16;
-    const uint32_t ldt = ((rows + 7u) & ~7u) + 8u * n_seq;
-    uint16_t* vt = static_cast<uint16_t*>(dc_workspace(ctx, dc_attention_tc_scratch_bytes(rows, n_seq, nkv)));
-    if (!vt) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot get %zu bytes of scratch", dc_attention_tc_scratch_bytes(rows, n_seq, nkv));
-    CUtensorMap tq, tk, tv;
-    int rc = dc_make_tmap(ctx, q, rows, nq * HD, nq * HD, TQ, f16, &tq);
-    if (rc == DC_OK) rc = dc_make_tmap(ctx, kc, rows, nkv * HD, nkv * HD, TKV, f16, &tk);
-    if (rc == DC_OK) rc = dc_make_tmap(ctx, vt, nkv * HD, ldt, ldt, HD, f16, &tv);
-    if (rc != DC_OK) return rc;
-    v_transpose_kernel<<<dim3((max_len + 16 + 63) / 64, nkv, n_seq), 256, 0, s>>>(static_cast<const uint16_t*>(vc), vt, rows, nkv, ldt, seq_start, n_seq);
-    rc = dc_check_launch(ctx, "attention (V transpose)");
-    if (rc != DC_OK) return rc;
+extern "C" size_t dc_attention_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv) { return dc_attention_tc_scratch_bytes(rows, n_seq, nkv); }
+
+int dc_attention_tc_warm(dc_ctx* ctx) {
     static bool attr_set[16] = {};
     if (!attr_set[ctx->device & 15]) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<ActF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Smem::kBytes));
@@ -493,6 +444,27 @@ int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, 
         if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "attention: cannot opt in to %zu bytes of shared memory: %s", Smem::kBytes, cudaGetErrorString(e));
         attr_set[ctx->device & 15] = true;
     }
+    return DC_OK;
+}
+
+int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,
+                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    const uint32_t ldt = ((rows + 7u) & ~7u) + 8u * n_seq;
+    void* ws = nullptr;
+    int rc = dc_get_workspace(ctx, dc_attention_tc_scratch_bytes(rows, n_seq, nkv), "attention", &ws);
+    if (rc != DC_OK) return rc;
+    uint16_t* vt = static_cast<uint16_t*>(ws);
+    CUtensorMap tq, tk, tv;
+    rc = dc_make_tmap(ctx, q, rows, nq * HD, nq * HD, TQ, f16, &tq);
+    if (rc == DC_OK) rc = dc_make_tmap(ctx, kc, rows, nkv * HD, nkv * HD, TKV, f16, &tk);
+    if (rc == DC_OK) rc = dc_make_tmap(ctx, vt, nkv * HD, ldt, ldt, HD, f16, &tv);
+    if (rc != DC_OK) return rc;
+    v_transpose_kernel<<<dim3((max_len + 16 + 63) / 64, nkv, n_seq), 256, 0, s>>>(static_cast<const uint16_t*>(vc), vt, rows, nkv, ldt, seq_start, n_seq);
+    rc = dc_check_launch(ctx, "attention (V transpose)");
+    if (rc != DC_OK) return rc;
+    rc = dc_attention_tc_warm(ctx);
+    if (rc != DC_OK) return rc;
     const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
     const dim3 grid((max_len + TQ - 1) / TQ, nq, n_seq);
     auto kern = f16 ? attn_tc_kernel<ActF16> : attn_tc_kernel<ActBF16>;

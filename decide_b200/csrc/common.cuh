@@ -44,13 +44,23 @@ struct dc_ctx {
     int* gemm_part_cnt = nullptr;    // their arrival counters, zero between launches
     void* workspace = nullptr;       // scratch for the chunked delta rule and other multi-pass ops
     size_t workspace_bytes = 0;
+    bool workspace_frozen = false;   // an op that needs more scratch than is reserved fails instead of allocating
+    uint64_t allocs = 0;             // device/pinned allocations this context made (dc_open, workspace growth)
+    uint64_t tmap_encodes = 0;       // tensor maps encoded (cache misses)
 };
 
 int dc_fail(dc_ctx* ctx, int code, const char* fmt, ...);
 int dc_check_launch(dc_ctx* ctx, const char* what);
-// Returns a workspace of at least `bytes` (growing it is an allocation: callers that
-// must not allocate during a timed forward reserve it up front with dc_reserve_workspace).
-void* dc_workspace(dc_ctx* ctx, size_t bytes);
+// Hands out the context's scratch workspace, at least `bytes` long, in *out. Growing it frees and
+// allocates device memory (a device-wide synchronisation): callers that must not allocate inside a
+// request reserve up front (dc_reserve_workspace) and freeze it (dc_set_workspace_frozen), after
+// which a larger demand is DC_INVALID_ARG naming `who`.
+int dc_get_workspace(dc_ctx* ctx, size_t bytes, const char* who, void** out);
+// One-time per-device kernel set-up of each family (opt-in shared-memory sizes): what dc_warm_up runs.
+int dc_gemm_warm(dc_ctx* ctx);
+int dc_attention_warm(dc_ctx* ctx);
+int dc_attention_tc_warm(dc_ctx* ctx);
+int dc_delta_chunk_warm(dc_ctx* ctx);
 // Cached 2-D tensor map over a 16-bit row-major matrix [rows][cols] (row stride ld elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zero fill outside the matrix.
 int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16, CUtensorMap* out);

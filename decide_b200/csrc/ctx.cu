@@ -23,19 +23,28 @@ int dc_check_launch(dc_ctx* ctx, const char* what) {
     return DC_OK;
 }
 
-void* dc_workspace(dc_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->workspace_bytes) return ctx->workspace;
+int dc_get_workspace(dc_ctx* ctx, size_t bytes, const char* who, void** out) {
+    *out = nullptr;
+    if (bytes <= ctx->workspace_bytes && ctx->workspace) {
+        *out = ctx->workspace;
+        return DC_OK;
+    }
+    if (ctx->workspace_frozen)
+        return dc_fail(ctx, DC_INVALID_ARG, "%s: needs %zu bytes of scratch but the workspace is frozen at %zu (reserve more with dc_reserve_workspace before freezing)",
+                       who, bytes, ctx->workspace_bytes);
     if (ctx->workspace) cudaFree(ctx->workspace);
     ctx->workspace = nullptr;
     ctx->workspace_bytes = 0;
     void* p = nullptr;
-    if (cudaMalloc(&p, bytes) != cudaSuccess) {
+    if (cudaMalloc(&p, bytes ? bytes : 256) != cudaSuccess) {
         cudaGetLastError();
-        return nullptr;
+        return dc_fail(ctx, DC_CUDA_ERROR, "%s: cannot allocate %zu bytes of scratch", who, bytes);
     }
+    ctx->allocs++;
     ctx->workspace = p;
-    ctx->workspace_bytes = bytes;
-    return p;
+    ctx->workspace_bytes = bytes ? bytes : 256;
+    *out = p;
+    return DC_OK;
 }
 
 static uint32_t impl_from_env(const char* name, bool* bad) {
@@ -120,6 +129,7 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         return nullptr;
     }
     *ctx->status_host = 0;
+    ctx->allocs += 2;
     const size_t ws = static_cast<size_t>(ctx->sm_count) * 128 * 256 * sizeof(float);
     if ((e = cudaMalloc(&ctx->gemm_part_ws, ws)) != cudaSuccess || (e = cudaMalloc(&ctx->gemm_part_cnt, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess ||
         (e = cudaMemset(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess) {
@@ -127,6 +137,7 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
         dc_close(ctx);
         return nullptr;
     }
+    ctx->allocs += 2;
     return ctx;
 }
 
@@ -212,6 +223,8 @@ int dc_check_status(dc_ctx* ctx, void* stream) {
     int code = *ctx->status_host;
     if (code != 0) {
         cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), s);
+        // a split GEMM that gave up leaves arrival counters of its tail tiles non-zero: the next one must start from zero
+        cudaMemsetAsync(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int), s);
         cudaStreamSynchronize(s);
         return dc_fail(ctx, DC_TIMEOUT, "a bounded device-side wait ran out (wait id %d); the results of this run are invalid", code);
     }
@@ -222,8 +235,29 @@ uint64_t dc_launch_count(dc_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 int dc_reserve_workspace(dc_ctx* ctx, size_t bytes) {
     if (!ctx) return DC_INVALID_ARG;
-    if (!dc_workspace(ctx, bytes)) return dc_fail(ctx, DC_CUDA_ERROR, "dc_reserve_workspace: cannot allocate %zu bytes", bytes);
+    void* p = nullptr;
+    return dc_get_workspace(ctx, bytes, "dc_reserve_workspace", &p);
+}
+
+int dc_set_workspace_frozen(dc_ctx* ctx, uint32_t on) {
+    if (!ctx) return DC_INVALID_ARG;
+    ctx->workspace_frozen = on != 0;
     return DC_OK;
+}
+
+size_t dc_workspace_bytes(dc_ctx* ctx) { return ctx ? ctx->workspace_bytes : 0; }
+uint64_t dc_alloc_count(dc_ctx* ctx) { return ctx ? ctx->allocs : 0; }
+uint64_t dc_tmap_encode_count(dc_ctx* ctx) { return ctx ? ctx->tmap_encodes : 0; }
+size_t dc_tmap_cache_size(dc_ctx* ctx) { return ctx ? ctx->tmaps.size() : 0; }
+
+int dc_warm_up(dc_ctx* ctx) {
+    if (!ctx) return DC_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    int rc = dc_gemm_warm(ctx);
+    if (rc == DC_OK) rc = dc_attention_warm(ctx);
+    if (rc == DC_OK) rc = dc_attention_tc_warm(ctx);
+    if (rc == DC_OK) rc = dc_delta_chunk_warm(ctx);
+    return rc;
 }
 
 int dc_sm_count(dc_ctx* ctx) { return ctx ? ctx->sm_count : 0; }

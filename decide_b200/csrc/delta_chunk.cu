@@ -197,13 +197,6 @@ __device__ __forceinline__ void gput4(uint8_t* base, int row, int col, const flo
     put4<CW, SPLIT>(hi, hi + ROWS * CW, row, col, v);
 }
 
-#ifdef DC_TC_TIMELINE
-// Debug build only (-DDC_TC_TIMELINE): cycle stamps per phase, lane 0 of each warp of one CTA of kernel 1.
-__device__ long long g_prep_timeline[8 * 16];
-#define TLP(k) do { if (blockIdx.x == 1 && blockIdx.y == 1 && blockIdx.z == 0 && (threadIdx.x & 31) == 0) g_prep_timeline[(threadIdx.x >> 5) * 16 + (k)] = clock64(); } while (0)
-#else
-#define TLP(k) do { } while (0)
-#endif
 // ---------------------------------------------------------------------------------------------
 // Kernel 1 on mma.sync (DC_ENGINE_MMA_SYNC, and split 1): one CTA (8 warps) per (chunk, head, sequence), two CTAs per SM. Shared memory: K and Q
 // tiles (hi, lo), reused later for beta*k*e^G and beta*v; the fp32 L and N matrices; T tiles aliased
@@ -654,13 +647,6 @@ __device__ __forceinline__ void tc_mma_split(uint32_t d_tmem, uint32_t a_hi, uin
     }
 }
 
-#ifdef DC_TC_TIMELINE
-// Debug build only: cycle stamps of the first chunks of CTA (0, 0), threads 0 and 128.
-__device__ long long g_tc_timeline[3 * 16 * 16];
-#define TL(k) do { if (tl_who >= 0 && c < 16) g_tc_timeline[(c * 3 + tl_who) * 16 + (k)] = clock64(); } while (0)
-#else
-#define TL(k) do { } while (0)
-#endif
 
 constexpr int kTcThreads = 288;   // warps 0..7 work on the rows, warp 8 issues the copies and the MMAs
 
@@ -728,39 +714,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             const uint64_t d_wq_hi = umma_desc_k128(smem_u32(smem + SlotTC::kWQ)), d_wq_lo = umma_desc_k128(smem_u32(smem + SlotTC::kWQ + SlotTC::kWQPart));
             const uint64_t d_ak_hi = umma_desc_k128(smem_u32(smem + SlotTC::kAK)), d_ak_lo = umma_desc_k128(smem_u32(smem + SlotTC::kAK + SlotTC::kAKPart));
             constexpr uint64_t kBufStep = TcSmem::kOps >> 4, kAtomStep = SlotTC::kAtom128 >> 4, kKdStep = kABytes >> 4;
-#ifdef DC_TC_TIMELINE
-            const int tl_who = (blockIdx.x == 0 && blockIdx.y == 0) ? 2 : -1;
-#endif
             for (uint32_t c = 0; c < n_chunks; ++c) {
                 const uint32_t ph = c & 1u;
                 const uint64_t boff = ph * kBufStep;
-                TL(0);
                 if (!sync_all(21)) break;                                 // S is in tensor memory
-                TL(1);
                 if (!mbar_wait(&full[ph], (c >> 1) & 1u, abort_flag, status, 22)) break;
                 loads_waited = c + 1;
                 tc_fence_after_sync();
-                TL(2);
 #pragma unroll
                 for (int ka = 0; ka < 2; ++ka)                            // [S W^T | S Qg^T] or [S Qg^T | S W^T]: acc_v and o buffer ph
                     tc_mma_split<4>(tmem_base + (ph ? kTcColO1 : kTcColV), t_shi + 32 * ka, t_slo + 32 * ka, d_wq_hi + boff + ka * kAtomStep,
                                     d_wq_lo + boff + ka * kAtomStep, idesc128, ka != 0);
                 umma_commit(m1_done);
-                TL(3);
                 if (c > 0 && c + 1 < n_chunks) {
                     // every product of the previous chunk is finished: its operand buffer takes the next chunk's
                     if (!mbar_wait(o_done, ph ^ 1u, abort_flag, status, 26)) break;
                     load_ops(c + 1);
                 }
-                TL(4);
                 if (!sync_all(24)) break;                                 // v' is in tensor memory
                 tc_fence_after_sync();
-                TL(5);
                 tc_mma_split<4>(tmem_base + kTcColDs, t_vhi, t_vlo, d_ak_hi + boff + kKdStep, d_ak_lo + boff + kKdStep, idesc128, false);
                 umma_commit(ds_done);
                 tc_mma_split<4>(tmem_base + (ph ? kTcColO1 : kTcColO0), t_vhi, t_vlo, d_ak_hi + boff, d_ak_lo + boff, idesc64, true);
                 umma_commit(o_done);
-                TL(6);
             }
             if (*abort_flag) {
                 // nothing may still be writing this CTA's shared or tensor memory when it exits
@@ -816,9 +792,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             load_u(0);
             write_s();
         }
-#ifdef DC_TC_TIMELINE
-        const int tl_who = (blockIdx.x == 0 && blockIdx.y == 0) ? (tid == 0 ? 0 : (tid == 128 ? 1 : -1)) : -1;
-#endif
         uint32_t c = 0;
         for (; c < n_chunks; ++c) {
             const uint32_t ph = c & 1u;
@@ -826,22 +799,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
             const bool more = c + 1 < n_chunks;
 
             // S is in tensor memory; acc_v, acc_ds and o buffer `ph` have been read
-            TL(0);
             tc_fence_before_sync();
             if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 21)) break;
-            TL(1);
             // while the first product runs: o of the previous chunk
             const float dl = *reinterpret_cast<const float*>(slot + SlotTC::kDecay);
-            TL(3);
             if (c > 0) {
                 if (!mbar_wait(o_done, ph ^ 1u, abort_flag, status, 26)) break;
                 __syncwarp();
                 tc_fence_after_sync();
                 store_o(ph ^ 1u, static_cast<size_t>(row_lo) + (c - 1) * C, C);
             }
-            TL(4);
             if (!mbar_wait(m1_done, ph, abort_flag, status, 23)) break;
-            TL(5);
             __syncwarp();
             tc_fence_after_sync();
             {   // v'^T = U^T - S W^T for rows j = 32 hh .. + 31 -> 16 hi and 16 lo columns of lane dv
@@ -857,13 +825,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
                 tmem_st_32x32_x16(tlane + kTcColVLo + 16 * hh, lo);
                 tmem_st_wait();
             }
-            TL(6);
             tc_fence_before_sync();
             if (!tc_block_sync(all_bar, sync_ph, lane, abort_flag, status, 24)) break;
-            TL(7);
             if (more) load_u(c + 1);   // lands while the state increment is computed
             if (!mbar_wait(ds_done, ph, abort_flag, status, 29)) break;
-            TL(9);
             __syncwarp();
             tc_fence_after_sync();
 #pragma unroll
@@ -874,9 +839,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
 #pragma unroll
                 for (int e = 0; e < 32; ++e) Sreg[32 * half + e] = fmaf(dl, Sreg[32 * half + e], __uint_as_float(r[e]));
             }
-            TL(10);
             if (more) write_s();
-            TL(11);
         }
         if (c == n_chunks && n_chunks) {   // o of the last chunk
             const uint32_t last = n_chunks - 1;
@@ -905,12 +868,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) delta_chunk_apply_tc_kernel(con
         tmem_dealloc(tmem_base, kTcTmemCols);
     }
 }
-#ifdef DC_TC_TIMELINE
-}  // namespace
-extern "C" int dc_debug_tc_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_timeline, sizeof(g_tc_timeline))); }
-extern "C" int dc_debug_prep_timeline(long long* out) { return static_cast<int>(cudaMemcpyFromSymbol(out, g_prep_timeline, sizeof(g_prep_timeline))); }
-namespace {
-#endif
 
 template <int DVB, int SPLIT>
 int launch_apply(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_seq) {
@@ -976,7 +933,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
     const size_t row_base = static_cast<size_t>(row_lo) + r0;
     uint8_t* slot = slot_ptr<3>(p, row_lo, seq, c, h);
 
-    TLP(15);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sX = smem + PrepTcSmem::kX;
@@ -1093,11 +1049,9 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
             }
         }
     }
-    TLP(0);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    TLP(1);
     const uint32_t tmem_base = *tmem_slot;
     {
         const float tot0 = Es[0], glast = tot0 + Es[1];
@@ -1126,7 +1080,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
             tc_put4(slot + SlotTC::kWQ, SlotTC::kWQPart, umma_off<128>(wq0 + r, c4), make_float4(qv[i].x * eq, qv[i].y * eq, qv[i].z * eq, qv[i].w * eq));
         }
     }
-    TLP(2);
     fence_proxy_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -1145,7 +1098,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
         umma_commit(mma_bar);
     }
     bool ok = mbar_wait(mma_bar, 0u, abort_flag, status, 61);
-    TLP(3);
     ok = __syncthreads_and(ok);
     if (ok) {
         tc_fence_after_sync();
@@ -1181,10 +1133,8 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
                 }
             }
         }
-        TLP(4);
         tc_fence_before_sync();
         __syncthreads();
-        TLP(5);
         if (warp < 4) {
             // warps 0..3: T = (I + L)^-1, then its K-major hi/lo tiles (which reuse L's storage)
             invert_unit_lower(Lf, Nf, Pf, warp, lane);
@@ -1285,15 +1235,11 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
                     split8_store(kdh + pos, kdh + SlotTC::kAKPart + pos, y);
                 }
             }
-            TLP(12);
-            TLP(13);
             tmem_st_wait();
         }
-        TLP(6);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncthreads();
-        TLP(7);
         if (tid == 0) {   // W^T = (beta k e^G)^T T^T, U^T = (beta v)^T T^T
             tc_fence_after_sync();
             const uint64_t th_d = umma_desc_k128(smem_u32(sT)), tl_d = umma_desc_k128(smem_u32(sT + 64 * 128));
@@ -1307,9 +1253,7 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
 #pragma unroll
             for (int i = 0; i < 12; ++i) dst[tid + 256 * i] = src[tid + 256 * i];
         }
-        TLP(8);
         ok = mbar_wait(mma_bar, 1u, abort_flag, status, 62);
-        TLP(9);
         ok = __syncthreads_and(ok);
         if (ok) {
             tc_fence_after_sync();
@@ -1338,7 +1282,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
 #pragma unroll
                 for (int e = 0; e < 32; ++e) up[e * D] = __uint_as_float(r[e]);
             }
-            TLP(10);
             __syncthreads();
             // staging -> scratch: W occupies rows 0..63 (even chunks) or 64..127 (odd chunks) of each k-atom of the W|Qg tiles
             const int wrow0 = c & 1u ? 64 : 0;
@@ -1351,7 +1294,6 @@ __global__ void __launch_bounds__(256, 2) delta_chunk_prepare_tc_kernel(const Ch
             }
         }
     }
-    TLP(11);
     // ------------------------------------------------------------------------------ teardown
     tmem_ld_wait();
     tc_fence_before_sync();
@@ -1400,6 +1342,26 @@ int launch_chunked(dc_ctx* ctx, cudaStream_t s, const ChunkArgs& a, uint32_t n_s
 
 }  // namespace
 
+// Opts every chunked delta-rule kernel in to its dynamic shared-memory size on the context's device, so that no
+// forward has to (the first launch of each variant would do it otherwise).
+int dc_delta_chunk_warm(dc_ctx* ctx) {
+    static bool done[16] = {};
+    if (done[ctx->device & 15]) return DC_OK;
+    auto opt_in = [](auto kern, size_t bytes) { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)); };
+    cudaError_t e = opt_in(delta_chunk_prepare_tc_kernel<true>, PrepTcSmem::kBytes);
+    if (e == cudaSuccess) e = opt_in(delta_chunk_prepare_tc_kernel<false>, PrepTcSmem::kBytes);
+    if (e == cudaSuccess) e = opt_in(delta_chunk_apply_tc_kernel, TcSmem::kBytes);
+    if (e == cudaSuccess) e = opt_in(delta_chunk_prepare_kernel<1>, kPrepSmem);
+    if (e == cudaSuccess) e = opt_in(delta_chunk_prepare_kernel<3>, kPrepSmem);
+    if (e == cudaSuccess) e = opt_in(delta_chunk_apply_kernel<128, 1>, apply_smem<128, 1>());
+    if (e == cudaSuccess) e = opt_in(delta_chunk_apply_kernel<32, 1>, apply_smem<32, 1>());
+    if (e == cudaSuccess) e = opt_in(delta_chunk_apply_kernel<128, 3>, apply_smem<128, 3>());
+    if (e == cudaSuccess) e = opt_in(delta_chunk_apply_kernel<32, 3>, apply_smem<32, 3>());
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot opt in to the kernels' shared memory: %s", cudaGetErrorString(e));
+    done[ctx->device & 15] = true;
+    return DC_OK;
+}
+
 size_t dc_delta_chunk_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv) {
     return (static_cast<size_t>(t) / C + n_seq + 1) * nv * Slot<3>::kBytes;
 }
@@ -1412,8 +1374,9 @@ int dc_gated_delta_chunked(dc_ctx* ctx, cudaStream_t s, const float* q, const fl
     if (praw && !(split == 3 && ctx->delta_engine == DC_ENGINE_TCGEN05))
         return dc_fail(ctx, DC_UNSUPPORTED, "conv_gated_delta: the fused form exists for the tcgen05 engine with split 3 only");
     const size_t bytes = dc_delta_chunk_scratch_bytes(t, n_seq, nv);
-    args.scratch = static_cast<uint8_t*>(dc_workspace(ctx, bytes));
-    if (!args.scratch) return dc_fail(ctx, DC_CUDA_ERROR, "gated_delta: cannot get %zu bytes of scratch", bytes);
+    void* ws = nullptr;
+    if (int rc = dc_get_workspace(ctx, bytes, "gated_delta", &ws); rc != DC_OK) return rc;
+    args.scratch = static_cast<uint8_t*>(ws);
     const uint32_t max_chunks = (max_len + C - 1) / C;
     if (split == 1) return launch_chunked<1>(ctx, s, args, n_seq, max_chunks);
     if (ctx->delta_engine == DC_ENGINE_TCGEN05) return launch_chunked_tc(ctx, s, args, n_seq, max_chunks);

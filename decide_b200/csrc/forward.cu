@@ -21,6 +21,7 @@ struct dc_model {
     const void* embed = nullptr;
     const float* final_norm = nullptr;
     uint32_t max_rows = 0, max_seqs = 0, max_answers = 0, max_cand = 0;
+    uint32_t act_dtype = DC_ACT_F16;   // the context's 16-bit type when the model was created: the type its weights are stored in
     // derived
     uint32_t key_dim = 0, value_dim = 0, conv_dim = 0, lin_in_n = 0, q_dim = 0, kv_dim = 0, att_in_n = 0, p_ld = 0;
     // device buffers
@@ -30,6 +31,19 @@ struct dc_model {
           *inv_freq = nullptr;
     void *h = nullptr, *g = nullptr, *mlp = nullptr, *qo = nullptr, *kc = nullptr, *vc = nullptr;
     uint32_t *ids = nullptr, *pos = nullptr, *seq_start = nullptr, *ans_rows = nullptr, *cand = nullptr, *ncand = nullptr;
+    // answer-row buffers of the pruned last layer (forward.rs:1150-1186): normed rows, q|gate projection, q, attention
+    // output, MLP intermediate, and per answer row its position in its request and its request's first cache row
+    void *hs = nullptr, *qa = nullptr, *ga = nullptr, *mlpa = nullptr;
+    float* ps = nullptr;
+    uint32_t *ans_pos = nullptr, *ans_kv = nullptr;
+    // work skipping (the reference's defaults: both on)
+    bool prune = true;      // last layer: everything after K/V for the answer rows only (set_pruning, forward.rs:517-522)
+    bool truncate = true;   // each request stops after its last answer row (forward.rs:830-831)
+    // the batch the last dc_model_prefill left on the device, as it was laid out after truncation
+    struct Resident {
+        std::vector<uint32_t> given_seq_start;   // what the caller passed
+        uint32_t rows = 0, n_seq = 0, max_len = 0, n_ans = 0, given_rows = 0;
+    } cur;
     // pinned host staging for the host-buffer entry point
     char* host = nullptr;
     size_t host_bytes = 0;
@@ -85,15 +99,53 @@ struct Prof {
         if (_rc != DC_OK) return _rc;    \
     } while (0)
 
+// While a forward is being enqueued the context's workspace may not grow: everything was reserved at
+// dc_model_create, and an op that asks for more is a refused call, not a hidden free + malloc.
+struct FreezeWorkspace {
+    dc_ctx* c;
+    bool was;
+    explicit FreezeWorkspace(dc_ctx* ctx) : c(ctx), was(ctx->workspace_frozen) { c->workspace_frozen = true; }
+    ~FreezeWorkspace() { c->workspace_frozen = was; }
+};
+
 int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, uint32_t max_len, uint32_t n_ans) {
     dc_ctx* c = m->ctx;
     const dc_dims& d = m->d;
+    DC_REQUIRE(c, c->act_dtype == m->act_dtype, "forward: the context's 16-bit type was changed after dc_model_create (the weights are stored in the type it had then)");
+    FreezeWorkspace frozen(c);
     const uint32_t H = d.hidden;
     void* st = s;
     RUN("embed", dc_embed(c, st, m->ids, m->embed, m->x, rows, H));
     const uint32_t n_run = m->layer_limit ? std::min(m->layer_limit, d.n_layers) : d.n_layers;
+    // Last-layer pruning applies to a full run that ends in a head over answer rows, when the last layer is full attention.
+    // A layer limit (the per-layer residual dump) turns it off: that caller wants every row of the residual.
+    const bool pruned = m->prune && m->layer_limit == 0 && n_ans > 0 && is_attention_layer(d, d.n_layers - 1);
     for (uint32_t l = 0; l < n_run; ++l) {
         const dc_layer_weights& w = m->layers[l];
+        if (pruned && l + 1 == d.n_layers) {
+            // Every row still needs its K and V (the answer rows attend to them); nothing else of a non-answer row is
+            // read again. So: norm and the k|v rows of the in-projection for all rows, then q|gate, attention, the output
+            // projection and the MLP for the answer rows only (forward.rs:1150-1186).
+            const uint32_t qn = (d.attn_gate ? 2 : 1) * m->q_dim;   // q|gate (or q) rows of w_in, then k|v
+            const uint32_t kvn = 2 * m->kv_dim;
+            const void* w_kv = static_cast<const char*>(w.w_in) + static_cast<size_t>(qn) * H * 2;
+            RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.in_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
+            RUN("gemm_attn_kv", dc_gemm(c, st, m->h, w_kv, m->p, rows, kvn, H, H, H, kvn, DC_EPI_STORE_F32, d.swiglu_block));
+            RUN("kv_norm_rope", dc_kv_norm_rope(c, st, m->p, w.k_norm, m->inv_freq, m->kc, m->vc, rows, kvn, 0, m->kv_dim, 0, m->pos, m->max_rows,
+                                                d.nkv, d.head_dim, d.rot_dim, d.eps));
+            RUN("gather_rows", dc_gather_rows_bf16(c, st, m->h, m->ans_rows, m->hs, n_ans, H));
+            RUN("gemm_ans_q", dc_gemm(c, st, m->hs, w.w_in, m->ps, n_ans, qn, H, H, H, qn, DC_EPI_STORE_F32, d.swiglu_block));
+            RUN("q_norm_rope", dc_q_norm_rope(c, st, m->ps, w.q_norm, m->inv_freq, m->ans_pos, m->qa, n_ans, qn, d.nq, d.head_dim, d.rot_dim, d.eps));
+            RUN("attention_rows", dc_attention_rows(c, st, m->qa, m->kc, m->vc, d.attn_gate ? m->ps + m->q_dim : nullptr, m->ans_pos, m->ans_kv, m->ga,
+                                                    n_ans, qn, d.nq, d.nkv, d.head_dim));
+            RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows, m->xs, n_ans, H));
+            RUN("gemm_ans_out", dc_gemm(c, st, m->ga, w.w_out, m->xs, n_ans, H, m->q_dim, m->q_dim, m->q_dim, H, DC_EPI_ADD_F32, d.swiglu_block));
+            RUN("rmsnorm", dc_rmsnorm(c, st, m->xs, w.post_norm, m->hs, nullptr, n_ans, H, H, H, d.eps, 1));
+            RUN("gemm_ans_gate_up", dc_gemm(c, st, m->hs, w.w_gu, m->mlpa, n_ans, 2 * d.inter, H, H, H, d.inter, DC_EPI_SWIGLU_BF16, d.swiglu_block));
+            RUN("gemm_ans_down", dc_gemm(c, st, m->mlpa, w.w_down, m->xs, n_ans, H, d.inter, d.inter, d.inter, H, DC_EPI_ADD_F32, d.swiglu_block));
+            RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
+            return DC_OK;
+        }
         RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.in_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
         uint32_t out_k;
         if (!is_attention_layer(d, l)) {
@@ -186,6 +238,7 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     m->max_seqs = max_seqs;
     m->max_answers = max_answers ? max_answers : 1;
     m->max_cand = max_cand;
+    m->act_dtype = ctx->act_dtype;
     m->key_dim = d.gdn_nk * d.gdn_dk;
     m->value_dim = d.gdn_nv * d.gdn_dv;
     m->conv_dim = 2 * m->key_dim + m->value_dim;
@@ -226,6 +279,13 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         {reinterpret_cast<void**>(&m->ans_rows), A * 4},
         {reinterpret_cast<void**>(&m->cand), A * max_cand * 4},
         {reinterpret_cast<void**>(&m->ncand), A * 4},
+        {&m->hs, A * d.hidden * 2},
+        {reinterpret_cast<void**>(&m->ps), A * 2 * m->q_dim * 4},
+        {&m->qa, A * m->q_dim * 2},
+        {&m->ga, A * m->q_dim * 2},
+        {&m->mlpa, A * d.inter * 2},
+        {reinterpret_cast<void**>(&m->ans_pos), A * 4},
+        {reinterpret_cast<void**>(&m->ans_kv), A * 4},
     };
     size_t total = 0;
     for (auto& wnt : wants) total += align_up(wnt.bytes, 1024);
@@ -242,11 +302,15 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         *wnt.ptr = m->arena + off;
         off += align_up(wnt.bytes, 1024);
     }
-    // scratch of the chunked delta rule and of the attention's transposed V for the largest batch, so that no forward allocates
-    if (!dc_workspace(ctx, std::max(dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv), dc_attention_tc_scratch_bytes(max_rows, max_seqs, d.nkv)))) {
+    ctx->allocs++;
+    // scratch of the chunked delta rule and of the attention's transposed V for the largest batch, so that no forward
+    // allocates; every kernel variant opted in to its shared memory now (Gemm::warm_up's role, gemm.rs:89-107)
+    void* ws = nullptr;
+    if (dc_get_workspace(ctx, std::max(dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv), dc_attention_tc_scratch_bytes(max_rows, max_seqs, d.nkv)),
+                         "dc_model_create", &ws) != DC_OK ||
+        dc_warm_up(ctx) != DC_OK) {
         cudaFree(m->arena);
         delete m;
-        dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate the scratch workspace");
         return nullptr;
     }
     // RoPE inverse frequencies in fp32, as the reference and HF compute them (config.rs:44-46)
@@ -254,7 +318,7 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     for (uint32_t i = 0; i < d.rot_dim / 2; ++i)
         f[i] = 1.0f / powf(d.rope_theta, static_cast<float>(2 * i) / static_cast<float>(d.rot_dim));
     cudaMemcpy(m->inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice);
-    m->host_bytes = align_up(R * 4, 64) * 2 + align_up((max_seqs + 1) * 4, 64) + align_up(A * 4, 64) * 2 + align_up(A * max_cand * 4, 64) * 2;
+    m->host_bytes = align_up(R * 4, 64) * 2 + align_up((max_seqs + 1) * 4, 64) + align_up(A * 4, 64) * 4 + align_up(A * max_cand * 4, 64) * 2;
     if (cudaMallocHost(&m->host, m->host_bytes) != cudaSuccess) {
         cudaGetLastError();
         cudaFree(m->arena);
@@ -262,6 +326,7 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         dc_fail(ctx, DC_CUDA_ERROR, "dc_model_create: cannot allocate pinned staging");
         return nullptr;
     }
+    ctx->allocs++;
     return m;
 }
 
@@ -325,21 +390,25 @@ static int check_batch(dc_model* m, uint32_t n_seq, const uint32_t* seq_start, u
 
 // Whole prefill with HOST buffers: copies ids / offsets / answers in, runs every layer, copies the
 // candidate logits out and waits. The analogue of Forward::logits (forward.rs:704-731) for a batch.
+//
+// Tail truncation (forward.rs:830-831): nothing after a request's last answer row can reach a logit (the model is
+// causal and no state is kept), so each request is packed only up to that row; answer rows are renumbered to
+// match. A request without answer rows is kept whole.
 int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint32_t* seq_start, uint32_t n_seq,
                      const uint32_t* ans_rows, const uint32_t* cand, const uint32_t* ncand, uint32_t n_ans, float* logits) {
     if (!m) return DC_INVALID_ARG;
     dc_ctx* ctx = m->ctx;
     DC_REQUIRE(ctx, ids && seq_start && (n_ans == 0 || (ans_rows && cand && ncand && logits)), "prefill: null argument");
-    uint32_t rows = 0, max_len = 0;
-    int rc = check_batch(m, n_seq, seq_start, n_ans, &rows, &max_len);
+    uint32_t given_rows = 0, max_len = 0;
+    int rc = check_batch(m, n_seq, seq_start, n_ans, &given_rows, &max_len);
     if (rc != DC_OK) return rc;
     for (uint32_t i = 0; i < n_ans; ++i) {
-        DC_REQUIRE(ctx, ans_rows[i] < rows, "prefill: answer row %u is past the %u rows", ans_rows[i], rows);
+        DC_REQUIRE(ctx, ans_rows[i] < given_rows, "prefill: answer row %u is past the %u rows", ans_rows[i], given_rows);
         DC_REQUIRE(ctx, ncand[i] >= 1 && ncand[i] <= m->max_cand, "prefill: answer %u has %u candidates (1..%u)", i, ncand[i], m->max_cand);
         for (uint32_t j = 0; j < ncand[i]; ++j)
             DC_REQUIRE(ctx, cand[static_cast<size_t>(i) * m->max_cand + j] < m->d.vocab, "prefill: candidate id out of the vocabulary");
     }
-    for (uint32_t i = 0; i < rows; ++i) DC_REQUIRE(ctx, ids[i] < m->d.vocab, "prefill: token id %u out of the vocabulary", ids[i]);
+    for (uint32_t i = 0; i < given_rows; ++i) DC_REQUIRE(ctx, ids[i] < m->d.vocab, "prefill: token id %u out of the vocabulary", ids[i]);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // stage through pinned memory: ids, positions, offsets, answers
@@ -354,21 +423,52 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
     uint32_t* h_seq = reinterpret_cast<uint32_t*>(take((static_cast<size_t>(m->max_seqs) + 1) * 4));
     uint32_t* h_ans = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
     uint32_t* h_ncand = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
+    uint32_t* h_apos = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
+    uint32_t* h_akv = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * 4));
     uint32_t* h_cand = reinterpret_cast<uint32_t*>(take(static_cast<size_t>(m->max_answers) * m->max_cand * 4));
     float* h_logits = reinterpret_cast<float*>(take(static_cast<size_t>(m->max_answers) * m->max_cand * 4));
-    memcpy(h_ids, ids, static_cast<size_t>(rows) * 4);
-    memcpy(h_seq, seq_start, (static_cast<size_t>(n_seq) + 1) * 4);
-    for (uint32_t i = 0; i < n_seq; ++i)
-        for (uint32_t r = seq_start[i]; r < seq_start[i + 1]; ++r) h_pos[r] = r - seq_start[i];
+
+    // request of each answer row, and each request's length after truncation
+    std::vector<uint32_t> ans_seq(n_ans), keep(n_seq);
+    for (uint32_t i = 0; i < n_seq; ++i) keep[i] = m->truncate && m->layer_limit == 0 && n_ans ? 0u : seq_start[i + 1] - seq_start[i];
+    for (uint32_t i = 0; i < n_ans; ++i) {
+        const uint32_t sq = static_cast<uint32_t>(std::upper_bound(seq_start, seq_start + n_seq + 1, ans_rows[i]) - seq_start) - 1u;
+        ans_seq[i] = sq;
+        keep[sq] = std::max(keep[sq], ans_rows[i] - seq_start[sq] + 1u);
+    }
+    uint32_t rows = 0;
+    max_len = 0;
+    for (uint32_t i = 0; i < n_seq; ++i) {
+        if (keep[i] == 0) keep[i] = seq_start[i + 1] - seq_start[i];   // no answer row in this request: kept whole
+        h_seq[i] = rows;
+        memcpy(h_ids + rows, ids + seq_start[i], static_cast<size_t>(keep[i]) * 4);
+        for (uint32_t r = 0; r < keep[i]; ++r) h_pos[rows + r] = r;
+        rows += keep[i];
+        max_len = std::max(max_len, keep[i]);
+    }
+    h_seq[n_seq] = rows;
+    for (uint32_t i = 0; i < n_ans; ++i) {
+        h_apos[i] = ans_rows[i] - seq_start[ans_seq[i]];
+        h_akv[i] = h_seq[ans_seq[i]];
+        h_ans[i] = h_akv[i] + h_apos[i];
+    }
     if (n_ans) {
-        memcpy(h_ans, ans_rows, static_cast<size_t>(n_ans) * 4);
         memcpy(h_ncand, ncand, static_cast<size_t>(n_ans) * 4);
         memcpy(h_cand, cand, static_cast<size_t>(n_ans) * m->max_cand * 4);
     }
+    m->cur.given_seq_start.assign(seq_start, seq_start + n_seq + 1);
+    m->cur.rows = rows;
+    m->cur.n_seq = n_seq;
+    m->cur.max_len = max_len;
+    m->cur.n_ans = n_ans;
+    m->cur.given_rows = given_rows;
+
     cudaError_t e = cudaMemcpyAsync(m->ids, h_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess) e = cudaMemcpyAsync(m->pos, h_pos, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess) e = cudaMemcpyAsync(m->seq_start, h_seq, (static_cast<size_t>(n_seq) + 1) * 4, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ans_rows, h_ans, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ans_pos, h_apos, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ans_kv, h_akv, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->ncand, h_ncand, static_cast<size_t>(n_ans) * 4, cudaMemcpyHostToDevice, s);
     if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->cand, h_cand, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: host-to-device copy failed: %s", cudaGetErrorString(e));
@@ -393,14 +493,32 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
 }
 
 // The same pass with inputs already resident in the model's device buffers (set by a previous
-// dc_model_prefill of the same batch): enqueues only, no copies, no synchronisation.
+// dc_model_prefill of the same batch): enqueues only, no copies, no synchronisation. The batch runs as that
+// prefill laid it out (truncated to each request's last answer row when truncation was on).
 int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_start, uint32_t n_seq, uint32_t n_ans) {
     if (!m) return DC_INVALID_ARG;
-    uint32_t rows = 0, max_len = 0;
-    int rc = check_batch(m, n_seq, seq_start, n_ans, &rows, &max_len);
-    if (rc != DC_OK) return rc;
-    return forward_device(m, static_cast<cudaStream_t>(stream), rows, n_seq, max_len, n_ans);
+    dc_ctx* ctx = m->ctx;
+    DC_REQUIRE(ctx, seq_start, "forward_resident: null argument");
+    DC_REQUIRE(ctx, m->cur.n_seq == n_seq && m->cur.n_ans == n_ans && m->cur.given_seq_start.size() == static_cast<size_t>(n_seq) + 1 &&
+                        std::equal(seq_start, seq_start + n_seq + 1, m->cur.given_seq_start.begin()),
+               "forward_resident: this is not the batch the last dc_model_prefill left on the device");
+    return forward_device(m, static_cast<cudaStream_t>(stream), m->cur.rows, n_seq, m->cur.max_len, n_ans);
 }
+
+int dc_model_set_pruning(dc_model* m, uint32_t on) {
+    if (!m) return DC_INVALID_ARG;
+    m->prune = on != 0;
+    return DC_OK;
+}
+
+int dc_model_set_truncation(dc_model* m, uint32_t on) {
+    if (!m) return DC_INVALID_ARG;
+    m->truncate = on != 0;
+    return DC_OK;
+}
+
+// Rows the last dc_model_prefill actually ran (after truncation), for throughput accounting.
+uint32_t dc_model_resident_rows(dc_model* m) { return m ? m->cur.rows : 0; }
 
 // Device address of a named activation buffer, for per-layer parity checks
 // (the reference's debug_layers, forward.rs:778-797).

@@ -9,6 +9,8 @@
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override);
 uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count);
+int dc_gemm_small(dc_ctx* ctx, cudaStream_t s, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k, uint32_t ldx,
+                  uint32_t ldw, uint32_t ldy, uint32_t epi);
 
 namespace {
 
@@ -136,6 +138,8 @@ extern "C" int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, 
     DC_REQUIRE(ctx, reinterpret_cast<uintptr_t>(y) % 16 == 0, "gemm (fast): y must be 16-byte aligned");
     if (epilogue == DC_EPI_SWIGLU_BF16 && swiglu_block != 16)
         return dc_fail(ctx, DC_UNSUPPORTED, "gemm (fast): the SwiGLU epilogue pairs columns 16 apart; swiglu_block = %u", swiglu_block);
+    // M <= 16 (answer rows): the weight-streaming kernel, as the reference's table picks gemm_nt_small (gemm_configs.rs:252-267)
+    if (m <= DC_GEMM_SMALL_MAX_M) return dc_gemm_small(ctx, s, x, w, y, m, n, k, ldx, ldw, ldy, epilogue);
     return dc_gemm_tc(ctx, s, x, w, y, m, n, k, ldx, ldw, ldy, epilogue, 0);
 }
 

@@ -494,20 +494,28 @@ int make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint3
                        rows, cols, ld);
     if (ctx->tmaps.size() >= 8192) ctx->tmaps.clear();
     ctx->tmaps.emplace(key, m);
+    ctx->tmap_encodes++;
     *out = m;
+    return DC_OK;
+}
+
+template <int BN, int EPI, typename Act>
+int opt_in(dc_ctx* ctx) {
+    using C = Cfg<BN>;
+    static bool attr_set[16] = {};
+    if (!attr_set[ctx->device & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, Act>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cannot opt in to %u bytes of shared memory: %s", C::kSmemBytes, cudaGetErrorString(e));
+        attr_set[ctx->device & 15] = true;
+    }
     return DC_OK;
 }
 
 template <int BN, int EPI, typename Act>
 int launch(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CUtensorMap& tw, void* y, const GemmArgs& a) {
     using C = Cfg<BN>;
-    static bool attr_set[16] = {};
     auto kern = gemm_tc_kernel<BN, EPI, Act>;
-    if (!attr_set[ctx->device & 15]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "gemm: cannot opt in to %u bytes of shared memory: %s", C::kSmemBytes, cudaGetErrorString(e));
-        attr_set[ctx->device & 15] = true;
-    }
+    if (int rc = opt_in<BN, EPI, Act>(ctx); rc != DC_OK) return rc;
     const uint32_t units = a.full_tiles + (a.m_tiles * a.n_tiles - a.full_tiles) * a.split;
     const uint32_t grid = units < static_cast<uint32_t>(ctx->sm_count) ? units : static_cast<uint32_t>(ctx->sm_count);
     kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tx, tw, y, a, ctx->status_dev);
@@ -528,7 +536,26 @@ int launch_epi(dc_ctx* ctx, cudaStream_t stream, const CUtensorMap& tx, const CU
     }
 }
 
+template <int BN>
+int warm_bn(dc_ctx* ctx) {
+    int rc = opt_in<BN, DC_EPI_STORE_F32, ActBF16>(ctx);
+    if (rc == DC_OK) rc = opt_in<BN, DC_EPI_ADD_F32, ActBF16>(ctx);
+    if (rc == DC_OK) rc = opt_in<BN, DC_EPI_STORE_BF16, ActF16>(ctx);
+    if (rc == DC_OK) rc = opt_in<BN, DC_EPI_STORE_BF16, ActBF16>(ctx);
+    if (rc == DC_OK) rc = opt_in<BN, DC_EPI_SWIGLU_BF16, ActF16>(ctx);
+    if (rc == DC_OK) rc = opt_in<BN, DC_EPI_SWIGLU_BF16, ActBF16>(ctx);
+    return rc;
+}
+
 }  // namespace
+
+// Every (tile width x epilogue x 16-bit type) variant made launchable now: the role of Gemm::warm_up
+// (crates/decide-engine/src/kernels/gemm.rs:89-107), which builds each pipeline before the first request.
+int dc_gemm_warm(dc_ctx* ctx) {
+    int rc = warm_bn<256>(ctx);
+    if (rc == DC_OK) rc = warm_bn<128>(ctx);
+    return rc;
+}
 
 namespace {
 // One warp; lane 0 waits on a barrier that never completes, with the same bounded wait every kernel here uses.
@@ -597,16 +624,34 @@ Plan best_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t bn_ove
 
 uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count) { return best_plan(m, n, k ? k : 2560, sm_count, 0).bn; }
 
+namespace {
+// DECIDE_GEMM_SPLIT caps the K split of tail-wave tiles (1 = never split); the fix-up sums at most 4 parts.
+uint32_t max_split_from_env() {
+    static const uint32_t v = [] {
+        const char* e = getenv("DECIDE_GEMM_SPLIT");
+        const int n = e ? atoi(e) : 4;
+        return static_cast<uint32_t>(n < 1 ? 1 : (n > 4 ? 4 : n));
+    }();
+    return v;
+}
+}  // namespace
+
 extern "C" uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split) {
-    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, 0);
+    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, 0, max_split_from_env());
+    if (tail_split) *tail_split = pl.split;
+    return pl.bn;
+}
+
+extern "C" uint32_t dc_gemm_plan_tile_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t bn, uint32_t* tail_split) {
+    if (bn != 128 && bn != 256) return 0;
+    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, bn, max_split_from_env());
     if (tail_split) *tail_split = pl.split;
     return pl.bn;
 }
 
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override) {
-    static const uint32_t max_split = getenv("DECIDE_GEMM_SPLIT") ? static_cast<uint32_t>(atoi(getenv("DECIDE_GEMM_SPLIT"))) : 4u;
-    const Plan pl = best_plan(m, n, k, static_cast<uint32_t>(ctx->sm_count), bn_override, max_split ? max_split : 1u);
+    const Plan pl = best_plan(m, n, k, static_cast<uint32_t>(ctx->sm_count), bn_override, max_split_from_env());
     const uint32_t bn = pl.bn;
     GemmArgs a;
     a.m = m;

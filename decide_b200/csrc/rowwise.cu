@@ -1,6 +1,8 @@
 // HBM-bound row kernels: RMSNorm, embedding gather, row gathers, the candidate-row logit head and
 // the gated RMSNorm. One warp per row (or per (row, head)), 128-bit loads and stores, shuffle
 // reductions. They replace kernels/rmsnorm.metal, embed.metal, head.metal and gnorm.metal.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -209,8 +211,9 @@ int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst
     if (!ctx) return DC_INVALID_ARG;
     DC_REQUIRE(ctx, src && dst, "convert: null operand");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned long long* counters = static_cast<unsigned long long*>(dc_workspace(ctx, 64));
-    if (!counters) return dc_fail(ctx, DC_CUDA_ERROR, "convert: no workspace");
+    void* ws = nullptr;
+    if (int rc = dc_get_workspace(ctx, 64, "convert", &ws); rc != DC_OK) return rc;
+    unsigned long long* counters = static_cast<unsigned long long*>(ws);
     cudaError_t e = cudaMemsetAsync(counters, 0, 32, s);
     if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "convert: %s", cudaGetErrorString(e));
     if (n) {
@@ -236,15 +239,15 @@ int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst
 // Device address of g_noalloc_counters on the current device, looked up once per device.
 static cudaError_t noalloc_counters(int device, unsigned long long** out) {
     constexpr int kMaxDevices = 64;
-    static unsigned long long* cached[kMaxDevices] = {};
+    static std::atomic<unsigned long long*> cached[kMaxDevices];   // threads may race on a device's first call: same value, stored atomically
     if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
-    if (!cached[device]) {
-        unsigned long long* p = nullptr;
+    unsigned long long* p = cached[device].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_counters);
         if (e != cudaSuccess) return e;
-        cached[device] = p;
+        cached[device].store(p, std::memory_order_release);
     }
-    *out = cached[device];
+    *out = p;
     return cudaSuccess;
 }
 

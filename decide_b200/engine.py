@@ -88,6 +88,19 @@ class Engine:
         """Enqueues the same pass over the inputs the last `logits(batch)` left on the device."""
         self._call("dc_model_forward_resident", _stream(stream), _u32p(batch.seq_start), batch.n_seq, len(batch.ans_rows))
 
+    def set_pruning(self, on: bool):
+        """Last-layer pruning to the answer rows (Forward::set_pruning, forward.rs:517-522); on by default."""
+        self._call("dc_model_set_pruning", int(on))
+
+    def set_truncation(self, on: bool):
+        """Stop each request after its last answer row (forward.rs:830-831); on by default."""
+        self._call("dc_model_set_truncation", int(on))
+
+    @property
+    def resident_rows(self) -> int:
+        """Rows the last `logits` call ran after truncation."""
+        return int(self.lib.dc_model_resident_rows(self.handle))
+
     def set_layer_limit(self, n: int):
         self._call("dc_model_set_layer_limit", n)
 

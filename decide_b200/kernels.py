@@ -172,6 +172,32 @@ class Device:
     def reserve_workspace(self, nbytes: int):
         self.call("dc_reserve_workspace", nbytes)
 
+    def set_workspace_frozen(self, on: bool):
+        """Frozen: an op that needs more scratch than is reserved raises instead of reallocating the workspace."""
+        self.call("dc_set_workspace_frozen", int(on))
+
+    def warm_up(self):
+        """Makes every kernel variant launchable now (Gemm::warm_up, kernels/gemm.rs:89-107)."""
+        self.call("dc_warm_up")
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self.lib.dc_workspace_bytes(self.handle))
+
+    @property
+    def alloc_count(self) -> int:
+        """Device/pinned allocations this context has made so far."""
+        return int(self.lib.dc_alloc_count(self.handle))
+
+    @property
+    def tmap_encodes(self) -> int:
+        """Tensor maps encoded so far (cache misses)."""
+        return int(self.lib.dc_tmap_encode_count(self.handle))
+
+    @property
+    def tmap_cache_size(self) -> int:
+        return int(self.lib.dc_tmap_cache_size(self.handle))
+
 
 class _Family:
     def __init__(self, dev: Device):
@@ -198,6 +224,13 @@ class Gemm(_Family):
         split = ctypes.c_uint32(0)
         bn = int(self.dev.lib.dc_gemm_plan_k(self.dev.handle, m, n, k, ctypes.byref(split)))
         return bn, int(split.value)
+
+    def plan_tile_k(self, m: int, n: int, k: int, bn: int) -> int:
+        """K split of the tail wave's tiles when the tile width is forced to `bn` (what gemm_tile follows)."""
+        split = ctypes.c_uint32(0)
+        got = int(self.dev.lib.dc_gemm_plan_tile_k(self.dev.handle, m, n, k, bn, ctypes.byref(split)))
+        assert got == bn, f"tile width {bn} is not one the fast GEMM has"
+        return int(split.value)
 
 
 class Norm(_Family):
@@ -254,6 +287,13 @@ class Attn(_Family):
         (`(p, col * 4)`), or None for no gate."""
         self.dev.call("dc_attention", _stream(stream), _ptr(q), _ptr(kc), _ptr(vc), _ptr(gate), _ptr(qpos), _ptr(y), rows, ldg, nq,
                       nkv, hd, _ptr(seq_start), n_seq, max_len)
+
+
+    def attention_rows(self, stream, q, kc, vc, gate, qpos, kv_start, y, rows, ldg, nq: int, nkv: int, hd: int = 128):
+        """The same for a few query rows scattered over the packed caches of a batch (the pruned last layer's call,
+        forward.rs:1176-1178): row r attends cache rows kv_start[r] .. kv_start[r] + qpos[r]."""
+        self.dev.call("dc_attention_rows", _stream(stream), _ptr(q), _ptr(kc), _ptr(vc), _ptr(gate), _ptr(qpos), _ptr(kv_start), _ptr(y),
+                      rows, ldg, nq, nkv, hd)
 
 
 class Conv(_Family):

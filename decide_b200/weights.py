@@ -69,6 +69,16 @@ class Dims:
         return total
 
 
+    def gemm_flops(self, rows: int, n_ans: int, pruned: bool) -> float:
+        """2*M*N*K over the projection GEMMs of one forward of `rows` rows; with `pruned`, the last (attention) layer
+        runs its k|v projection over all rows and everything else over the n_ans answer rows only."""
+        if not (pruned and self.is_full_attention(self.n_layers - 1)):
+            return self.gemm_flops_per_row() * rows
+        last = 2.0 * self.hidden * self.att_in_n + 2.0 * self.q_dim * self.hidden + 2.0 * self.hidden * 2 * self.inter + 2.0 * self.inter * self.hidden
+        kv = 2.0 * self.hidden * 2 * self.kv_dim
+        return (self.gemm_flops_per_row() - last) * rows + kv * rows + (last - kv) * n_ans
+
+
 # The dims the benchmark configs use, and the reference checkpoint's own dims cut to what the kernels
 # support (head_dim 128 only), for a second tested instantiation.
 BASELINE_DIMS = Dims()

@@ -18,7 +18,16 @@
  *    read), in the style of the reference's own C ABI (crates/decide-ane/src/lib.rs:22-35).
  *  - There is no CPU fallback: without a CUDA device dc_open fails.
  *  - A context is not thread-safe (the reference's Forward::logits takes &mut self,
- *    forward.rs:704); distinct contexts are independent.
+ *    forward.rs:704) and serves ONE stream at a time: its scratch workspace, the partial-sum
+ *    buffers of the split GEMM and their arrival counters are one per context, so two streams
+ *    running ops of one context concurrently race on them. Distinct contexts are independent.
+ *  - Ops that need scratch (dc_attention with seq_start, dc_gated_delta, dc_conv_gated_delta,
+ *    dc_convert_bf16_to_f16) take it from the context's workspace. If the workspace is too small
+ *    the op grows it: a cudaFree + cudaMalloc, i.e. a device-wide synchronisation inside the
+ *    call, which also fails under stream capture. To keep requests allocation-free, call
+ *    dc_reserve_workspace once with the largest demand (dc_gated_delta_scratch_bytes,
+ *    dc_attention_scratch_bytes), then dc_set_workspace_frozen(ctx, 1): from then on an op that
+ *    would have grown the workspace returns DC_INVALID_ARG instead. dc_model_* does both itself.
  */
 #ifndef DECIDE_CUDA_H
 #define DECIDE_CUDA_H
@@ -103,6 +112,22 @@ uint64_t dc_launch_count(dc_ctx* ctx);
 /* Grows the context's scratch workspace to at least `bytes` now, so that later calls do not
  * allocate (Gemm::warm_up's role for pipelines, gemm.rs:89-107). */
 int dc_reserve_workspace(dc_ctx* ctx, size_t bytes);
+/* on = 1: an op that needs more scratch than is reserved returns DC_INVALID_ARG (naming the demand)
+ * instead of freeing and reallocating the workspace; on = 0 restores growing on demand. */
+int dc_set_workspace_frozen(dc_ctx* ctx, uint32_t on);
+size_t dc_workspace_bytes(dc_ctx* ctx);
+/* Makes every kernel variant launchable now (opts each into its shared-memory size on this device), so
+ * that no request does it: Gemm::warm_up (kernels/gemm.rs:89-107; checked in engine.rs:168-172).
+ * dc_model_create calls it. */
+int dc_warm_up(dc_ctx* ctx);
+/* What the "nothing is allocated or encoded inside a request" rule can be checked with
+ * (device.rs:482-543 keeps the same kind of cache for pipelines): device/pinned allocations this
+ * context has made so far (open, workspace growth, dc_model_create), tensor maps encoded so far
+ * (cache misses), and the number of cached tensor maps. A second request of a shape the context has
+ * already served leaves all three unchanged. The cache is dropped whole when it reaches 8,192 maps. */
+uint64_t dc_alloc_count(dc_ctx* ctx);
+uint64_t dc_tmap_encode_count(dc_ctx* ctx);
+size_t dc_tmap_cache_size(dc_ctx* ctx);
 /* Number of SMs of the context's device. */
 int dc_sm_count(dc_ctx* ctx);
 
@@ -127,7 +152,12 @@ int dc_convert_bf16_to_f16(dc_ctx* ctx, void* stream, const void* src, void* dst
  *  - Limit: at most DC_NOALLOC_MAX_VALUES (2^32) values per call; larger n is refused with
  *    DC_INVALID_ARG and a message in `err` (split the tensor).
  *  - The first call on each device looks the array's device address up (cudaGetSymbolAddress);
- *    make that first call before any stream capture begins on that device.
+ *    make that first call before any stream capture begins on that device. With CUDA's lazy
+ *    module loading that first look-up and launch also make the driver load this library's
+ *    kernel image onto the device, which takes device memory: the guarantee "nothing is
+ *    allocated" holds from the SECOND call on a device onwards, so warm the entry point up (an
+ *    n = 0 call is enough) before the no-allocation regime starts. First calls on one device
+ *    may come from several threads at once (the look-up is idempotent and stored atomically).
  *  - All calls share the one array, which still holds the previous call's counts: it is cleared on
  *    `stream` at the start of every call. Two calls that overlap on the GPU (different streams, or
  *    host threads racing on one device) corrupt each other's report; serialise them.
@@ -142,7 +172,11 @@ int dc_convert_bf16_to_f16_noalloc(void* stream, const void* src, void* dst, siz
  * ldy in elements of Y's type. fp32 accumulation. Requires N%32==0, K%32==0, M>=1,
  * ldx,ldw >= K, ldy >= output columns. The fast (tcgen05) kernels also need ldx%8==0, ldw%8==0,
  * x,w 16-byte aligned, ldy%8==0 (bf16 outputs) or ldy%4==0 (fp32 outputs), y 16-byte aligned, and
- * swiglu_block == 16 for DC_EPI_SWIGLU_BF16 (as gemm_fast.metal hard-codes). */
+ * swiglu_block == 16 for DC_EPI_SWIGLU_BF16 (as gemm_fast.metal hard-codes).
+ * M <= DC_GEMM_SMALL_MAX_M runs the weight-streaming small-M kernel (the reference's gemm_nt_small,
+ * kernels/gemm_fast.metal:470-517, chosen for M <= 16 by gemm_configs.rs:252-267); larger M the tcgen05
+ * kernel. dc_gemm_tile always runs the tcgen05 kernel, whatever M. */
+#define DC_GEMM_SMALL_MAX_M 16u
 int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
             uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t swiglu_block);
 
@@ -155,6 +189,8 @@ uint32_t dc_gemm_plan(dc_ctx* ctx, uint32_t m, uint32_t n);
 /* The same for a given K (dc_gemm_plan assumes K = 2560): the tile width, and into *tail_split (may be NULL) the number of
  * parts the tiles of the last, partial wave are cut into along K (1 = whole tiles). */
 uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split);
+/* The plan dc_gemm_tile follows for a forced tile width bn (128 or 256; returns 0 otherwise). */
+uint32_t dc_gemm_plan_tile_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t bn, uint32_t* tail_split);
 
 /* ---- Norm::rmsnorm (kernels/norm.rs:23-33; spec cpu_ref.rs:11-22) ----
  * y[r] = x[rowmap[r]] * rsqrt(mean(x^2)+eps) * (add_one ? 1+w : w); x fp32, w fp32 [h], y bf16.
@@ -216,6 +252,15 @@ int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void* kc, const
                  const uint32_t* qpos, void* y, uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, uint32_t hd,
                  const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
 
+/* ---- Attn::attention for answer rows of a packed batch (the call of the pruned last layer,
+ * forward.rs:1176-1178: a few query rows at given positions over the whole cache) ----
+ * As dc_attention without seq_start, plus kv_start (u32 [rows], NULL = all 0): query row r attends
+ * cache rows kv_start[r] .. kv_start[r] + qpos[r], i.e. the cache rows of its own request in a
+ * packed batch. Built for few rows: one CTA per (row, kv head), fp32 throughout. nq / nkv <= 16. */
+int dc_attention_rows(dc_ctx* ctx, void* stream, const void* q, const void* kc, const void* vc, const float* gate,
+                      const uint32_t* qpos, const uint32_t* kv_start, void* y, uint32_t rows, uint32_t ldg, uint32_t nq,
+                      uint32_t nkv, uint32_t hd);
+
 /* ---- Conv::conv_silu_l2 (kernels/conv.rs:21-36; spec cpu_ref.rs:55-81) ----
  * Depthwise causal conv (kernel 4) + SiLU over the qkv columns 0..(2nk+nv)*128 of `t` rows of p (fp32,
  * row stride ldp); prev = the 3 raw rows before them (fp32 [3,conv_dim], oldest first; NULL = zeros);
@@ -244,6 +289,8 @@ int dc_gated_delta(dc_ctx* ctx, void* stream, const float* q, const float* k, co
                    float* o, uint32_t t, uint32_t ldab, uint32_t write_state, uint32_t nk, uint32_t nv, uint32_t dk,
                    uint32_t dv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);
 size_t dc_gated_delta_scratch_bytes(uint32_t t, uint32_t n_seq, uint32_t nv);
+/* Scratch dc_attention takes for packed batches (seq_start given): the transposed V of `rows` cache rows. */
+size_t dc_attention_scratch_bytes(uint32_t rows, uint32_t n_seq, uint32_t nkv);
 
 /* ---- Conv::conv_silu_l2 + Delta::gated_delta in one call (no single counterpart in the reference, which
  * encodes the two back to back: forward.rs:1214-1234) ----
@@ -316,11 +363,25 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
                      float* logits);
 
 /* The same pass over the inputs left on the device by the last dc_model_prefill of this batch:
- * only enqueues (no copies, no wait); the logits stay in the model's device buffer. */
+ * only enqueues (no copies, no wait); the logits stay in the model's device buffer. seq_start, n_seq
+ * and n_ans must be that batch's (DC_INVALID_ARG otherwise). */
 int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_start, uint32_t n_seq, uint32_t n_ans);
 
+/* Work skipping, both on by default as in the reference:
+ *  - truncation (forward.rs:830-831): a request is run only up to its last answer row; rows after it
+ *    cannot reach a logit. A request without answer rows runs whole.
+ *  - last-layer pruning (Forward::set_pruning, forward.rs:517-522, 1150-1186): when the last layer is
+ *    full attention, only its K/V are computed for every row; the q|gate projection, attention,
+ *    output projection, MLP and head run for the answer rows alone.
+ * Results must not depend on either switch beyond fp32 rounding. */
+int dc_model_set_pruning(dc_model* m, uint32_t on);
+int dc_model_set_truncation(dc_model* m, uint32_t on);
+/* Rows the last dc_model_prefill ran after truncation. */
+uint32_t dc_model_resident_rows(dc_model* m);
+
 /* Runs only the first `n` layers and skips the head when n < n_layers (0 restores all layers): the
- * residual stream after layer n-1 is then in buffer "x" (debug_layers, forward.rs:778-797). */
+ * residual stream after layer n-1 is then in buffer "x" (debug_layers, forward.rs:778-797). While a
+ * limit is set, pruning and truncation are off: every row of the residual is computed. */
 int dc_model_set_layer_limit(dc_model* m, uint32_t n);
 /* Device address of a named activation buffer: "x" (fp32 residual [rows,hidden]), "h", "p", "g",
  * "mlp", "xs", "logits". */

@@ -3,8 +3,9 @@
 TEST INFRASTRUCTURE ONLY (see oracle/cpu_ref.py). It composes oracle/cpu_ref.py in the order of
 the reference's Forward (crates/decide-engine/src/forward.rs:1191-1276 encode_layer / encode_mlp,
 1312-1328 head) over weights in the engine's fused layouts, with fp32 activations everywhere
-(`round_bf16=True` additionally rounds the GEMM inputs and 16-bit intermediates the way the engine
-stores them). Its purpose is to tie the two oracles together: tests check that this composition
+(`round_bf16=True` or `round_to="bf16" | "f16"` additionally rounds the GEMM inputs and 16-bit
+intermediates the way the engine stores them; `exact_inputs` names GEMMs whose input is NOT
+rounded, which is what feeding that GEMM the activation as a hi + lo pair of 16-bit values does). Its purpose is to tie the two oracles together: tests check that this composition
 agrees with the Hugging Face model code that reference/gold.py runs, which pins both the restated
 kernels' semantics and the fused weight layouts without a GPU. Slow; small cases only.
 """
@@ -21,15 +22,29 @@ def _w(t):
     return t.detach().float().cpu().numpy()
 
 
-def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, round_bf16: bool = False, layer_outputs=None):
-    """One request: ids [T] -> list of logits arrays (one per answer position)."""
-    r = cpu_ref.bf16_round if round_bf16 else (lambda a: a)
+def f16_round(a):
+    """Round-to-nearest-even f32 -> fp16 -> f32."""
+    return np.asarray(a, dtype=f32).astype(np.float16).astype(f32)
+
+
+def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, round_bf16: bool = False, layer_outputs=None,
+                   round_to: str | None = None, exact_inputs: tuple = ()):
+    """One request: ids [T] -> list of logits arrays (one per answer position).
+
+    exact_inputs: subset of ("in", "out", "gate_up", "down"): the projections whose 16-bit input is kept exact."""
+    if round_bf16:
+        round_to = "bf16"
+    rnd = {None: (lambda a: a), "bf16": cpu_ref.bf16_round, "f16": f16_round}[round_to]
+    r = rnd
+
+    def rin(name, a):
+        return a if name in exact_inputs else rnd(a)
     t = len(ids)
     emb = _w(embed)
     x = emb[np.asarray(ids, dtype=np.int64)].astype(f32)
     pos = np.arange(t)
     for l, lw in enumerate(fused_layers):
-        h = r(cpu_ref.rmsnorm(x, _w(lw["in_norm"]), d.hidden, True))
+        h = rin("in", cpu_ref.rmsnorm(x, _w(lw["in_norm"]), d.hidden, True))
         if not d.is_full_attention(l):
             ld = d.lin_in_n
             p = cpu_ref.gemm_nt(h, _w(lw["w_in"]), t, ld, d.hidden)
@@ -39,7 +54,7 @@ def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, ro
             state = np.zeros((d.gdn_nv, d.gdn_dv, d.gdn_dk), f32)
             o = cpu_ref.gated_delta(q, k, v, a, b, d.gdn_nv, _w(lw["a_log"]), _w(lw["dt_bias"]), state, t, d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv)
             z = np.ascontiguousarray(p[:, d.conv_dim:d.conv_dim + d.value_dim])
-            g = r(cpu_ref.gated_rmsnorm_silu(o, z, d.value_dim, _w(lw["gnorm"]), t, d.gdn_nv, d.gdn_dv))
+            g = rin("out", cpu_ref.gated_rmsnorm_silu(o, z, d.value_dim, _w(lw["gnorm"]), t, d.gdn_nv, d.gdn_dv))
             out_k = d.value_dim
         else:
             ld = d.att_in_n
@@ -52,12 +67,12 @@ def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, ro
             kc = r(cpu_ref.head_norm_rope(kh, _w(lw["k_norm"]), pos[:, None].repeat(d.nkv, 1), d.rot_dim, d.rope_theta))
             vc = r(p[:, vcol:vcol + d.kv_dim].reshape(t, d.nkv, d.head_dim))
             gate = p[:, d.q_dim:2 * d.q_dim] if d.attn_gate else None
-            g = r(cpu_ref.attention(qo, pos, kc, vc, gate, d.nq, d.nkv, d.head_dim))
+            g = rin("out", cpu_ref.attention(qo, pos, kc, vc, gate, d.nq, d.nkv, d.head_dim))
             out_k = d.q_dim
         x = (x + cpu_ref.gemm_nt(g, _w(lw["w_out"]), t, d.hidden, out_k)).astype(f32)
-        h = r(cpu_ref.rmsnorm(x, _w(lw["post_norm"]), d.hidden, True))
+        h = rin("gate_up", cpu_ref.rmsnorm(x, _w(lw["post_norm"]), d.hidden, True))
         gu = cpu_ref.gemm_nt(h, _w(lw["w_gu"]), t, 2 * d.inter, d.hidden)
-        mlp = r(cpu_ref.swiglu_interleaved(gu, t, 2 * d.inter, d.swiglu_block))
+        mlp = rin("down", cpu_ref.swiglu_interleaved(gu, t, 2 * d.inter, d.swiglu_block))
         x = (x + cpu_ref.gemm_nt(mlp, _w(lw["w_down"]), t, d.hidden, d.inter)).astype(f32)
         if layer_outputs is not None:
             layer_outputs.append(x.copy())

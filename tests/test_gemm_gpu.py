@@ -105,6 +105,72 @@ def test_config0_gate_up_swiglu(k):
     assert_close(got, _want(x, w, m, n, kk, 3), what="config 0", **BF16_TOL)
 
 
+# Shapes whose last, partial wave of tiles is cut along K (the down projection of the benchmark at 603 and
+# 2,307 rows; the same with an N tail; a forced 128-wide tile). (m, n, k, forced tile width or None)
+SPLIT_SHAPES = [(603, 2560, 9728, None), (2307, 2560, 9728, None), (603, 2592, 9728, None), (300, 2560, 9728, 128)]
+
+
+@pytest.mark.parametrize("m,n,kk,bn", SPLIT_SHAPES)
+def test_k_split_tail_wave(k, m, n, kk, bn, act):
+    """The tail-wave K split: parts park fp32 partials in the context's workspace and the last epilogue warp to
+    arrive sums them in part order. Every epilogue, both 16-bit types, M and N tails; each case runs twice and
+    the two results must be bit-identical (arrival order must not matter, the arrival counters must be back at
+    zero). The plan is asserted first so that this test cannot silently stop covering the split path."""
+    split = k.gemm.plan_tile_k(m, n, kk, bn) if bn else k.gemm.plan_k(m, n, kk)[1]
+    assert split >= 2, f"plan for {m}x{n}x{kk} no longer splits the tail wave (split {split}): pick another shape"
+    x, w = _operands(50 + m + n, m, n, kk, act=act)
+    acc = cpu_ref.gemm_nt(np32(x), np32(w), m, n, kk)
+    y0 = np32(randn(51, m, n))
+    for epi in (0, 1, 2, 3):
+        want = cpu_ref.swiglu_interleaved(acc, m, n, 16) if epi == 3 else (acc + y0 if epi == 2 else acc)
+        tol = F32_TOL if epi in (0, 2) else dict(atol=2e-3, rtol=half_ulp(act))
+        first = _run(k, x, w, m, n, kk, epi, y0=y0 if epi == 2 else None, bn=bn)
+        assert_close(first, want, what=f"split {split} epilogue {epi} {m}x{n}x{kk}", **tol)
+        again = _run(k, x, w, m, n, kk, epi, y0=y0 if epi == 2 else None, bn=bn)
+        assert np.array_equal(first, again), f"epilogue {epi}: two runs of a K-split GEMM differ"
+
+
+def test_k_split_full_batch_tail_rows(k):
+    """The benchmark's down projection at its full batch (38,592 rows): 3,020 tiles = 20 whole waves + 60 tail
+    tiles cut in two. Checked on the rows of the tail tiles (the last requests of the batch) and a band of whole-tile rows."""
+    from decide_b200.kernels import Epilogue
+
+    m, n, kk = 38592, 2560, 9728
+    bn, split = k.gemm.plan_k(m, n, kk)
+    assert split >= 2, f"plan for {m}x{n}x{kk} no longer splits the tail wave"
+    act = k.dev.act_torch
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn(m, kk, generator=g, device="cuda").to(act)
+    w = (torch.randn(n, kk, generator=g, device="cuda") * 0.02).to(act)
+    y = torch.randn(m, n, generator=g, device="cuda")
+    y0 = y.clone()
+    k.gemm.gemm(None, x, w, y, m, n, kk, kk, kk, n, Epilogue.AddF32)
+    k.dev.check_status()
+    for lo, hi in ((0, 256), (m - 1024, m)):
+        acc = cpu_ref.gemm_nt(np32(x[lo:hi]), np32(w), hi - lo, n, kk)
+        assert_close(np32(y[lo:hi]), acc + np32(y0[lo:hi]), what=f"rows {lo}..{hi}", **F32_TOL)
+
+
+@pytest.mark.parametrize("m", [1, 3, 6, 8, 9, 16])
+@pytest.mark.parametrize("n,kk,epi", [(19456, 2560, 3), (2560, 9728, 2), (8224, 2560, 0), (2560, 2048, 1), (10240, 2560, 0),
+                                      (32, 32, 0), (96, 160, 2), (64, 64, 3), (2560, 4096, 0)])
+def test_small_m_streaming_gemm(k, m, n, kk, epi, act):
+    """M <= 16 (the answer rows of the pruned last layer) runs the weight-streaming kernel (the reference's
+    gemm_nt_small): every projection shape of the model, all four epilogues, every K split (1, 2, 4, 8), row counts
+    on both sides of the MMA's 8-row halves, strided outputs with a canary."""
+    if m not in (3, 16) and n * kk > 2 ** 22 and (n, kk) != (2560, 9728):
+        pytest.skip("the large shapes run at M = 3 and 16 (and the down projection at every M)")
+    x, w = _operands(70 + m + n, m, n, kk, act=act)
+    y0 = np32(randn(71, m, n)) if epi == 2 else None
+    n_out = n // 2 if epi == 3 else n
+    got = _run(k, x, w, m, n, kk, epi, y0=y0, ldy=n_out + (0 if epi == 2 else 8))
+    tol = F32_TOL if epi in (0, 2) else dict(atol=2e-3, rtol=half_ulp(act))
+    assert_close(got, _want(x, w, m, n, kk, epi, y0), what=f"small-M {m}x{n}x{kk} epilogue {epi}", **tol)
+    # and it agrees with the tcgen05 kernel on the same operands to fp32 summation order
+    big = _run(k, x, w, m, n, kk, epi, y0=y0, bn=256)
+    assert_close(got, big, what="small-M vs tcgen05", **(dict(atol=1e-4, rtol=1e-5) if epi in (0, 2) else dict(atol=2e-3, rtol=2 * half_ulp(act))))
+
+
 @pytest.mark.parametrize("epi", [0, 1, 2, 3])
 @pytest.mark.parametrize("block", [16, 32])
 def test_baseline_kernel(k, epi, block, act):

@@ -113,6 +113,34 @@ def test_attention_scattered_query_positions(k):
     assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
 
 
+@pytest.mark.parametrize("gated", [True, False])
+def test_attention_rows_over_packed_caches(k, gated, act):
+    """The pruned last layer's attention: a few answer rows of several requests, each attending the cache rows of its own
+    request up to its position (1 key, a tile boundary, more than two tiles of 256), 4 query heads per kv head."""
+    nq, nkv, hd = 8, 2, 128
+    lens = [603, 1, 257, 700]
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    total = int(starts[-1])
+    kc = randn(61, total, nkv, hd).to(act)
+    vc = randn(62, total, nkv, hd).to(act)
+    picks = [(0, 602), (0, 0), (0, 255), (0, 256), (1, 0), (2, 256), (3, 699), (3, 511), (3, 512)]   # (request, position)
+    rows = len(picks)
+    q = randn(63, rows, nq, hd).to(act)
+    gate = randn(64, rows, nq * hd + 16) if gated else None
+    qpos = np.array([p for _, p in picks])
+    kv0 = np.array([starts[s] for s, _ in picks])
+    y = torch.full((rows + 1, nq * hd), 5.0, dtype=act, device="cuda")
+    k.attn.attention_rows(None, q.cuda(), kc.cuda(), vc.cuda(), gate.cuda() if gated else None, _u32(qpos), _u32(kv0), y, rows,
+                          gate.shape[1] if gated else 0, nq, nkv, hd)
+    k.dev.check_status()
+    for i, (s, p) in enumerate(picks):
+        lo, hi = int(starts[s]), int(starts[s + 1])
+        want = cpu_ref.attention(np32(q[i:i + 1]), np.array([p]), np32(kc[lo:hi]), np32(vc[lo:hi]),
+                                 np32(gate)[i:i + 1, :nq * hd] if gated else None, nq, nkv, hd)
+        assert_close(np32(y[i:i + 1]), want, atol=2e-3 if act == torch.bfloat16 else 3e-4, rtol=half_ulp(act), what=f"attention_rows {picks[i]}")
+    assert (np32(y[rows]) == 5.0).all()
+
+
 @pytest.fixture(params=["fast", "fast-mma", "baseline"])
 def attn_impl(request, k):
     """Packed-batch attention on the tcgen05 kernel (fast), the mma.sync flash kernel (fast-mma) and the warp-per-row baseline."""

@@ -75,6 +75,45 @@ def test_request_alone_equals_request_in_a_batch(dev):
     eng.close()
 
 
+def test_pruning_and_truncation_do_not_change_the_logits(dev):
+    """The reference's set_pruning invariance (forward.rs:517-522) and its tail truncation (forward.rs:830-831): the
+    last layer pruned to the answer rows (small-M GEMMs, answer-row attention) and requests cut after their last
+    answer row give the logits of the full pass to fp32 rounding. Ragged requests, answers in any order, a request
+    with a single answer at its last row, one with its answers early."""
+    sd, eng = make(SMALL, dev, 9, max_rows=1024, max_seqs=8, max_answers=32, max_cand=8)
+    lens = [70, 9, 131, 300]
+    parts = [synth_batch(SMALL, 1, n, seed=20 + n, n_answers=3, n_cand=5, max_cand=8) for n in lens]
+    starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    ans = [p.ans_rows + starts[i] for i, p in enumerate(parts)]
+    ans[1] = np.array([starts[1] + 8], np.uint32)                     # one answer, the request's last row
+    ans[3] = np.array([starts[3] + 40, starts[3] + 7, starts[3] + 41], np.uint32)   # early, unordered
+    cand = np.concatenate([parts[0].cand, parts[1].cand[:1], parts[2].cand, parts[3].cand])
+    ncand = np.concatenate([parts[0].ncand, parts[1].ncand[:1], parts[2].ncand, parts[3].ncand])
+    batch = Batch(np.concatenate([p.ids for p in parts]), starts, np.concatenate(ans).astype(np.uint32), cand, ncand)
+    got = {}
+    try:
+        for prune in (False, True):
+            for trunc in (False, True):
+                eng.set_pruning(prune)
+                eng.set_truncation(trunc)
+                got[prune, trunc] = eng.logits(batch)
+                assert eng.resident_rows == (64 + 9 + 125 + 42 if trunc else batch.rows)   # last answer row of a request + 1
+                eng.forward_resident(batch)      # the resident form runs the same layout
+                dev.check_status()
+    finally:
+        eng.set_pruning(True)
+        eng.set_truncation(True)
+    full = got[False, False]
+    d_trunc = np.abs(got[False, True] - full).max()
+    print(f"truncation alone: max |dlogit| {d_trunc:.2e} ({'bit-identical' if d_trunc == 0 else 'not bit-identical'})")
+    assert d_trunc < 1e-5, "truncation runs the same kernels on the kept rows"
+    for key in ((True, False), (True, True)):
+        assert np.abs(got[key] - full).max() < 2e-3, f"pruning changed the logits by {np.abs(got[key] - full).max():.2e}"
+    want, _ = gold_synth.gold_batch_logits(gold_synth.build_model(SMALL, sd), batch, 8)
+    check_parity(got[True, True], want, batch.ncand, "pruned + truncated")
+    eng.close()
+
+
 def test_engines_agree_on_the_whole_model(dev):
     """The same batch through the tcgen05 kernels (delta rule with the conv fused in, attention) and through
     the mma.sync kernels (separate conv): identical decisions, logits within a fraction of the gold tolerance."""
@@ -127,6 +166,111 @@ def test_full_model_parity(dev):
     got = eng.logits(batch)
     dl, dp = check_parity(got, want, batch.ncand, "full model")
     print(f"full model: max|dlogit| {dl:.5f} max|dp| {dp:.5f}; CPU gold {secs:.1f}s for 2 requests")
+    eng.close()
+
+
+def test_full_model_one_2307_token_request(dev):
+    """The long-document case of the benchmark: one 2,307-token request through all 36 layers (19 attention
+    tiles, 37 delta-rule chunks, GEMMs whose tail wave is K-split) against the fp32 CPU gold forward."""
+    dims = BASELINE_DIMS
+    sd, eng = make(dims, dev, 1, max_rows=2307, max_seqs=1, max_answers=4, max_cand=16)
+    model = gold_synth.build_model(dims, sd)
+    batch = synth_batch(dims, 1, 2307, seed=7, n_answers=3, n_cand=16, max_cand=16)
+    want, secs = gold_synth.gold_batch_logits(model, batch, 16)
+    got = eng.logits(batch)
+    dl, dp = check_parity(got, want, batch.ncand, "2,307-token request")
+    print(f"2,307-token request: max|dlogit| {dl:.5f} max|dp| {dp:.5f}; CPU gold {secs:.1f}s")
+    eng.close()
+
+
+def test_bf16_engine_matches_its_cpu_emulation(dev):
+    """bf16 as the 16-bit type misses the 0.02 logit bar over 36 layers, and that is the format, not a kernel:
+    the engine in bf16 mode reproduces the logits of the CPU forward that rounds the same tensors to bf16
+    (tests/golden/bf16_study.json, made by tests/golden/make_bf16_study.py), far more closely than either
+    matches the fp32 forward. The fp16 engine on the same request meets the bars."""
+    import json
+    from pathlib import Path
+
+    from decide_b200.kernels import Act
+    from tests.golden.make_bf16_study import study_batch, study_dims
+
+    study = json.loads((Path(__file__).parent / "golden" / "bf16_study.json").read_text())
+    dims = study_dims()
+    batch = study_batch(dims, study["tokens"], study["seed"])
+    fp32 = np.array(study["logits_fp32"], np.float32)
+    got = {}
+    for act in (Act.BF16, Act.F16):
+        dev.set_activation_dtype(act)
+        try:
+            sd, eng = make(dims, dev, study["seed"], max_rows=study["tokens"], max_seqs=1, max_answers=8, max_cand=16)
+            got[act] = eng.logits(batch)
+            eng.close()
+        finally:
+            dev.set_activation_dtype(Act.F16)
+    emu = np.array(study["logits_bf16"], np.float32)
+    d_emu = np.abs(got[Act.BF16] - emu).max()
+    d_fp32 = np.abs(got[Act.BF16] - fp32).max()
+    d_f16 = np.abs(got[Act.F16] - fp32).max()
+    print(f"bf16 engine: max|dlogit| {d_fp32:.4f} vs fp32 (CPU emulation of bf16: {study['variants']['bf16']['max_abs_dlogit_vs_fp32']:.4f}), "
+          f"{d_emu:.4f} vs the emulation; fp16 engine: {d_f16:.4f} vs fp32")
+    # the same rounding points, but every rounding decision sits on an fp32-vs-f64 knife edge somewhere: the two bf16
+    # forwards agree to well within the distance of either from fp32, and the fp16 engine is inside the bar
+    assert d_emu < 0.5 * max(d_fp32, study["variants"]["bf16"]["max_abs_dlogit_vs_fp32"])
+    assert d_f16 <= check.MAX_DLOGIT
+    assert d_fp32 < 0.25, "bf16 error is far beyond what the format explains"
+
+
+def test_second_forward_allocates_and_encodes_nothing(dev):
+    """Nothing is allocated, compiled or tensor-map-encoded inside a request once its shape has been served
+    (the reference checks the same for pipelines, engine.rs:168-172): across the second and third forward of a
+    batch the context's allocation count, its tensor-map encodes and cache size, and the device's free memory
+    stay put. A request that would need more scratch than the model reserved is refused, not served by a
+    hidden reallocation."""
+    import torch
+
+    from decide_b200.kernels import KernelError
+
+    sd, eng = make(SMALL, dev, 5, max_rows=512, max_seqs=4, max_answers=16, max_cand=8)
+    batch = synth_batch(SMALL, 3, 150, seed=6, n_answers=2, n_cand=8, max_cand=8)
+    first = eng.logits(batch)
+    torch.cuda.synchronize()
+    before = (dev.alloc_count, dev.tmap_encodes, dev.tmap_cache_size, dev.workspace_bytes, torch.cuda.mem_get_info()[0])
+    for _ in range(2):
+        again = eng.logits(batch)
+        eng.forward_resident(batch)
+    torch.cuda.synchronize()
+    after = (dev.alloc_count, dev.tmap_encodes, dev.tmap_cache_size, dev.workspace_bytes, torch.cuda.mem_get_info()[0])
+    assert after == before, f"a repeated forward changed (allocations, tensor-map encodes, cache size, workspace bytes, free memory): {before} -> {after}"
+    assert np.array_equal(first, again)
+    # frozen workspace: an op that needs more scratch than reserved is an error, and the workspace is untouched
+    dev.set_workspace_frozen(True)
+    try:
+        with pytest.raises(KernelError) as e:      # every op takes its scratch through the same call
+            dev.reserve_workspace(before[3] + (1 << 20))
+        assert e.value.code == 1 and "frozen" in str(e.value)
+        dev.reserve_workspace(before[3])           # what is already there is still handed out
+    finally:
+        dev.set_workspace_frozen(False)
+    assert dev.workspace_bytes == before[3]
+    eng.close()
+
+
+def test_model_refuses_a_changed_16_bit_type(dev):
+    """A model's weights are stored in the 16-bit type the context had at dc_model_create; flipping the type
+    afterwards is an error at the next forward, not fp16 bits read as bf16."""
+    from decide_b200.kernels import Act, KernelError
+
+    sd, eng = make(SMALL, dev, 5, max_rows=64, max_seqs=2, max_answers=4, max_cand=8)
+    ok = synth_batch(SMALL, 1, 20, seed=1, n_answers=2, n_cand=4, max_cand=8)
+    want = eng.logits(ok)
+    dev.set_activation_dtype(Act.BF16)
+    try:
+        with pytest.raises(KernelError) as e:
+            eng.logits(ok)
+        assert e.value.code == 1 and "16-bit type" in str(e.value)
+    finally:
+        dev.set_activation_dtype(Act.F16)
+    assert np.array_equal(eng.logits(ok), want)
     eng.close()
 
 

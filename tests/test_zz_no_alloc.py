@@ -51,6 +51,24 @@ def test_noalloc_matches_the_allocating_entry_point_twice(dev):
     assert lib.dc_convert_bf16_to_f16_noalloc(stream, src.data_ptr(), dst.data_ptr(), 0, None, err, len(err)) == 0
 
 
+def test_noalloc_leaves_free_memory_alone(dev):
+    """The property in the name: once the entry point has run on the device (the first call makes the driver
+    load the kernel image), further calls take no device memory."""
+    lib = dev.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    err = ctypes.create_string_buffer(256)
+    buf = _inputs(4).cuda()
+    assert lib.dc_convert_bf16_to_f16_noalloc(stream, buf.data_ptr(), buf.data_ptr(), 0, None, err, len(err)) == 0   # warm
+    assert lib.dc_convert_bf16_to_f16_noalloc(stream, buf.data_ptr(), buf.data_ptr(), buf.numel(), None, err, len(err)) == 0
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        src = buf   # no torch allocation inside the measured region
+        assert lib.dc_convert_bf16_to_f16_noalloc(stream, src.data_ptr(), src.data_ptr(), src.numel(), None, err, len(err)) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+
+
 def test_noalloc_refuses_more_than_its_limit(dev):
     lib = dev.lib
     err = ctypes.create_string_buffer(256)
