@@ -334,6 +334,79 @@ def run_engine(args):
         dist.destroy_process_group()
 
 
+def run_tp(args):
+    """Latency mode of the benchmark's config: ONE 2,307-token request, tensor-parallel over all ranks of the launch
+    (torch.distributed.run --nproc-per-node N bench.py --gpus N --tp). Prints its own JSON line: p50 / p95 of the forward
+    from host ids to host logits (max over ranks), the share of the all-reduces, and the logits against rank 0's
+    one-GPU engine on the same weights."""
+    import torch
+    import torch.distributed as dist
+
+    from decide_b200 import dist as ddist
+    from decide_b200.engine import Engine
+    from decide_b200.kernels import Device
+    from decide_b200.synth import synth_batch, synth_fused_on_device
+    from decide_b200.weights import BASELINE_DIMS as dims, tp_shard_layer
+
+    rank, local, world = ddist.env_rank()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    cuda = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=cuda)
+    uid = torch.zeros(128, dtype=torch.uint8, device=cuda)
+    if rank == 0:
+        uid = torch.frombuffer(bytearray(Device.tp_unique_id()), dtype=torch.uint8).to(cuda)
+    if world > 1:
+        dist.broadcast(uid, 0)
+    dev = Device(local)
+    dev.tp_init(bytes(uid.cpu().numpy().tobytes()), world, rank)
+    whole, embed, final_norm = synth_fused_on_device(dims, 1, cuda)   # the same weights on every rank
+    shard = [tp_shard_layer(whole[l], l, dims, world, rank) for l in range(dims.n_layers)] if world > 1 else whole
+    toks, nans = 2307, 3
+    one = synth_batch(dims, 1, toks, seed=7, n_answers=nans, n_cand=CANDS, max_cand=CANDS)
+    eng = Engine(dims, dev=dev, max_rows=toks, max_seqs=1, max_answers=nans, max_cand=CANDS, fused_layers=shard, embed=embed, final_norm=final_norm)
+    stream = torch.cuda.current_stream()
+    for _ in range(max(3, args.warmup)):
+        got = eng.logits(one)
+    eng.profile()
+    eng.set_profiling(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    samples = []
+    runs = max(10, args.steps)
+    for _ in range(runs):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0.record(stream)
+        eng.logits(one)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        samples.append(ddist.max_over_ranks(e0.elapsed_time(e1), cuda))
+    prof = {name: ms / runs for name, ms, _ in eng.profile()}
+    eng.set_profiling(False)
+    parity = None
+    if rank == 0:
+        ref_dev = Device(local)       # a second context on this GPU, outside the group: the one-GPU engine
+        ref = Engine(dims, dev=ref_dev, max_rows=toks, max_seqs=1, max_answers=nans, max_cand=CANDS, fused_layers=whole, embed=embed, final_norm=final_norm)
+        want = ref.logits(one)
+        ref.close()
+        parity = float(np.abs(got - want).max())
+        print(json.dumps({
+            "mode": "tensor-parallel single request", "tp": world, "tokens": toks, "runs": runs,
+            "p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)),
+            "all_reduce_ms_per_forward": prof.get("all_reduce", 0.0), "per_op_ms": dict(sorted(prof.items(), key=lambda kv: -kv[1])),
+            "max_abs_dlogit_vs_one_gpu": parity, "dtype": "f16" if dev.act.name == "F16" else "bf16",
+            "exchange": "ncclAllReduce of the fp32 [rows, 2560] partial sums after each out / down projection (72 per forward)"}))
+        if parity > 0.02:
+            raise SystemExit(f"tensor-parallel logits differ from the one-GPU engine by {parity}")
+    eng.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -342,9 +415,12 @@ def main():
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
     ap.add_argument("--no-latency", action="store_true", help="skip the single-request latency runs (for short profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU forward (weights are then drawn on the GPU)")
+    ap.add_argument("--tp", action="store_true", help="latency mode: one 2,307-token request, tensor-parallel over all ranks of the launch")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.tp:
+        run_tp(args)
     else:
         run_engine(args)
 

@@ -47,6 +47,8 @@ struct dc_ctx {
     bool workspace_frozen = false;   // an op that needs more scratch than is reserved fails instead of allocating
     uint64_t allocs = 0;             // device/pinned allocations this context made (dc_open, workspace growth)
     uint64_t tmap_encodes = 0;       // tensor maps encoded (cache misses)
+    void* tp_comm = nullptr;         // NCCL communicator of the tensor-parallel group (dc_tp_init), or null
+    uint32_t tp_world = 1, tp_rank = 0;
 };
 
 int dc_fail(dc_ctx* ctx, int code, const char* fmt, ...);

@@ -144,6 +144,7 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
 void dc_close(dc_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    dc_tp_destroy(ctx);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->workspace) cudaFree(ctx->workspace);

@@ -24,11 +24,13 @@ struct dc_model {
     uint32_t act_dtype = DC_ACT_F16;   // the context's 16-bit type when the model was created: the type its weights are stored in
     // derived
     uint32_t key_dim = 0, value_dim = 0, conv_dim = 0, lin_in_n = 0, q_dim = 0, kv_dim = 0, att_in_n = 0, p_ld = 0;
+    uint32_t gate_cols = 0;   // columns of each of the b and a blocks of the fused Gated DeltaNet projection: gdn_nv rounded up to 16
     // device buffers
     char* arena = nullptr;
     size_t arena_bytes = 0;
     float *x = nullptr, *p = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *xs = nullptr, *logits = nullptr,
           *inv_freq = nullptr;
+    float* xr = nullptr;      // tensor-parallel shard only: this rank's partial output of a row-split projection, all-reduced in place
     void *h = nullptr, *g = nullptr, *mlp = nullptr, *qo = nullptr, *kc = nullptr, *vc = nullptr;
     uint32_t *ids = nullptr, *pos = nullptr, *seq_start = nullptr, *ans_rows = nullptr, *cand = nullptr, *ncand = nullptr;
     // answer-row buffers of the pruned last layer (forward.rs:1150-1186): normed rows, q|gate projection, q, attention
@@ -119,7 +121,32 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
     const uint32_t n_run = m->layer_limit ? std::min(m->layer_limit, d.n_layers) : d.n_layers;
     // Last-layer pruning applies to a full run that ends in a head over answer rows, when the last layer is full attention.
     // A layer limit (the per-layer residual dump) turns it off: that caller wants every row of the residual.
-    const bool pruned = m->prune && m->layer_limit == 0 && n_ans > 0 && is_attention_layer(d, d.n_layers - 1);
+    // Tensor-parallel shard: the out / down projections see only this rank's input columns, so their outputs are partial
+    // sums. They go to `xr`, are all-reduced over the group, and join the residual inside the next norm (`pending`).
+    const bool tp = c->tp_world > 1;
+    bool pending = false;
+    auto norm = [&](const float* wn) -> int {
+        if (pending) {
+            pending = false;
+            return dc_add_rmsnorm(c, st, m->x, m->xr, wn, m->h, rows, H, d.eps, 1);
+        }
+        return dc_rmsnorm(c, st, m->x, wn, m->h, nullptr, rows, H, H, H, d.eps, 1);
+    };
+    auto project_back = [&](const char* name, const void* a, const void* wt, uint32_t kk) -> int {
+        if (!tp) {
+            Prof _p(m, s, name);
+            return dc_gemm(c, st, a, wt, m->x, rows, H, kk, kk, kk, H, DC_EPI_ADD_F32, d.swiglu_block);
+        }
+        {
+            Prof _p(m, s, name);
+            const int rc = dc_gemm(c, st, a, wt, m->xr, rows, H, kk, kk, kk, H, DC_EPI_STORE_F32, d.swiglu_block);
+            if (rc != DC_OK) return rc;
+        }
+        Prof _p(m, s, "all_reduce");
+        pending = true;
+        return dc_tp_all_reduce_f32(c, st, m->xr, static_cast<size_t>(rows) * H);
+    };
+    const bool pruned = m->prune && !tp && m->layer_limit == 0 && n_ans > 0 && is_attention_layer(d, d.n_layers - 1);
     for (uint32_t l = 0; l < n_run; ++l) {
         const dc_layer_weights& w = m->layers[l];
         if (pruned && l + 1 == d.n_layers) {
@@ -146,13 +173,13 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
             RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
             return DC_OK;
         }
-        RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.in_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
+        RUN("rmsnorm", norm(w.in_norm));
         uint32_t out_k;
         if (!is_attention_layer(d, l)) {
             const uint32_t ld = m->lin_in_n;
             RUN("gemm_gdn_in", dc_gemm(c, st, m->h, w.w_in, m->p, rows, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
             const float* b = m->p + m->conv_dim + m->value_dim;  // fused order qkv|z|b|a (config.rs:14-17)
-            const float* a = b + d.gdn_nv;
+            const float* a = b + m->gate_cols;
             if (dc_conv_gated_delta_supported(c)) {
                 // conv + SiLU + L2 norm inside the delta rule's first kernel: q, k, v never reach memory
                 RUN("gated_delta", dc_conv_gated_delta(c, st, m->p, nullptr, w.conv_w, a, b, w.a_log, w.dt_bias, nullptr, nullptr, m->o, rows, ld, 0,
@@ -177,11 +204,12 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
                                           d.nkv, d.head_dim, m->seq_start, n_seq, max_len));
             out_k = m->q_dim;
         }
-        RUN("gemm_out", dc_gemm(c, st, m->g, w.w_out, m->x, rows, H, out_k, out_k, out_k, H, DC_EPI_ADD_F32, d.swiglu_block));
-        RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.post_norm, m->h, nullptr, rows, H, H, H, d.eps, 1));
+        if (int rc = project_back("gemm_out", m->g, w.w_out, out_k); rc != DC_OK) return rc;
+        RUN("rmsnorm", norm(w.post_norm));
         RUN("gemm_gate_up", dc_gemm(c, st, m->h, w.w_gu, m->mlp, rows, 2 * d.inter, H, H, H, d.inter, DC_EPI_SWIGLU_BF16, d.swiglu_block));
-        RUN("gemm_down", dc_gemm(c, st, m->mlp, w.w_down, m->x, rows, H, d.inter, d.inter, d.inter, H, DC_EPI_ADD_F32, d.swiglu_block));
+        if (int rc = project_back("gemm_down", m->mlp, w.w_down, d.inter); rc != DC_OK) return rc;
     }
+    if (pending) RUN("add_partial", dc_add_rmsnorm(c, st, m->x, m->xr, nullptr, nullptr, rows, H, d.eps, 1));
     if (n_ans && n_run == d.n_layers) {
         RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows, m->xs, n_ans, H));
         RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
@@ -226,7 +254,6 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     if (d.full_attn_interval == 0 || d.swiglu_block != 16) return fail("full_attn_interval must be positive and swiglu_block 16");
     if (d.rot_dim % 8 || d.rot_dim > d.head_dim || d.rot_dim == 0) return fail("rotary dims must be a multiple of 8 within head_dim");
     if (max_rows == 0 || max_seqs == 0 || max_cand == 0) return fail("capacities must be positive");
-    if (d.gdn_nv % 4) return fail("the number of value heads must be a multiple of 4 (row alignment of the fused projection)");
 
     dc_model* m = new dc_model();
     m->ctx = ctx;
@@ -242,7 +269,8 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     m->key_dim = d.gdn_nk * d.gdn_dk;
     m->value_dim = d.gdn_nv * d.gdn_dv;
     m->conv_dim = 2 * m->key_dim + m->value_dim;
-    m->lin_in_n = m->conv_dim + m->value_dim + 2 * d.gdn_nv;
+    m->gate_cols = (d.gdn_nv + 15u) / 16u * 16u;
+    m->lin_in_n = m->conv_dim + m->value_dim + 2 * m->gate_cols;
     m->q_dim = d.nq * d.head_dim;
     m->kv_dim = d.nkv * d.head_dim;
     m->att_in_n = (d.attn_gate ? 2 : 1) * m->q_dim + 2 * m->kv_dim;
@@ -286,6 +314,7 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         {&m->mlpa, A * d.inter * 2},
         {reinterpret_cast<void**>(&m->ans_pos), A * 4},
         {reinterpret_cast<void**>(&m->ans_kv), A * 4},
+        {reinterpret_cast<void**>(&m->xr), ctx->tp_world > 1 ? R * d.hidden * 4 : 0},
     };
     size_t total = 0;
     for (auto& wnt : wants) total += align_up(wnt.bytes, 1024);

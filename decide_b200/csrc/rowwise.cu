@@ -75,6 +75,43 @@ rmsnorm_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, uin
     }
 }
 
+// x[r] += add[r]; then (y != null) y[r] = x[r] * rsqrt(mean(x^2) + eps) * (w or 1 + w). The partial-sum add of a tensor-parallel
+// group (the all-reduced output of a row-split projection joins the residual; the reference's ane_add_partial,
+// kernels/ane.metal:10-18) fused with the RMSNorm that follows it.
+template <typename Act>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, uint16_t* __restrict__ y, uint32_t rows,
+                   uint32_t h, float eps, uint32_t add_one) {
+    const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    float4* xr = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * h);
+    const float4* ar = reinterpret_cast<const float4*>(add + static_cast<size_t>(r) * h);
+    const uint32_t nv = h >> 2;
+    float ss = 0.0f;
+    for (uint32_t i = lane; i < nv; i += 32) {
+        float4 v = xr[i];
+        const float4 a = ar[i];
+        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        xr[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (!y) return;
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(h) + eps);
+    const float one = add_one ? 1.0f : 0.0f;
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    uint2* yr = reinterpret_cast<uint2*>(y + static_cast<size_t>(r) * h);
+    for (uint32_t i = lane; i < nv; i += 32) {
+        const float4 v = xr[i];   // this lane's own stores of the first pass
+        const float4 g = wr[i];
+        uint2 o;
+        o.x = Act::pack(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
+        o.y = Act::pack(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
+        yr[i] = o;
+    }
+}
+
 // out[t] = float(table[ids[t]]); embed.metal:4-13.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 embed_kernel(const uint32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table, float* __restrict__ out, uint32_t t,
@@ -314,6 +351,20 @@ int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* 
         rmsnorm_kernel<ActBF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(
             x, w, static_cast<uint16_t*>(y), rowmap, rows, h, ld_in, ld_out, eps, add_one);
     return dc_check_launch(ctx, "rmsnorm");
+}
+
+int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const float* w, void* y, uint32_t rows, uint32_t h, float eps,
+                   uint32_t add_one) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, x && add && (!y || w), "add_rmsnorm: null operand");
+    DC_REQUIRE(ctx, h % 4 == 0 && h > 0, "add_rmsnorm: H = %u must be a multiple of 4", h);
+    DC_REQUIRE(ctx, aligned16(x) && aligned16(add) && (!y || (aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0)), "add_rmsnorm: misaligned operand");
+    if (rows == 0) return DC_OK;
+    if (ctx->act_dtype == DC_ACT_F16)
+        add_rmsnorm_kernel<ActF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(x, add, w, static_cast<uint16_t*>(y), rows, h, eps, add_one);
+    else
+        add_rmsnorm_kernel<ActBF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(x, add, w, static_cast<uint16_t*>(y), rows, h, eps, add_one);
+    return dc_check_launch(ctx, "add_rmsnorm");
 }
 
 int dc_embed(dc_ctx* ctx, void* stream, const uint32_t* ids, const void* table, float* out, uint32_t t, uint32_t h) {

@@ -16,7 +16,7 @@ import torch
 
 from .kernels import Act, ConvertReport, Device, KernelError, _stream
 from .synth import Batch
-from .weights import LAYER_FIELDS, CDims, CLayerWeights, Dims, fuse_layer
+from .weights import LAYER_FIELDS, CDims, CLayerWeights, Dims, fuse_layer, tp_shard_layer
 
 
 def _u32p(a: np.ndarray):
@@ -29,16 +29,23 @@ class Engine:
                  max_seqs: int = 64, max_answers: int = 1024, max_cand: int = 16, fused_layers: list | None = None,
                  embed: torch.Tensor | None = None, final_norm: torch.Tensor | None = None):
         """Either `state_dict` (checkpoint names, CPU tensors) or already fused device tensors
-        (`fused_layers`, `embed`, `final_norm`) must be given."""
+        (`fused_layers`, `embed`, `final_norm`) must be given. `dims` are the WHOLE model's. When the device's
+        context belongs to a tensor-parallel group (`Device.tp_init`), this engine is that rank's shard: a state
+        dict is cut by `weights.tp_shard_layer`; fused layers given directly must already be the rank's slices."""
         self.dims = dims
         self.dev = dev or Device(0)
+        self.tp_world, self.tp_rank = self.dev.tp_world, self.dev.tp_rank
+        self.local_dims = dims.tp_local(self.tp_world) if self.tp_world > 1 else dims
         self.lib = self.dev.lib
         self.max_cand = max_cand
         cuda = torch.device("cuda", self.dev.device)
         if fused_layers is None:
             fused_layers = []
             for l in range(dims.n_layers):
-                fused_layers.append({k: v.to(cuda) for k, v in fuse_layer(state_dict, l, dims).items()})
+                lw = fuse_layer(state_dict, l, dims)
+                if self.tp_world > 1:
+                    lw = tp_shard_layer(lw, l, dims, self.tp_world, self.tp_rank)
+                fused_layers.append({k: v.to(cuda) for k, v in lw.items()})
             embed = state_dict["embed_tokens.weight"].to(torch.bfloat16).to(cuda)
             final_norm = state_dict["norm.weight"].to(torch.float32).to(cuda)
         # Weight matrices are stored in the context's 16-bit type. In fp16 mode the bf16 checkpoint values
@@ -59,7 +66,7 @@ class Engine:
         for l, lw in enumerate(fused_layers):
             for name in LAYER_FIELDS:
                 setattr(arr[l], name, lw[name].data_ptr() if name in lw else None)
-        cd = CDims.of(dims)
+        cd = CDims.of(self.local_dims)
         self.handle = self.lib.dc_model_create(self.dev.handle, ctypes.byref(cd), arr, embed.data_ptr(), final_norm.data_ptr(),
                                                max_rows, max_seqs, max_answers, max_cand)
         if not self.handle:

@@ -172,6 +172,33 @@ class Device:
     def reserve_workspace(self, nbytes: int):
         self.call("dc_reserve_workspace", nbytes)
 
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """A fresh 128-byte id for a tensor-parallel group: make it on one rank, hand it to all."""
+        lib = _lib.load()
+        buf, err = ctypes.create_string_buffer(128), ctypes.create_string_buffer(256)
+        rc = lib.dc_tp_unique_id(buf, err, len(err))
+        if rc != 0:
+            raise KernelError(rc, err.value.decode())
+        return buf.raw
+
+    def tp_init(self, unique_id: bytes, world: int, rank: int):
+        """Joins this context to a tensor-parallel group (collective: every rank calls it with the same id)."""
+        assert len(unique_id) == 128
+        self.call("dc_tp_init", ctypes.create_string_buffer(unique_id, 128), world, rank)
+
+    @property
+    def tp_world(self) -> int:
+        return int(self.lib.dc_tp_world(self.handle))
+
+    @property
+    def tp_rank(self) -> int:
+        return int(self.lib.dc_tp_rank(self.handle))
+
+    def tp_all_reduce_f32(self, t: torch.Tensor, stream=None):
+        assert t.dtype == torch.float32 and t.is_cuda and t.is_contiguous()
+        self.call("dc_tp_all_reduce_f32", _stream(stream), t.data_ptr(), t.numel())
+
     def set_workspace_frozen(self, on: bool):
         """Frozen: an op that needs more scratch than is reserved raises instead of reallocating the workspace."""
         self.call("dc_set_workspace_frozen", int(on))

@@ -46,7 +46,9 @@ class Dims:
     @property
     def conv_dim(self): return 2 * self.key_dim + self.value_dim
     @property
-    def lin_in_n(self): return self.conv_dim + self.value_dim + 2 * self.gdn_nv
+    def gate_cols(self): return -(-self.gdn_nv // 16) * 16   # columns of each of the b and a blocks: gdn_nv rounded up to 16
+    @property
+    def lin_in_n(self): return self.conv_dim + self.value_dim + 2 * self.gate_cols
     @property
     def q_dim(self): return self.nq * self.head_dim
     @property
@@ -56,6 +58,17 @@ class Dims:
 
     def is_full_attention(self, layer: int) -> bool:  # config.rs:39-41
         return (layer + 1) % self.full_attn_interval == 0
+
+    def tp_local(self, world: int) -> "Dims":
+        """The dims of one rank's shard in a tensor-parallel group of `world`: heads and the intermediate size divided,
+        hidden size, layer count and vocabulary whole."""
+        for name in ("nq", "nkv", "gdn_nk", "gdn_nv"):
+            if getattr(self, name) % world:
+                raise ValueError(f"{name} = {getattr(self, name)} does not divide over {world} ranks")
+        if self.inter % (32 * world):
+            raise ValueError(f"inter = {self.inter} must split into multiples of 32 over {world} ranks")
+        return Dims(**{**self.__dict__, "nq": self.nq // world, "nkv": self.nkv // world, "gdn_nk": self.gdn_nk // world,
+                       "gdn_nv": self.gdn_nv // world, "inter": self.inter // world})
 
     def gemm_flops_per_row(self) -> float:
         """2*N*K summed over the projection GEMMs of all layers, per token row."""
@@ -136,8 +149,9 @@ def fuse_layer(sd: dict, i: int, d: Dims) -> dict:
         assert out["w_in"].shape == (d.att_in_n, d.hidden)
     else:
         la = p + "linear_attn."
-        out["w_in"] = bf(torch.cat([sd[la + "in_proj_qkv.weight"], sd[la + "in_proj_z.weight"], sd[la + "in_proj_b.weight"],
-                                    sd[la + "in_proj_a.weight"]], dim=0))
+        pad = torch.zeros(d.gate_cols - d.gdn_nv, d.hidden, dtype=sd[la + "in_proj_b.weight"].dtype)   # b and a blocks are 16 columns wide
+        out["w_in"] = bf(torch.cat([sd[la + "in_proj_qkv.weight"], sd[la + "in_proj_z.weight"], sd[la + "in_proj_b.weight"], pad,
+                                    sd[la + "in_proj_a.weight"], pad], dim=0))
         out["conv_w"] = f32(sd[la + "conv1d.weight"].reshape(d.conv_dim, 4))
         out["a_log"] = f32(sd[la + "A_log"])
         out["dt_bias"] = f32(sd[la + "dt_bias"])
@@ -146,4 +160,47 @@ def fuse_layer(sd: dict, i: int, d: Dims) -> dict:
         assert out["w_in"].shape == (d.lin_in_n, d.hidden)
     out["w_gu"] = bf(interleave_gate_up(sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"], d.swiglu_block))
     out["w_down"] = bf(sd[p + "mlp.down_proj.weight"])
+    return out
+
+
+def tp_shard_layer(lw: dict, layer: int, d: Dims, world: int, rank: int) -> dict:
+    """Rank `rank`'s slice of one layer in the fused layouts (`lw` = fuse_layer's output for the whole model, `d` the
+    whole model's dims): in-projections and gate_up split by output row (per head, per gate|up block), out and down
+    projections by input column, per-head vectors by head; norm weights are replicated. The result is a fused layer of
+    the dims `d.tp_local(world)`, so that the sum over ranks of the out / down projections is the unsplit layer's.
+    The reference's precedent: the two-way split of each MLP between GPU and Neural Engine
+    (crates/decide-engine/src/forward.rs:270-303; convert.rs's ANE split set)."""
+    loc = d.tp_local(world)
+    rows = lambda t, lo, n: t[lo:lo + n]
+    out = {"in_norm": lw["in_norm"], "post_norm": lw["post_norm"]}
+    if d.is_full_attention(layer):
+        hd = d.head_dim
+        parts = [rows(lw["w_in"], rank * loc.q_dim, loc.q_dim)]
+        off = d.q_dim
+        if d.attn_gate:
+            parts.append(rows(lw["w_in"], off + rank * loc.q_dim, loc.q_dim))
+            off += d.q_dim
+        parts.append(rows(lw["w_in"], off + rank * loc.kv_dim, loc.kv_dim))
+        parts.append(rows(lw["w_in"], off + d.kv_dim + rank * loc.kv_dim, loc.kv_dim))
+        out["w_in"] = torch.cat(parts, dim=0).contiguous()
+        out["w_out"] = lw["w_out"][:, rank * loc.q_dim:(rank + 1) * loc.q_dim].contiguous()
+        out["q_norm"], out["k_norm"] = lw["q_norm"], lw["k_norm"]
+        assert out["w_in"].shape[0] == loc.att_in_n and hd == loc.head_dim
+    else:
+        kd, vd = d.key_dim, d.value_dim
+        seg = [(0, rank * loc.key_dim, loc.key_dim), (kd, rank * loc.key_dim, loc.key_dim), (2 * kd, rank * loc.value_dim, loc.value_dim)]
+        conv_rows = torch.cat([torch.arange(base + lo, base + lo + n) for base, lo, n in seg])
+        gate_pad = torch.zeros(loc.gate_cols - loc.gdn_nv, lw["w_in"].shape[1], dtype=lw["w_in"].dtype)
+        b0 = d.conv_dim + vd
+        out["w_in"] = torch.cat([lw["w_in"][conv_rows], rows(lw["w_in"], d.conv_dim + rank * loc.value_dim, loc.value_dim),
+                                 rows(lw["w_in"], b0 + rank * loc.gdn_nv, loc.gdn_nv), gate_pad,
+                                 rows(lw["w_in"], b0 + d.gate_cols + rank * loc.gdn_nv, loc.gdn_nv), gate_pad], dim=0).contiguous()
+        out["conv_w"] = lw["conv_w"][conv_rows].contiguous()
+        out["a_log"] = rows(lw["a_log"], rank * loc.gdn_nv, loc.gdn_nv).contiguous()
+        out["dt_bias"] = rows(lw["dt_bias"], rank * loc.gdn_nv, loc.gdn_nv).contiguous()
+        out["gnorm"] = lw["gnorm"]
+        out["w_out"] = lw["w_out"][:, rank * loc.value_dim:(rank + 1) * loc.value_dim].contiguous()
+        assert out["w_in"].shape[0] == loc.lin_in_n
+    out["w_gu"] = rows(lw["w_gu"], rank * 2 * loc.inter, 2 * loc.inter).contiguous()
+    out["w_down"] = lw["w_down"][:, rank * loc.inter:(rank + 1) * loc.inter].contiguous()
     return out

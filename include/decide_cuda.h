@@ -198,6 +198,30 @@ uint32_t dc_gemm_plan_tile_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, ui
 int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* y, const uint32_t* rowmap,
                uint32_t rows, uint32_t h, uint32_t ld_in, uint32_t ld_out, float eps, uint32_t add_one);
 
+/* ---- Ane::add_partial + Norm::rmsnorm in one pass (kernels/ane.rs:23, kernels/ane.metal:10-18; norm.rs:23-33) ----
+ * x[r] += add[r] over `rows` dense fp32 rows of h values (the summed partial outputs of a row-split
+ * projection join the residual), then, unless y is NULL, y[r] = rmsnorm(x[r]) as dc_rmsnorm writes it. */
+int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const float* w, void* y, uint32_t rows, uint32_t h,
+                   float eps, uint32_t add_one);
+
+/* ---- tensor-parallel group (no counterpart in the reference beyond its two-way GPU + Neural Engine MLP
+ * split with a partial-sum add, forward.rs:270-303, 1286-1309) ----
+ * One process and one context per GPU. dc_tp_unique_id makes a 128-byte id on one rank; the host hands
+ * it to every rank; dc_tp_init (collective: every rank calls it) joins the context to the group, NCCL
+ * being loaded with dlopen at that moment (DECIDE_NCCL_LIB names the library if it is not on the
+ * loader's path). A dc_model created on a context that is in a group of G > 1 is one RANK's SHARD: its
+ * dc_dims carry the rank's head counts and intermediate size (nq/G, nkv/G, gdn_nk/G, gdn_nv/G, inter/G,
+ * hidden whole), its weights are the matching slices (in-projections and gate_up by output row, out and
+ * down projections by input column), and its forward all-reduces the fp32 [rows, hidden] partial sums
+ * after each row-split projection. Embedding, norms, residual and head are replicated.
+ * dc_tp_all_reduce_f32 is that exchange (in place, enqueued on `stream`). */
+int dc_tp_unique_id(void* id128, char* err, size_t err_len);
+int dc_tp_init(dc_ctx* ctx, const void* id128, uint32_t world, uint32_t rank);
+int dc_tp_all_reduce_f32(dc_ctx* ctx, void* stream, float* buf, size_t n);
+uint32_t dc_tp_world(dc_ctx* ctx);
+uint32_t dc_tp_rank(dc_ctx* ctx);
+void dc_tp_destroy(dc_ctx* ctx);
+
 /* ---- Embed::embed (kernels/embed.rs:16-22) ---- out[t] = float(table[ids[t]]), table bf16 [vocab,h]. */
 int dc_embed(dc_ctx* ctx, void* stream, const uint32_t* ids, const void* table, float* out, uint32_t t, uint32_t h);
 

@@ -28,10 +28,13 @@ def f16_round(a):
 
 
 def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, round_bf16: bool = False, layer_outputs=None,
-                   round_to: str | None = None, exact_inputs: tuple = ()):
+                   round_to: str | None = None, exact_inputs: tuple = (), all_reduce=None):
     """One request: ids [T] -> list of logits arrays (one per answer position).
 
-    exact_inputs: subset of ("in", "out", "gate_up", "down"): the projections whose 16-bit input is kept exact."""
+    exact_inputs: subset of ("in", "out", "gate_up", "down"): the projections whose 16-bit input is kept exact.
+    all_reduce: for one rank's shard of a tensor-parallel group (d and fused_layers are the shard's): a function that
+    sums an fp32 array over the ranks; it is applied to the out and down projections before they join the residual."""
+    ar = all_reduce or (lambda a: a)
     if round_bf16:
         round_to = "bf16"
     rnd = {None: (lambda a: a), "bf16": cpu_ref.bf16_round, "f16": f16_round}[round_to]
@@ -50,7 +53,7 @@ def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, ro
             p = cpu_ref.gemm_nt(h, _w(lw["w_in"]), t, ld, d.hidden)
             q, k, v = cpu_ref.conv_silu_l2(p, ld, t, np.zeros((3, d.conv_dim), f32), _w(lw["conv_w"]), d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv)
             b = p[:, d.conv_dim + d.value_dim:d.conv_dim + d.value_dim + d.gdn_nv]
-            a = p[:, d.conv_dim + d.value_dim + d.gdn_nv:]
+            a = p[:, d.conv_dim + d.value_dim + d.gate_cols:d.conv_dim + d.value_dim + d.gate_cols + d.gdn_nv]
             state = np.zeros((d.gdn_nv, d.gdn_dv, d.gdn_dk), f32)
             o = cpu_ref.gated_delta(q, k, v, a, b, d.gdn_nv, _w(lw["a_log"]), _w(lw["dt_bias"]), state, t, d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv)
             z = np.ascontiguousarray(p[:, d.conv_dim:d.conv_dim + d.value_dim])
@@ -69,11 +72,11 @@ def forward_logits(d, fused_layers, embed, final_norm, ids, positions, cands, ro
             gate = p[:, d.q_dim:2 * d.q_dim] if d.attn_gate else None
             g = rin("out", cpu_ref.attention(qo, pos, kc, vc, gate, d.nq, d.nkv, d.head_dim))
             out_k = d.q_dim
-        x = (x + cpu_ref.gemm_nt(g, _w(lw["w_out"]), t, d.hidden, out_k)).astype(f32)
+        x = (x + ar(cpu_ref.gemm_nt(g, _w(lw["w_out"]), t, d.hidden, out_k))).astype(f32)
         h = rin("gate_up", cpu_ref.rmsnorm(x, _w(lw["post_norm"]), d.hidden, True))
         gu = cpu_ref.gemm_nt(h, _w(lw["w_gu"]), t, 2 * d.inter, d.hidden)
         mlp = rin("down", cpu_ref.swiglu_interleaved(gu, t, 2 * d.inter, d.swiglu_block))
-        x = (x + cpu_ref.gemm_nt(mlp, _w(lw["w_down"]), t, d.hidden, d.inter)).astype(f32)
+        x = (x + ar(cpu_ref.gemm_nt(mlp, _w(lw["w_down"]), t, d.hidden, d.inter))).astype(f32)
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
     xs = x[np.asarray(positions, dtype=np.int64)]

@@ -58,3 +58,76 @@ def test_gloo_ranks(world):
     assert all(v[0] == float(world) for v in results.values())          # the slowest rank's time everywhere
     assert results[0][1] == [[10.0 * i] * 4 for i in range(7)]           # rank order = request order
     assert all(results[r][1] is None for r in range(1, world))
+
+
+# ---------------------------------------------------------------------------------------------
+# Tensor-parallel partition arithmetic on CPU ranks: every rank cuts its shard of a small model with
+# weights.tp_shard_layer, runs the restated CPU forward over its shard with a gloo all-reduce where the
+# engine all-reduces (after the out and down projections), and must reproduce the unsplit forward.
+TP_DIMS = dict(hidden=64, n_layers=4, nq=4, nkv=2, head_dim=128, rot_dim=32, gdn_nk=2, gdn_nv=4, inter=128, vocab=50)
+
+
+def _tp_worker(rank, world, port, out):
+    from decide_b200.synth import synth_batch, synth_state_dict
+    from decide_b200.weights import Dims, fuse_layer, tp_shard_layer
+    from oracle import cpu_forward
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        d = Dims(**TP_DIMS)
+        sd = synth_state_dict(d, seed=5)
+        batch = synth_batch(d, 1, 21, seed=6, n_answers=2, n_cand=4, max_cand=4)
+        positions = [int(r) for r in batch.ans_rows]
+        cands = [batch.cand[i, :4] for i in range(2)]
+        fused = [fuse_layer(sd, l, d) for l in range(d.n_layers)]
+        local = [tp_shard_layer(fused[l], l, d, world, rank) for l in range(d.n_layers)]
+
+        def all_reduce(a):
+            t = torch.from_numpy(np.ascontiguousarray(a))
+            dist.all_reduce(t)
+            return t.numpy()
+
+        got = cpu_forward.forward_logits(d.tp_local(world), local, sd["embed_tokens.weight"], sd["norm.weight"], batch.ids, positions, cands,
+                                         all_reduce=all_reduce)
+        want = cpu_forward.forward_logits(d, fused, sd["embed_tokens.weight"], sd["norm.weight"], batch.ids, positions, cands)
+        out.put((rank, float(max(np.abs(g - w).max() for g, w in zip(got, want))), float(max(np.abs(w).max() for w in want))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_shards_reproduce_the_whole_model_on_gloo_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_tp_worker, args=(r, world, 29610, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, scale in results:
+        assert err < 1e-4 * max(scale, 1.0), f"rank {rank}: sharded forward differs from the whole model by {err:.3e}"
+
+
+def test_tp_local_dims_and_shapes():
+    from decide_b200.synth import synth_state_dict
+    from decide_b200.weights import BASELINE_DIMS, Dims, fuse_layer, tp_shard_layer
+
+    for world in (2, 4, 8):
+        loc = BASELINE_DIMS.tp_local(world)
+        assert (loc.nq, loc.nkv, loc.gdn_nv, loc.inter) == (32 // world, 8 // world, 16 // world, 9728 // world)
+        assert loc.lin_in_n % 32 == 0 and loc.att_in_n % 32 == 0 and loc.inter % 32 == 0 and loc.gate_cols == 16
+    with pytest.raises(ValueError):
+        BASELINE_DIMS.tp_local(3)
+    d = Dims(**TP_DIMS)
+    sd = synth_state_dict(d, seed=1)
+    for l in (0, 3):
+        whole = fuse_layer(sd, l, d)
+        parts = [tp_shard_layer(whole, l, d, 2, r) for r in range(2)]
+        loc = d.tp_local(2)
+        assert all(p["w_in"].shape == ((loc.att_in_n if d.is_full_attention(l) else loc.lin_in_n), d.hidden) for p in parts)
+        assert torch.equal(torch.cat([p["w_down"] for p in parts], dim=1), whole["w_down"])
+        assert torch.equal(torch.cat([p["w_gu"] for p in parts], dim=0), whole["w_gu"])
+        assert torch.equal(torch.cat([p["w_out"] for p in parts], dim=1), whole["w_out"])
