@@ -274,6 +274,24 @@ def test_model_refuses_a_changed_16_bit_type(dev):
     eng.close()
 
 
+def test_engine_from_a_converted_directory(dev, tmp_path):
+    """Engine::open's weight half: a decide-weights-v1 directory written by the converter, mapped and uploaded, gives
+    bit for bit the logits of the engine built from the state dict (same fp16 bits by both routes)."""
+    from decide_b200 import weight_files as wf
+
+    sd, eng = make(SMALL, dev, 33, max_rows=256, max_seqs=2, max_answers=8, max_cand=8)
+    batch = synth_batch(SMALL, 2, 80, seed=34, n_answers=3, n_cand=8, max_cand=8)
+    want = eng.logits(batch)
+    report = eng.convert_report.as_dict()
+    eng.close()
+    disk_report = wf.convert_state_dict(sd, SMALL, tmp_path)
+    assert (disk_report["f16_values"], disk_report["f16_subnormal"], disk_report["f16_flushed_to_zero"], disk_report["f16_overflow"]) == \
+        (report["values"], report["f16_subnormal"], report["f16_flushed_to_zero"], report["f16_overflow"])   # CPU converter = device converter
+    eng2 = wf.open_engine(tmp_path, dev=dev, max_rows=256, max_seqs=2, max_answers=8, max_cand=8)
+    assert np.array_equal(eng2.logits(batch), want)
+    eng2.close()
+
+
 def test_prefill_argument_checks(dev):
     from decide_b200.kernels import KernelError
 
