@@ -189,8 +189,9 @@ def tp_shard_layer(lw: dict, layer: int, d: Dims, world: int, rank: int) -> dict
     else:
         kd, vd = d.key_dim, d.value_dim
         seg = [(0, rank * loc.key_dim, loc.key_dim), (kd, rank * loc.key_dim, loc.key_dim), (2 * kd, rank * loc.value_dim, loc.value_dim)]
-        conv_rows = torch.cat([torch.arange(base + lo, base + lo + n) for base, lo, n in seg])
-        gate_pad = torch.zeros(loc.gate_cols - loc.gdn_nv, lw["w_in"].shape[1], dtype=lw["w_in"].dtype)
+        dev = lw["w_in"].device
+        conv_rows = torch.cat([torch.arange(base + lo, base + lo + n, device=dev) for base, lo, n in seg])
+        gate_pad = torch.zeros(loc.gate_cols - loc.gdn_nv, lw["w_in"].shape[1], dtype=lw["w_in"].dtype, device=dev)
         b0 = d.conv_dim + vd
         out["w_in"] = torch.cat([lw["w_in"][conv_rows], rows(lw["w_in"], d.conv_dim + rank * loc.value_dim, loc.value_dim),
                                  rows(lw["w_in"], b0 + rank * loc.gdn_nv, loc.gdn_nv), gate_pad,
