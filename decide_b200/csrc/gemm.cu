@@ -148,7 +148,7 @@ extern "C" int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, 
 extern "C" int dc_gemm_tile(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                             uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t bn) {
     if (!ctx) return DC_INVALID_ARG;
-    DC_REQUIRE(ctx, bn == 128 || bn == 256, "gemm: tile width %u is not 128 or 256", bn);
+    DC_REQUIRE(ctx, bn == 128 || bn == 192 || bn == 224 || bn == 256, "gemm: tile width %u is not 128, 192, 224 or 256", bn);
     DC_REQUIRE(ctx, x && w && y && m >= 1 && n % 32 == 0 && k % 32 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0 &&
                         epilogue <= DC_EPI_SWIGLU_BF16,
                "gemm: bad arguments");

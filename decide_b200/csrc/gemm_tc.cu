@@ -67,7 +67,7 @@ __device__ __forceinline__ Unit unit_of(uint32_t u, const GemmArgs& a) {
 
 template <int BN>
 struct Cfg {
-    static constexpr int kStages = (BN == 256) ? 4 : 6;
+    static constexpr int kStages = BN >= 224 ? 4 : (BN == 192 ? 5 : 6);   // what fits in 227 KB beside the epilogue staging
     static constexpr uint32_t kABytes = BM * BK * 2;
     static constexpr uint32_t kBBytes = BN * BK * 2;
     static constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -97,6 +97,24 @@ __device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
     return true;
 }
 
+
+// Bounded wait until an arrival counter in global memory reads `want` (ordered accumulation of K-split parts).
+__device__ __forceinline__ bool wait_turn(const volatile int* cnt, int want, volatile uint32_t* abort_flag, int* status, int code) {
+    if (*cnt == want) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (*cnt != want) {
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1u;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
 
 // One 32-row x 32-column chunk of the accumulator. tcgen05.ld hands each thread one ROW (32 columns);
 // stored like that, a warp instruction would touch 32 different 128-byte lines. The chunk goes through
@@ -154,7 +172,7 @@ __device__ __forceinline__ void epilogue_chunk(void* __restrict__ y, float* __re
 #pragma unroll
             for (int it = 0; it < 8; ++it) {   // all eight reads of the residual in flight before the first add
                 const size_t row = row0 + it * 4 + sub;
-                old[it] = row < m ? *reinterpret_cast<const float4*>(yf + row * ldy) : make_float4(0.f, 0.f, 0.f, 0.f);
+                old[it] = row < m ? __ldcg(reinterpret_cast<const float4*>(yf + row * ldy)) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -336,6 +354,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[acc]);
+            } else if constexpr (EPI == DC_EPI_ADD_F32 || EPI == DC_EPI_STORE_F32) {
+                // One part of a K-split tile with an fp32 output: the parts accumulate straight into Y, IN PART ORDER. Part 0
+                // runs the epilogue as given (store, or += residual); part p > 0 waits until part p - 1 has finished these 32
+                // rows, then adds its accumulator on top. ((y + p0) + p1) + ... is one fixed order of fp32 additions, so
+                // the result does not depend on timing. No workspace, and each part's epilogue is the normal coalesced one.
+                // The wait cannot deadlock: all parts of the tail wave are resident at once (one unit per CTA, grid <= SMs)
+                // and part 0 waits for nobody; it is bounded all the same.
+                const uint32_t rt = w.tile - a.full_tiles;
+                int* cnt = a.part_cnt + rt * 4u + q;
+                bool go = true;
+                if (w.part > 0) {
+                    if (lane == 0) go = wait_turn(cnt, static_cast<int>(w.part), abort_flag, status, 5);
+                    go = __shfl_sync(0xffffffffu, go ? 1 : 0, 0) != 0;
+                    __threadfence();
+                }
+                if (!go) break;
+#pragma unroll 1
+                for (uint32_t c = 0; c < BN / 32; ++c) {
+                    const uint32_t col0 = tn * BN + c * 32u;
+                    if (col0 >= a.n) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(taddr + c * 32u, r);
+                    tmem_ld_wait();
+                    if (w.part == 0) epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
+                    else epilogue_chunk<DC_EPI_ADD_F32, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
+                }
+                tc_fence_before_sync();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&acc_empty[acc]);
+                    __threadfence();
+                    atomicExch(cnt, w.part + 1u == a.split ? 0 : static_cast<int>(w.part) + 1);   // the last part leaves it at zero
+                }
             } else {
                 // One part of a K-split tile: park the raw accumulator in the workspace, laid out
                 // [part][32-column chunk][128 rows][32] so that every warp instruction moves 4 whole rows of
@@ -378,48 +430,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 if (prev == static_cast<int>(a.split) - 1) {
                     __threadfence();
                     const float* base = a.part_ws + static_cast<size_t>(rt * a.split) * kPartFloats + q * 32u * 32u;
-                    if constexpr (EPI == DC_EPI_ADD_F32 || EPI == DC_EPI_STORE_F32) {
-                        // fp32 outputs: the parts already sit in the layout the stores want (a warp instruction covers 4 whole
-                        // rows of the chunk), so they are summed and written straight out; the residual values of `+=` are
-                        // requested together with the parts, one round trip to L2 per chunk instead of two.
-                        float* yf = static_cast<float*>(y);
-#pragma unroll 1
-                        for (uint32_t c = 0; c < BN / 32; ++c) {
-                            const uint32_t col0 = tn * BN + c * 32u;
-                            if (col0 >= a.n) break;
-                            float4 sum[8];
-#pragma unroll
-                            for (int it = 0; it < 8; ++it) {
-                                const size_t row = row0 + it * 4 + sub;
-                                sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (EPI == DC_EPI_ADD_F32 && row < a.m) sum[it] = *reinterpret_cast<const float4*>(yf + row * a.ldy + col0 + 4 * l8);
-                            }
-                            float4 acc4[8];
-#pragma unroll
-                            for (int it = 0; it < 8; ++it) acc4[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                            for (uint32_t pt = 0; pt < 4; ++pt) {
-                                if (pt < a.split) {
-                                    const float* src = base + pt * kPartFloats + c * kChunkFloats;
-#pragma unroll
-                                    for (int it = 0; it < 8; ++it) {
-                                        const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (it * 4 + sub) * 32 + 4 * l8));
-                                        acc4[it].x += v.x;
-                                        acc4[it].y += v.y;
-                                        acc4[it].z += v.z;
-                                        acc4[it].w += v.w;
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int it = 0; it < 8; ++it) {
-                                const size_t row = row0 + it * 4 + sub;
-                                if (row < a.m)
-                                    *reinterpret_cast<float4*>(yf + row * a.ldy + col0 + 4 * l8) =
-                                        make_float4(sum[it].x + acc4[it].x, sum[it].y + acc4[it].y, sum[it].z + acc4[it].z, sum[it].w + acc4[it].w);
-                            }
-                        }
-                    } else
 #pragma unroll 1
                     for (uint32_t c = 0; c < BN / 32; ++c) {
                         const uint32_t col0 = tn * BN + c * 32u;
@@ -553,6 +563,8 @@ int warm_bn(dc_ctx* ctx) {
 // (crates/decide-engine/src/kernels/gemm.rs:89-107), which builds each pipeline before the first request.
 int dc_gemm_warm(dc_ctx* ctx) {
     int rc = warm_bn<256>(ctx);
+    if (rc == DC_OK) rc = warm_bn<224>(ctx);
+    if (rc == DC_OK) rc = warm_bn<192>(ctx);
     if (rc == DC_OK) rc = warm_bn<128>(ctx);
     return rc;
 }
@@ -585,46 +597,51 @@ int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, ui
 
 // Tile plan: the analogue of gemm_configs::plan (crates/decide-metal/src/gemm_configs.rs:312).
 // Whole waves of 128 x BN tiles run as whole tiles; the tiles of the last, partial wave are cut along
-// K into up to 4 parts so that wave fills the SMs as well. BN = 256 unless the narrower tile is
-// clearly cheaper under this model, calibrated on the B200: relative time = waves x tile width; a
-// 128-wide tile costs 0.9 of a 256-wide one (its operand feed, not its MMAs, sets its pace); the
-// fix-up of a split tile costs as much as ~45 k-blocks of main loop, so only long-K GEMMs split.
+// K into up to 4 parts so that wave fills the SMs as well. The tile width is the cheapest of 256, 224,
+// 192 and 128 under this model, calibrated on the B200: time = waves x (time of one tile); a narrower
+// tile takes kTileTime[] of a 256-wide one (its operand feed, not its MMAs, sets its pace, so 128
+// columns cost 0.9 of 256). A split tile costs its share of the main loop plus its epilogues: with an
+// fp32 output the parts add into Y one after the other, each epilogue worth ~kEpiF32 k-blocks of
+// main loop; with a 16-bit output the parts meet in a workspace and the last one to arrive sums them,
+// worth ~45 k-blocks, so only long-K GEMMs split there.
 namespace {
 struct Plan {
     uint32_t bn, full_tiles, split, kb_per_part;
     double cost;
 };
-Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t max_split = 4) {
+constexpr double kEpiF32 = 8.0, kFixup16 = 45.0;
+double tile_time(uint32_t bn) { return bn == 256 ? 1.0 : bn == 224 ? 0.94 : bn == 192 ? 0.90 : 0.90; }
+
+Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t epi, uint32_t max_split = 4) {
+    const bool f32_out = epi == DC_EPI_ADD_F32 || epi == DC_EPI_STORE_F32;
     const uint32_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
     const uint32_t k_blocks = (k + BK - 1) / BK;
     const uint32_t rest = tiles % sms;
     Plan p{bn, tiles - rest, 1, k_blocks, 0.0};
-    if (rest > 0) {
-        uint32_t split = sms / rest < max_split ? sms / rest : max_split;
-        while (split > 1 && k_blocks / split < 8) --split;
-        p.split = split ? split : 1;
-        p.kb_per_part = (k_blocks + p.split - 1) / p.split;
-    }
     auto tail_of = [&](uint32_t split) {
         const uint32_t per = (k_blocks + split - 1) / split;
-        return static_cast<double>(per) / k_blocks + (split > 1 ? 45.0 / k_blocks : 0.0);
+        if (split == 1) return 1.0;
+        return static_cast<double>(per) / k_blocks + (f32_out ? split * kEpiF32 : kFixup16) / k_blocks;
     };
-    while (p.split > 1 && tail_of(p.split) >= 1.0) --p.split;   // not worth it
+    if (rest > 0) {
+        const uint32_t cap = sms / rest < max_split ? sms / rest : max_split;
+        for (uint32_t split = 2; split <= cap; ++split)
+            if (k_blocks / split >= 8 && tail_of(split) < tail_of(p.split)) p.split = split;
+    }
     p.kb_per_part = (k_blocks + p.split - 1) / p.split;
     const double tail = rest == 0 ? 0.0 : tail_of(p.split);
-    p.cost = (tiles / sms + tail) * bn * (bn == 128 ? 1.8 : 1.0);
+    p.cost = (tiles / sms + tail) * tile_time(bn);
     return p;
 }
-Plan best_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t bn_override, uint32_t max_split = 4) {
-    if (bn_override) return plan_for(bn_override, m, n, k, sms, max_split);
-    const Plan a = plan_for(256, m, n, k, sms, max_split), b = plan_for(128, m, n, k, sms, max_split);
-    return b.cost < a.cost ? b : a;
+Plan best_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t bn_override, uint32_t epi, uint32_t max_split = 4) {
+    if (bn_override) return plan_for(bn_override, m, n, k, sms, epi, max_split);
+    Plan best = plan_for(256, m, n, k, sms, epi, max_split);
+    for (uint32_t bn : {224u, 192u, 128u}) {
+        const Plan c = plan_for(bn, m, n, k, sms, epi, max_split);
+        if (c.cost < best.cost * 0.98) best = c;   // a narrower tile has to win by a margin
+    }
+    return best;
 }
-}  // namespace
-
-uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count) { return best_plan(m, n, k ? k : 2560, sm_count, 0).bn; }
-
-namespace {
 // DECIDE_GEMM_SPLIT caps the K split of tail-wave tiles (1 = never split); the fix-up sums at most 4 parts.
 uint32_t max_split_from_env() {
     static const uint32_t v = [] {
@@ -634,24 +651,35 @@ uint32_t max_split_from_env() {
     }();
     return v;
 }
+// DECIDE_GEMM_BN forces a tile width for every shape (a measuring aid, like the reference's DECIDE_GEMM switches).
+uint32_t bn_from_env() {
+    static const uint32_t v = [] {
+        const char* e = getenv("DECIDE_GEMM_BN");
+        const int n = e ? atoi(e) : 0;
+        return static_cast<uint32_t>((n == 128 || n == 192 || n == 224 || n == 256) ? n : 0);
+    }();
+    return v;
+}
 }  // namespace
 
-extern "C" uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split) {
-    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, 0, max_split_from_env());
+uint32_t dc_gemm_plan_bn(uint32_t m, uint32_t n, uint32_t k, int sm_count) {
+    return best_plan(m, n, k ? k : 2560, sm_count, bn_from_env(), DC_EPI_STORE_F32, max_split_from_env()).bn;
+}
+
+extern "C" uint32_t dc_gemm_plan_for(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t epilogue, uint32_t bn, uint32_t* tail_split) {
+    if (bn != 0 && bn != 128 && bn != 192 && bn != 224 && bn != 256) return 0;
+    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, bn ? bn : bn_from_env(), epilogue, max_split_from_env());
     if (tail_split) *tail_split = pl.split;
     return pl.bn;
 }
 
-extern "C" uint32_t dc_gemm_plan_tile_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t bn, uint32_t* tail_split) {
-    if (bn != 128 && bn != 256) return 0;
-    const Plan pl = best_plan(m, n, k ? k : 2560, ctx ? static_cast<uint32_t>(ctx->sm_count) : 148u, bn, max_split_from_env());
-    if (tail_split) *tail_split = pl.split;
-    return pl.bn;
+extern "C" uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split) {
+    return dc_gemm_plan_for(ctx, m, n, k, DC_EPI_ADD_F32, 0, tail_split);
 }
 
 int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n,
                uint32_t k, uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epi, uint32_t bn_override) {
-    const Plan pl = best_plan(m, n, k, static_cast<uint32_t>(ctx->sm_count), bn_override, max_split_from_env());
+    const Plan pl = best_plan(m, n, k, static_cast<uint32_t>(ctx->sm_count), bn_override ? bn_override : bn_from_env(), epi, max_split_from_env());
     const uint32_t bn = pl.bn;
     GemmArgs a;
     a.m = m;
@@ -677,6 +705,10 @@ int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, v
     if (rc != DC_OK) return rc;
     rc = make_tmap(ctx, w, n, k, ldw, bn, f16, &tw);
     if (rc != DC_OK) return rc;
-    if (bn == 256) return launch_epi<256>(ctx, stream, tx, tw, y, a, epi);
-    return launch_epi<128>(ctx, stream, tx, tw, y, a, epi);
+    switch (bn) {
+        case 256: return launch_epi<256>(ctx, stream, tx, tw, y, a, epi);
+        case 224: return launch_epi<224>(ctx, stream, tx, tw, y, a, epi);
+        case 192: return launch_epi<192>(ctx, stream, tx, tw, y, a, epi);
+        default: return launch_epi<128>(ctx, stream, tx, tw, y, a, epi);
+    }
 }

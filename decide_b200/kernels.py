@@ -252,12 +252,12 @@ class Gemm(_Family):
         bn = int(self.dev.lib.dc_gemm_plan_k(self.dev.handle, m, n, k, ctypes.byref(split)))
         return bn, int(split.value)
 
-    def plan_tile_k(self, m: int, n: int, k: int, bn: int) -> int:
-        """K split of the tail wave's tiles when the tile width is forced to `bn` (what gemm_tile follows)."""
+    def plan_for(self, m: int, n: int, k: int, epi: Epilogue, bn: int = 0) -> tuple[int, int]:
+        """(tile width, K split of the tail wave's tiles) for a shape and epilogue; bn forces the width (as gemm_tile does)."""
         split = ctypes.c_uint32(0)
-        got = int(self.dev.lib.dc_gemm_plan_tile_k(self.dev.handle, m, n, k, bn, ctypes.byref(split)))
-        assert got == bn, f"tile width {bn} is not one the fast GEMM has"
-        return int(split.value)
+        got = int(self.dev.lib.dc_gemm_plan_for(self.dev.handle, m, n, k, int(epi), bn, ctypes.byref(split)))
+        assert got != 0, f"tile width {bn} is not one the fast GEMM has"
+        return got, int(split.value)
 
 
 class Norm(_Family):

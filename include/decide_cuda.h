@@ -180,17 +180,22 @@ int dc_convert_bf16_to_f16_noalloc(void* stream, const void* src, void* dst, siz
 int dc_gemm(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
             uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t swiglu_block);
 
-/* Test hooks for the fast GEMM: dc_gemm_tile forces the output tile width (128 or 256) that
- * dc_gemm_plan would otherwise choose per shape (the role of gemm_configs::plan,
- * crates/decide-metal/src/gemm_configs.rs:312, and of the reference's per-config test sweep). */
+/* Test hooks for the fast GEMM: dc_gemm_tile forces the output tile width (128, 192, 224 or 256) that
+ * the plan would otherwise choose per shape (the role of gemm_configs::plan,
+ * crates/decide-metal/src/gemm_configs.rs:312, and of the reference's per-config test sweep).
+ * DECIDE_GEMM_BN = 128 | 192 | 224 | 256 forces it for every dc_gemm of the process, DECIDE_GEMM_SPLIT = 1..4
+ * caps the K split of the tail wave. */
 int dc_gemm_tile(dc_ctx* ctx, void* stream, const void* x, const void* w, void* y, uint32_t m, uint32_t n, uint32_t k,
                  uint32_t ldx, uint32_t ldw, uint32_t ldy, uint32_t epilogue, uint32_t bn);
+/* The plan for a shape and epilogue: returns the tile width (bn = 0: the planner's choice; otherwise the plan
+ * dc_gemm_tile follows for that width; 0 is returned for a width the kernel does not have) and stores into
+ * *tail_split (may be NULL) the number of parts each tile of the last, partial wave is cut into along K
+ * (1 = whole tiles). With an fp32 output the parts accumulate into Y in part order; with a 16-bit output they
+ * meet in the context's workspace. Either way the result does not depend on timing. */
+uint32_t dc_gemm_plan_for(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t epilogue, uint32_t bn, uint32_t* tail_split);
+/* Shorthands: the tile width for K = 2560 and an fp32 store; width and split for a given K and the `+=` epilogue. */
 uint32_t dc_gemm_plan(dc_ctx* ctx, uint32_t m, uint32_t n);
-/* The same for a given K (dc_gemm_plan assumes K = 2560): the tile width, and into *tail_split (may be NULL) the number of
- * parts the tiles of the last, partial wave are cut into along K (1 = whole tiles). */
 uint32_t dc_gemm_plan_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t* tail_split);
-/* The plan dc_gemm_tile follows for a forced tile width bn (128 or 256; returns 0 otherwise). */
-uint32_t dc_gemm_plan_tile_k(dc_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t bn, uint32_t* tail_split);
 
 /* ---- Norm::rmsnorm (kernels/norm.rs:23-33; spec cpu_ref.rs:11-22) ----
  * y[r] = x[rowmap[r]] * rsqrt(mean(x^2)+eps) * (add_one ? 1+w : w); x fp32, w fp32 [h], y bf16.

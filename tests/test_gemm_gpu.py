@@ -59,7 +59,7 @@ def _run(k, x, w, m, n, kk, epi, ldy=None, y0=None, bn=None, block=16):
     return out[:, :n_out]
 
 
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 192, 224, 256])
 @pytest.mark.parametrize("m,n,kk", [(128, 256, 64), (128, 256, 256), (1, 32, 32), (37, 96, 160), (276, 512, 2560),
                                     (300, 8224, 512), (603, 2560, 1024)])
 def test_fast_store_f32_shapes(k, m, n, kk, bn, act):
@@ -70,7 +70,7 @@ def test_fast_store_f32_shapes(k, m, n, kk, bn, act):
 
 
 @pytest.mark.parametrize("epi", [0, 1, 2, 3])
-@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("bn", [128, 192, 224, 256])
 def test_fast_epilogues(k, epi, bn, act):
     m, n, kk = 276, 1024, 2560
     x, w = _operands(3, m, n, kk, act=act)
@@ -116,8 +116,10 @@ def test_k_split_tail_wave(k, m, n, kk, bn, act):
     arrive sums them in part order. Every epilogue, both 16-bit types, M and N tails; each case runs twice and
     the two results must be bit-identical (arrival order must not matter, the arrival counters must be back at
     zero). The plan is asserted first so that this test cannot silently stop covering the split path."""
-    split = k.gemm.plan_tile_k(m, n, kk, bn) if bn else k.gemm.plan_k(m, n, kk)[1]
-    assert split >= 2, f"plan for {m}x{n}x{kk} no longer splits the tail wave (split {split}): pick another shape"
+    from decide_b200.kernels import Epilogue
+
+    splits = {epi: k.gemm.plan_for(m, n, kk, Epilogue(epi), bn or 0)[1] for epi in (0, 1, 2, 3)}
+    assert min(splits.values()) >= 2, f"plan for {m}x{n}x{kk} no longer splits the tail wave for every epilogue ({splits}): pick another shape"
     x, w = _operands(50 + m + n, m, n, kk, act=act)
     acc = cpu_ref.gemm_nt(np32(x), np32(w), m, n, kk)
     y0 = np32(randn(51, m, n))
@@ -125,7 +127,7 @@ def test_k_split_tail_wave(k, m, n, kk, bn, act):
         want = cpu_ref.swiglu_interleaved(acc, m, n, 16) if epi == 3 else (acc + y0 if epi == 2 else acc)
         tol = F32_TOL if epi in (0, 2) else dict(atol=2e-3, rtol=half_ulp(act))
         first = _run(k, x, w, m, n, kk, epi, y0=y0 if epi == 2 else None, bn=bn)
-        assert_close(first, want, what=f"split {split} epilogue {epi} {m}x{n}x{kk}", **tol)
+        assert_close(first, want, what=f"split {splits[epi]} epilogue {epi} {m}x{n}x{kk}", **tol)
         again = _run(k, x, w, m, n, kk, epi, y0=y0 if epi == 2 else None, bn=bn)
         assert np.array_equal(first, again), f"epilogue {epi}: two runs of a K-split GEMM differ"
 
