@@ -407,6 +407,99 @@ def run_tp(args):
         dist.destroy_process_group()
 
 
+def cpu_config_seconds(cfg: int, gated: bool, repeats: int) -> tuple[float, int]:
+    """The same op sequence as decide_b200.bench_ops.config_case(cfg) in fp32 on the host cores with torch (the arithmetic
+    the reference's CPU gold path runs: F.linear in fp32, torch SDPA, the transformers chunk-64 delta rule). Best of `repeats`."""
+    import math
+
+    import torch
+    import torch.nn.functional as F
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    H, I, nq, nkv, hd, nk, nv = 2560, 9728, 32, 8, 128, 16, 16
+    m = {0: 276, 1: 603, 2: 2307, 3: 2307}[cfg]
+    g = torch.Generator().manual_seed(cfg)
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=g) * std
+    x, nw = rn(m, H), rn(H, std=0.02)
+    rms = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * (1.0 + w)
+    if cfg in (0, 1):
+        w_g, w_u, w_d = rn(I, H, std=0.02), rn(I, H, std=0.02), rn(H, I, std=0.02)
+        if cfg == 0:
+            fn = lambda: F.silu(F.linear(x, w_g)) * F.linear(x, w_u)
+        else:
+            def fn():
+                h = rms(x, nw)
+                return x + F.linear(F.silu(F.linear(h, w_g)) * F.linear(h, w_u), w_d)
+    elif cfg == 2:
+        qd, kvd = nq * hd, nkv * hd
+        w_in, w_o = rn((2 if gated else 1) * qd + 2 * kvd, H, std=0.02), rn(H, qd, std=0.02)
+        qw, kw = rn(hd, std=0.02), rn(hd, std=0.02)
+        ang = torch.arange(m, dtype=torch.float32)[:, None] * torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)])
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1)[:, None], torch.cat([ang.sin(), ang.sin()], -1)[:, None]
+        rot = lambda t: t * cos + torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1) * sin
+
+        def fn():
+            p = F.linear(rms(x, nw), w_in)
+            q = rot(rms(p[:, :qd].view(m, nq, hd), qw)).transpose(0, 1)[None]
+            kcol = (2 if gated else 1) * qd
+            kk = rot(rms(p[:, kcol:kcol + kvd].view(m, nkv, hd), kw)).transpose(0, 1)[None]
+            v = p[:, kcol + kvd:].view(m, nkv, hd).transpose(0, 1)[None]
+            y = F.scaled_dot_product_attention(q, kk, v, is_causal=True, enable_gqa=True)[0].transpose(0, 1).reshape(m, qd)
+            if gated:
+                y = y * torch.sigmoid(p[:, qd:2 * qd])
+            return x + F.linear(y, w_o)
+    else:
+        from transformers.models.qwen3_5.modeling_qwen3_5 import torch_chunk_gated_delta_rule
+
+        conv_dim, vd = (2 * nk + nv) * 128, nv * 128
+        w_in, w_out, cw = rn(conv_dim + vd + 2 * nv, H, std=0.02), rn(H, vd, std=0.02), rn(conv_dim, 1, 4, std=0.3)
+        a_log, dt, gw = torch.rand(nv, generator=g) * math.log(16.0), torch.ones(nv), torch.ones(128)
+
+        def fn():
+            p = F.linear(rms(x, nw), w_in)
+            qkv = F.silu(F.conv1d(p[:, :conv_dim].t()[None], cw, padding=3, groups=conv_dim)[0, :, :m]).t()
+            q, kk, v = qkv[:, :nk * 128].view(1, m, nk, 128), qkv[:, nk * 128:2 * nk * 128].view(1, m, nk, 128), qkv[:, 2 * nk * 128:].view(1, m, nv, 128)
+            beta = torch.sigmoid(p[:, conv_dim + vd:conv_dim + vd + nv])[None]
+            gdecay = (-a_log.exp() * F.softplus(p[:, conv_dim + vd + nv:] + dt))[None]
+            o, _ = torch_chunk_gated_delta_rule(q, kk, v, g=gdecay, beta=beta, initial_state=None, output_final_state=False, use_qk_l2norm_in_kernel=True)
+            o = o[0]
+            z = p[:, conv_dim:conv_dim + vd].view(m, nv, 128)
+            gg = (o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + 1e-6) * gw * F.silu(z)).reshape(m, vd)
+            return x + F.linear(gg, w_out)
+    best = float("inf")
+    with torch.inference_mode():
+        fn()
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+    return best, torch.get_num_threads()
+
+
+def run_config(args):
+    """`--config k`: one of the benchmark's single-block configs (0: gate_up GEMM at M = 276; 1: MLP block at M = 603; 2: attention layer
+    at M = 2,307, gated and un-gated; 3: Gated DeltaNet layer at M = 2,307), one JSON line each: GPU microseconds, TFLOP/s and the fraction
+    of the measured burst peak, beside the fp32 CPU time of the same op sequence."""
+    from decide_b200 import bench_ops
+    from decide_b200.kernels import Device, Kernels
+
+    dev = Device(0)
+    k = Kernels(dev)
+    peaks = measured_peaks()
+    for gated in ((True, False) if args.config == 2 else (True,)):
+        r = bench_ops.config_case(k, args.config, iters=max(args.steps, 10), warmup=max(args.warmup, 3), gated=gated)
+        sec, cores = cpu_config_seconds(args.config, gated, repeats=3)
+        print(json.dumps({
+            "metric": "block_forward_us", "value": r["us"], "unit": "us", "n_gpus": 1, "higher_is_better": False, "dtype": "f16" if dev.act.name == "F16" else "bf16",
+            "data": "synthetic", "config": {"workload": f"configs[{args.config}]: {r['what']}, M = {r['rows']}"},
+            "roofline": {"bound": "tensor", "achieved": r["tflops"], "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": r["tflops"] / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} (burst cuBLAS bf16; the sequence is timed alone)", "flops_per_pass": r["flops"],
+                         "note": "whole op sequence (norms, RoPE, attention / delta rule included) against the GEMM peak"},
+            "cpu_baseline": {"value": sec * 1e6, "unit": "us", "cores": cores, "kind": "port", "sample": "the same op sequence in fp32 with torch on the host cores, best of 3"},
+            "speedup_vs_cpu": sec * 1e6 / r["us"]}))
+    dev.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,10 +508,13 @@ def main():
     ap.add_argument("--impl", choices=["engine", "reference"], default="engine")
     ap.add_argument("--no-latency", action="store_true", help="skip the single-request latency runs (for short profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU forward (weights are then drawn on the GPU)")
+    ap.add_argument("--config", type=int, choices=[0, 1, 2, 3], default=None, help="measure one of the single-block configs instead of the full model")
     ap.add_argument("--tp", action="store_true", help="latency mode: one 2,307-token request, tensor-parallel over all ranks of the launch")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config is not None:
+        run_config(args)
     elif args.tp:
         run_tp(args)
     else:

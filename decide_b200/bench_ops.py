@@ -197,6 +197,83 @@ def attention(k, n_seq, tokens, nq, nkv, gated, iters, warmup):
     return {"op": "attention", "seqs": n_seq, "tokens": tokens, "gated": gated, "us": us, "flops": flops, "tflops": flops / us / 1e6}
 
 
+def config_case(k: Kernels, cfg: int, iters: int, warmup: int, gated: bool = True) -> dict:
+    """One of the benchmark's single-block configs as an op SEQUENCE on the GPU (weights ~N(0, 0.02), inputs ~N(0, 1)):
+      0  gate_up GEMM with SwiGLU, M = 276             1  MLP block, M = 603: RMSNorm -> gate_up (SwiGLU) -> down (+ residual)
+      2  attention layer, M = 2,307: RMSNorm -> in-projection -> q/k norm + RoPE -> causal GQA attention -> o-projection + residual
+      3  Gated DeltaNet layer, M = 2,307: RMSNorm -> in-projection -> conv + SiLU + L2 + chunk-64 delta rule -> gated RMSNorm -> out-projection + residual
+    Returns microseconds per pass and the algorithmic FLOPs of its GEMMs (+ the attention core)."""
+    act = k.dev.act_torch
+    H, I, nq, nkv, hd, nk, nv = 2560, 9728, 32, 8, 128, 16, 16
+    g = torch.Generator(device="cuda").manual_seed(cfg)
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=g, device="cuda") * std
+    wmat = lambda n, kk: rn(n, kk, std=0.02).to(act)
+    m = {0: 276, 1: 603, 2: 2307, 3: 2307}[cfg]
+    x = rn(m, H)
+    h = torch.empty(m, H, dtype=act, device="cuda")
+    nw = rn(H, std=0.02)
+    norm = lambda: k.norm.rmsnorm(None, x, nw, h, None, m, H, H, H, True)
+    if cfg in (0, 1):
+        w_gu, w_down = wmat(2 * I, H), wmat(H, I)
+        mlp = torch.empty(m, I, dtype=act, device="cuda")
+        gu = lambda: k.gemm.gemm(None, h, w_gu, mlp, m, 2 * I, H, H, H, I, Epilogue.SwigluBF16)
+        if cfg == 0:
+            h.copy_(rn(m, H).to(act))
+            fn, flops, what = gu, 2.0 * m * 2 * I * H, "gate_up GEMM + SwiGLU"
+        else:
+            def fn():
+                norm()
+                gu()
+                k.gemm.gemm(None, mlp, w_down, x, m, H, I, I, I, H, Epilogue.AddF32)
+            flops, what = 2.0 * m * 2 * I * H + 2.0 * m * H * I, "RMSNorm -> gate_up (SwiGLU) -> down + residual"
+    elif cfg == 2:
+        qd, kvd = nq * hd, nkv * hd
+        n_in = (2 if gated else 1) * qd + 2 * kvd
+        w_in, w_o = wmat(n_in, H), wmat(H, qd)
+        p = torch.empty(m, n_in, device="cuda")
+        qw, kw = rn(hd, std=0.02), rn(hd, std=0.02)
+        inv = torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)], device="cuda")
+        starts, pos = _seqs(1, m)
+        qo = torch.empty(m, nq, hd, dtype=act, device="cuda")
+        kc, vc = torch.empty(m, nkv, hd, dtype=act, device="cuda"), torch.empty(m, nkv, hd, dtype=act, device="cuda")
+        y = torch.empty(m, qd, dtype=act, device="cuda")
+        kcol = (2 if gated else 1) * qd
+
+        def fn():
+            norm()
+            k.gemm.gemm(None, h, w_in, p, m, n_in, H, H, H, n_in, Epilogue.StoreF32)
+            k.rope.q_norm_rope(None, p, qw, inv, pos, qo, m, n_in, nq, hd, hd)
+            k.rope.kv_norm_rope(None, p, kw, inv, kc, vc, m, n_in, kcol, kcol + kvd, 0, m, nkv, hd, hd, pos=pos)
+            k.attn.attention(None, qo, kc, vc, (p, qd * 4) if gated else None, pos, y, m, n_in, nq, nkv, hd, seq_start=starts, n_seq=1, max_len=m)
+            k.gemm.gemm(None, y, w_o, x, m, H, qd, qd, qd, H, Epilogue.AddF32)
+        flops = 2.0 * m * n_in * H + 2.0 * m * H * qd + 4.0 * hd * nq * m * (m + 1) / 2
+        what = f"attention layer, {'gated (N = 10240)' if gated else 'un-gated (N = 6144)'}"
+    else:
+        conv_dim, vd = (2 * nk + nv) * 128, nv * 128
+        n_in = conv_dim + vd + 2 * nv
+        w_in, w_out = wmat(n_in, H), wmat(H, vd)
+        p = torch.empty(m, n_in, device="cuda")
+        cw = rn(conv_dim, 4, std=0.3)
+        a_log = torch.rand(nv, generator=g, device="cuda") * math.log(16.0)
+        dt, gw = torch.ones(nv, device="cuda"), torch.ones(128, device="cuda")
+        o = torch.empty(m, nv, 128, device="cuda")
+        gg = torch.empty(m, vd, dtype=act, device="cuda")
+        starts, _ = _seqs(1, m)
+        b_col, a_col = conv_dim + vd, conv_dim + vd + nv
+
+        def fn():
+            norm()
+            k.gemm.gemm(None, h, w_in, p, m, n_in, H, H, H, n_in, Epilogue.StoreF32)
+            k.delta.conv_gated_delta(None, p, None, cw, (p, a_col * 4), (p, b_col * 4), a_log, dt, None, None, o, m, n_in, False, nk, nv,
+                                     seq_start=starts, n_seq=1, max_len=m)
+            k.gnorm.gated_rmsnorm_silu(None, o, (p, conv_dim * 4), gw, gg, m, n_in, nv)
+            k.gemm.gemm(None, gg, w_out, x, m, H, vd, vd, vd, H, Epilogue.AddF32)
+        flops, what = 2.0 * m * n_in * H + 2.0 * m * H * vd, "Gated DeltaNet layer"
+    us = _time(fn, iters, warmup)
+    k.dev.check_status()
+    return {"config": cfg, "what": what, "rows": m, "us": us, "flops": flops, "tflops": flops / us / 1e6}
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("op", choices=["gemm", "gemms", "rowwise", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "all"])
