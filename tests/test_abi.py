@@ -51,3 +51,19 @@ def test_gemm_plan_covers_engine_shapes():
     for n in (19456, 2560, 8224, 6144, 10240):
         for m in (1, 8, 16, 163, 276, 603, 2307, 38592):
             assert lib.dc_gemm_plan(None, m, n) in (128, 192, 224, 256)
+
+
+def test_rust_ffi_is_generated_from_the_header():
+    """crates/decide-cuda/src/ffi.rs is what crates/decide-cuda/gen_ffi.py makes of include/decide_cuda.h: one `pub fn` per
+    declared dc_* function, so the (uncompiled) Rust binding cannot drift from the ABI the tests exercise through ctypes."""
+    import importlib.util
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    spec = importlib.util.spec_from_file_location("gen_ffi", root / "crates" / "decide-cuda" / "gen_ffi.py")
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    text = (root / "crates" / "decide-cuda" / "src" / "ffi.rs").read_text()
+    assert text == gen.render(), "run `python crates/decide-cuda/gen_ffi.py` after changing include/decide_cuda.h"
+    declared = set(_lib.header_prototypes())
+    assert all(f"pub fn {name}(" in text for name in declared) and len(declared) >= 50
