@@ -95,6 +95,9 @@ extern "C" {
     pub fn dc_model_set_pruning(m: *mut DcModel, on: u32) -> i32;
     pub fn dc_model_set_truncation(m: *mut DcModel, on: u32) -> i32;
     pub fn dc_model_resident_rows(m: *mut DcModel) -> u32;
+    pub fn dc_model_set_chunk(m: *mut DcModel, rows: u32) -> i32;
+    pub fn dc_model_build_snapshot(m: *mut DcModel, stream: *mut c_void, prefix_ids: *const u32, n: u32) -> i32;
+    pub fn dc_model_last_route(m: *mut DcModel) -> u32;
     pub fn dc_model_set_layer_limit(m: *mut DcModel, n: u32) -> i32;
     pub fn dc_model_buffer(m: *mut DcModel, name: *const c_char) -> *mut c_void;
     pub fn dc_model_read_buffer(m: *mut DcModel, name: *const c_char, dst: *mut c_void, bytes: usize) -> i32;

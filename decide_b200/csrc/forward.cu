@@ -41,10 +41,26 @@ struct dc_model {
     // work skipping (the reference's defaults: both on)
     bool prune = true;      // last layer: everything after K/V for the answer rows only (set_pruning, forward.rs:517-522)
     bool truncate = true;   // each request stops after its last answer row (forward.rs:830-831)
+    // Chunked prefill of ONE request and the prefix snapshot (forward.rs:919-942, 645-673): state that outlives a chunk.
+    // Per Gated DeltaNet layer the 3 raw conv rows and the recurrent state, per attention layer its own K/V cache.
+    struct Carry {
+        char* mem = nullptr;
+        std::vector<void*> kc, vc;          // [layer] -> [max_rows, kv_dim] in the 16-bit type (null for linear layers)
+        std::vector<float*> conv, state;    // [layer] -> [3, conv_dim], [nv, dv, dk] (null for attention layers)
+    } carry, snap;
+    uint32_t chunk_rows = 0;                // 0 = one request runs whole (no carry needed)
+    std::vector<uint32_t> snap_ids;         // token ids of the captured prefix; empty = no snapshot
+    uint32_t last_route = 0;                // 0 full, 1 from the prefix snapshot
+    struct Chunk {
+        uint32_t c0, c1, a0, na;            // rows [c0, c1) of the request; its answers are sorted slots [a0, a0 + na)
+    };
     // the batch the last dc_model_prefill left on the device, as it was laid out after truncation
     struct Resident {
         std::vector<uint32_t> given_seq_start;   // what the caller passed
         uint32_t rows = 0, n_seq = 0, max_len = 0, n_ans = 0, given_rows = 0;
+        bool single = false;                     // ran through forward_single (chunks / snapshot)
+        uint32_t row0 = 0;                       // first row computed (the snapshot's length, or 0)
+        std::vector<Chunk> chunks;
     } cur;
     // pinned host staging for the host-buffer entry point
     char* host = nullptr;
@@ -217,6 +233,123 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
     return DC_OK;
 }
 
+bool ensure_carry(dc_model* m, dc_model::Carry& c) {
+    if (c.mem) return true;
+    const dc_dims& d = m->d;
+    const size_t kv = align_up(static_cast<size_t>(m->max_rows) * m->kv_dim * 2, 1024), cv = align_up(static_cast<size_t>(3) * m->conv_dim * 4, 1024),
+                 st = align_up(static_cast<size_t>(d.gdn_nv) * d.gdn_dv * d.gdn_dk * 4, 1024);
+    size_t total = 0;
+    for (uint32_t l = 0; l < d.n_layers; ++l) total += is_attention_layer(d, l) ? 2 * kv : cv + st;
+    cudaSetDevice(m->ctx->device);
+    if (cudaMalloc(&c.mem, total) != cudaSuccess) {
+        cudaGetLastError();
+        c.mem = nullptr;
+        return false;
+    }
+    m->ctx->allocs++;
+    c.kc.assign(d.n_layers, nullptr);
+    c.vc.assign(d.n_layers, nullptr);
+    c.conv.assign(d.n_layers, nullptr);
+    c.state.assign(d.n_layers, nullptr);
+    size_t off = 0;
+    for (uint32_t l = 0; l < d.n_layers; ++l) {
+        if (is_attention_layer(d, l)) {
+            c.kc[l] = c.mem + off;
+            c.vc[l] = c.mem + off + kv;
+            off += 2 * kv;
+        } else {
+            c.conv[l] = reinterpret_cast<float*>(c.mem + off);
+            c.state[l] = reinterpret_cast<float*>(c.mem + off + cv);
+            off += cv + st;
+        }
+    }
+    return true;
+}
+
+// Copies the carried state of rows [0, rows) from one Carry to another on the stream (snapshot capture and restore).
+int copy_carry(dc_model* m, cudaStream_t s, const dc_model::Carry& from, dc_model::Carry& to, uint32_t rows) {
+    const dc_dims& d = m->d;
+    cudaError_t e = cudaSuccess;
+    for (uint32_t l = 0; l < d.n_layers && e == cudaSuccess; ++l) {
+        if (is_attention_layer(d, l)) {
+            const size_t bytes = static_cast<size_t>(rows) * m->kv_dim * 2;
+            e = cudaMemcpyAsync(to.kc[l], from.kc[l], bytes, cudaMemcpyDeviceToDevice, s);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(to.vc[l], from.vc[l], bytes, cudaMemcpyDeviceToDevice, s);
+        } else {
+            e = cudaMemcpyAsync(to.conv[l], from.conv[l], static_cast<size_t>(3) * m->conv_dim * 4, cudaMemcpyDeviceToDevice, s);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(to.state[l], from.state[l], static_cast<size_t>(d.gdn_nv) * d.gdn_dv * d.gdn_dk * 4, cudaMemcpyDeviceToDevice, s);
+        }
+    }
+    if (e != cudaSuccess) return dc_fail(m->ctx, DC_CUDA_ERROR, "copying the carried state failed: %s", cudaGetErrorString(e));
+    return DC_OK;
+}
+
+// ONE request, chunk by chunk (encode_chunk over chunks(start, end), forward.rs:919-942, 1129-1142): all layers of a chunk,
+// then the next chunk. Linear layers carry their conv rows and recurrent state from chunk to chunk; attention layers append
+// the chunk's K/V rows to their own cache and attend over rows 0..=position. `row0 > 0` continues from state already in
+// `carry` (the restored prefix snapshot). The ids and absolute positions of the whole request are on the device.
+int forward_single(dc_model* m, cudaStream_t s, const std::vector<dc_model::Chunk>& chunks, uint32_t n_ans) {
+    dc_ctx* c = m->ctx;
+    const dc_dims& d = m->d;
+    const uint32_t H = d.hidden;
+    void* st = s;
+    DC_REQUIRE(c, c->act_dtype == m->act_dtype, "forward: the context's 16-bit type was changed after dc_model_create");
+    DC_REQUIRE(c, c->tp_world <= 1, "forward: chunked prefill and the prefix snapshot are not available on a tensor-parallel shard");
+    FreezeWorkspace frozen(c);
+    const uint32_t n_run = m->layer_limit ? std::min(m->layer_limit, d.n_layers) : d.n_layers;
+    const bool fused = dc_conv_gated_delta_supported(c) != 0;
+    for (const dc_model::Chunk& ch : chunks) {
+        const uint32_t n = ch.c1 - ch.c0;
+        const bool first = ch.c0 == 0;
+        RUN("embed", dc_embed(c, st, m->ids + ch.c0, m->embed, m->x, n, H));
+        for (uint32_t l = 0; l < n_run; ++l) {
+            const dc_layer_weights& w = m->layers[l];
+            RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.in_norm, m->h, nullptr, n, H, H, H, d.eps, 1));
+            uint32_t out_k;
+            if (!is_attention_layer(d, l)) {
+                const uint32_t ld = m->lin_in_n;
+                RUN("gemm_gdn_in", dc_gemm(c, st, m->h, w.w_in, m->p, n, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
+                const float* b = m->p + m->conv_dim + m->value_dim;
+                const float* a = b + m->gate_cols;
+                const float* prev = first ? nullptr : m->carry.conv[l];
+                const float* s_in = first ? nullptr : m->carry.state[l];
+                if (fused) {
+                    RUN("gated_delta", dc_conv_gated_delta(c, st, m->p, prev, w.conv_w, a, b, w.a_log, w.dt_bias, s_in, m->carry.state[l], m->o, n, ld, 1,
+                                                           d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, nullptr, 1, n));
+                } else {
+                    RUN("conv_silu_l2", dc_conv_silu_l2(c, st, m->p, prev, w.conv_w, m->q, m->k, m->v, n, ld, d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, nullptr, 1, n));
+                    RUN("gated_delta", dc_gated_delta(c, st, m->q, m->k, m->v, a, b, w.a_log, w.dt_bias, s_in, m->carry.state[l], m->o, n, ld, 1,
+                                                      d.gdn_nk, d.gdn_nv, d.gdn_dk, d.gdn_dv, nullptr, 1, n));
+                }
+                // the 3 raw rows that end this chunk, after the conv has read the old ones (conv.rs:38-46)
+                RUN("conv_state_update", dc_conv_state_update(c, st, m->p, prev, m->carry.conv[l], n, ld, m->conv_dim));
+                RUN("gated_rmsnorm_silu", dc_gated_rmsnorm_silu(c, st, m->o, m->p + m->conv_dim, w.gnorm, m->g, n, d.gdn_nv, d.gdn_dv, ld, d.eps));
+                out_k = m->value_dim;
+            } else {
+                const uint32_t ld = m->att_in_n;
+                const uint32_t kcol = d.attn_gate ? 2 * m->q_dim : m->q_dim;
+                RUN("gemm_attn_in", dc_gemm(c, st, m->h, w.w_in, m->p, n, ld, H, H, H, ld, DC_EPI_STORE_F32, d.swiglu_block));
+                RUN("q_norm_rope", dc_q_norm_rope(c, st, m->p, w.q_norm, m->inv_freq, m->pos + ch.c0, m->qo, n, ld, d.nq, d.head_dim, d.rot_dim, d.eps));
+                RUN("kv_norm_rope", dc_kv_norm_rope(c, st, m->p, w.k_norm, m->inv_freq, m->carry.kc[l], m->carry.vc[l], n, ld, kcol, kcol + m->kv_dim, ch.c0, nullptr,
+                                                    m->max_rows, d.nkv, d.head_dim, d.rot_dim, d.eps));
+                RUN("attention", dc_attention(c, st, m->qo, m->carry.kc[l], m->carry.vc[l], d.attn_gate ? m->p + m->q_dim : nullptr, m->pos + ch.c0, m->g, n, ld,
+                                              d.nq, d.nkv, d.head_dim, nullptr, 1, 0));
+                out_k = m->q_dim;
+            }
+            RUN("gemm_out", dc_gemm(c, st, m->g, w.w_out, m->x, n, H, out_k, out_k, out_k, H, DC_EPI_ADD_F32, d.swiglu_block));
+            RUN("rmsnorm", dc_rmsnorm(c, st, m->x, w.post_norm, m->h, nullptr, n, H, H, H, d.eps, 1));
+            RUN("gemm_gate_up", dc_gemm(c, st, m->h, w.w_gu, m->mlp, n, 2 * d.inter, H, H, H, d.inter, DC_EPI_SWIGLU_BF16, d.swiglu_block));
+            RUN("gemm_down", dc_gemm(c, st, m->mlp, w.w_down, m->x, n, H, d.inter, d.inter, d.inter, H, DC_EPI_ADD_F32, d.swiglu_block));
+        }
+        if (ch.na && n_run == d.n_layers)   // this chunk's answer rows (chunk-relative, sorted) into their slots
+            RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows + ch.a0, m->xs + static_cast<size_t>(ch.a0) * H, ch.na, H));
+    }
+    if (n_ans && n_run == d.n_layers)
+        RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
+    return DC_OK;
+}
+
 void collect_profile(dc_model* m) {
     for (auto& sp : m->spans) {
         float ms = 0.f;
@@ -365,6 +498,8 @@ void dc_model_destroy(dc_model* m) {
     collect_profile(m);
     for (auto e : m->event_pool) cudaEventDestroy(e);
     if (m->arena) cudaFree(m->arena);
+    if (m->carry.mem) cudaFree(m->carry.mem);
+    if (m->snap.mem) cudaFree(m->snap.mem);
     if (m->host) cudaFreeHost(m->host);
     delete m;
 }
@@ -485,6 +620,40 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
         memcpy(h_ncand, ncand, static_cast<size_t>(n_ans) * 4);
         memcpy(h_cand, cand, static_cast<size_t>(n_ans) * m->max_cand * 4);
     }
+    // One request may run chunk by chunk and / or start from the prefix snapshot (Forward's plan: Full | Snapshot,
+    // forward.rs:708-729). The snapshot serves a request that begins with the captured ids, is longer than them, and has
+    // every answer row past them.
+    const uint32_t P = static_cast<uint32_t>(m->snap_ids.size());
+    bool from_snapshot = n_seq == 1 && P > 0 && rows > P && m->layer_limit == 0 && std::equal(m->snap_ids.begin(), m->snap_ids.end(), h_ids);
+    for (uint32_t i = 0; from_snapshot && i < n_ans; ++i) from_snapshot = h_ans[i] >= P;
+    const bool single = n_seq == 1 && (m->chunk_rows > 0 || from_snapshot);
+    std::vector<uint32_t> order(n_ans);          // sorted slot -> the caller's answer index
+    std::vector<dc_model::Chunk> chunks;
+    if (single) {
+        for (uint32_t i = 0; i < n_ans; ++i) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) { return h_ans[x] < h_ans[y]; });
+        const uint32_t row0 = from_snapshot ? P : 0u, step = m->chunk_rows ? m->chunk_rows : rows - row0;
+        uint32_t slot = 0;
+        for (uint32_t c0 = row0; c0 < rows; c0 += step) {
+            dc_model::Chunk ch{c0, std::min(rows, c0 + step), slot, 0};
+            while (slot < n_ans && h_ans[order[slot]] < ch.c1) ++slot;
+            ch.na = slot - ch.a0;
+            chunks.push_back(ch);
+        }
+        // answers in sorted order: chunk-relative rows, candidates permuted alike
+        std::vector<uint32_t> rel(n_ans);
+        for (const auto& ch : chunks)
+            for (uint32_t a = ch.a0; a < ch.a0 + ch.na; ++a) rel[a] = h_ans[order[a]] - ch.c0;
+        for (uint32_t a = 0; a < n_ans; ++a) {
+            h_ncand[a] = ncand[order[a]];
+            memcpy(h_cand + static_cast<size_t>(a) * m->max_cand, cand + static_cast<size_t>(order[a]) * m->max_cand, static_cast<size_t>(m->max_cand) * 4);
+        }
+        memcpy(h_ans, rel.data(), static_cast<size_t>(n_ans) * 4);
+    }
+    m->last_route = from_snapshot ? 1u : 0u;
+    m->cur.single = single;
+    m->cur.row0 = from_snapshot ? P : 0u;
+    m->cur.chunks = chunks;
     m->cur.given_seq_start.assign(seq_start, seq_start + n_seq + 1);
     m->cur.rows = rows;
     m->cur.n_seq = n_seq;
@@ -502,7 +671,12 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
     if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->cand, h_cand, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: host-to-device copy failed: %s", cudaGetErrorString(e));
 
-    rc = forward_device(m, s, rows, n_seq, max_len, n_ans);
+    if (single) {
+        if (from_snapshot) rc = copy_carry(m, s, m->snap, m->carry, P);
+        if (rc == DC_OK) rc = forward_single(m, s, chunks, n_ans);
+    } else {
+        rc = forward_device(m, s, rows, n_seq, max_len, n_ans);
+    }
     if (rc != DC_OK) return rc;
     if (n_ans) {
         e = cudaMemcpyAsync(h_logits, m->logits, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyDeviceToHost, s);
@@ -511,7 +685,12 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
     rc = dc_check_status(ctx, s);  // synchronises
     if (rc != DC_OK) return rc;
     if (n_ans) {
-        memcpy(logits, h_logits, static_cast<size_t>(n_ans) * m->max_cand * 4);
+        if (single) {   // back from sorted slots to the caller's order
+            for (uint32_t a = 0; a < n_ans; ++a)
+                memcpy(logits + static_cast<size_t>(order[a]) * m->max_cand, h_logits + static_cast<size_t>(a) * m->max_cand, static_cast<size_t>(m->max_cand) * 4);
+        } else {
+            memcpy(logits, h_logits, static_cast<size_t>(n_ans) * m->max_cand * 4);
+        }
         // non-finite logits are an error, as forward.rs:906-913
         for (uint32_t i = 0; i < n_ans; ++i)
             for (uint32_t j = 0; j < ncand[i]; ++j)
@@ -531,8 +710,60 @@ int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_sta
     DC_REQUIRE(ctx, m->cur.n_seq == n_seq && m->cur.n_ans == n_ans && m->cur.given_seq_start.size() == static_cast<size_t>(n_seq) + 1 &&
                         std::equal(seq_start, seq_start + n_seq + 1, m->cur.given_seq_start.begin()),
                "forward_resident: this is not the batch the last dc_model_prefill left on the device");
-    return forward_device(m, static_cast<cudaStream_t>(stream), m->cur.rows, n_seq, m->cur.max_len, n_ans);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (m->cur.single) {
+        if (m->cur.row0) {
+            const int rc = copy_carry(m, s, m->snap, m->carry, m->cur.row0);
+            if (rc != DC_OK) return rc;
+        }
+        return forward_single(m, s, m->cur.chunks, n_ans);
+    }
+    return forward_device(m, s, m->cur.rows, n_seq, m->cur.max_len, n_ans);
 }
+
+// Forward::set_chunk (forward.rs:504-510): a single request runs in chunks of at most `rows` rows, all layers of a chunk
+// before the next, with the linear layers' state and the attention layers' K/V carried across (0 = whole requests).
+int dc_model_set_chunk(dc_model* m, uint32_t rows) {
+    if (!m) return DC_INVALID_ARG;
+    if (rows && !ensure_carry(m, m->carry)) return dc_fail(m->ctx, DC_CUDA_ERROR, "dc_model_set_chunk: cannot allocate the carried state");
+    m->chunk_rows = rows;
+    return DC_OK;
+}
+
+// Forward::build_snapshot (forward.rs:645-673): runs the constant prefix once and keeps every layer's state after it.
+// n = 0 drops the snapshot.
+int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_ids, uint32_t n) {
+    if (!m) return DC_INVALID_ARG;
+    dc_ctx* ctx = m->ctx;
+    m->snap_ids.clear();
+    if (n == 0) return DC_OK;
+    DC_REQUIRE(ctx, prefix_ids && n < m->max_rows, "build_snapshot: %u prefix rows (capacity %u)", n, m->max_rows);
+    for (uint32_t i = 0; i < n; ++i) DC_REQUIRE(ctx, prefix_ids[i] < m->d.vocab, "build_snapshot: token id %u out of the vocabulary", prefix_ids[i]);
+    if (!ensure_carry(m, m->carry) || !ensure_carry(m, m->snap)) return dc_fail(ctx, DC_CUDA_ERROR, "build_snapshot: cannot allocate the carried state");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    std::vector<uint32_t> pos(n);
+    for (uint32_t i = 0; i < n; ++i) pos[i] = i;
+    cudaError_t e = cudaMemcpyAsync(m->ids, prefix_ids, static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m->pos, pos.data(), static_cast<size_t>(n) * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);   // the staging vectors are pageable
+    if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "build_snapshot: copy failed: %s", cudaGetErrorString(e));
+    std::vector<dc_model::Chunk> chunks;
+    const uint32_t step = m->chunk_rows ? m->chunk_rows : n;
+    for (uint32_t c0 = 0; c0 < n; c0 += step) chunks.push_back({c0, std::min(n, c0 + step), 0, 0});
+    const uint32_t limit = m->layer_limit;
+    m->layer_limit = 0;
+    int rc = forward_single(m, s, chunks, 0);
+    m->layer_limit = limit;
+    if (rc == DC_OK) rc = copy_carry(m, s, m->carry, m->snap, n);
+    if (rc == DC_OK) rc = dc_check_status(ctx, s);
+    if (rc != DC_OK) return rc;
+    m->snap_ids.assign(prefix_ids, prefix_ids + n);
+    m->cur = dc_model::Resident();   // the device no longer holds a batch
+    return DC_OK;
+}
+
+// 0: the last dc_model_prefill ran every row; 1: it started from the prefix snapshot.
+uint32_t dc_model_last_route(dc_model* m) { return m ? m->last_route : 0; }
 
 int dc_model_set_pruning(dc_model* m, uint32_t on) {
     if (!m) return DC_INVALID_ARG;

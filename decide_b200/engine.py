@@ -103,6 +103,20 @@ class Engine:
         """Stop each request after its last answer row (forward.rs:830-831); on by default."""
         self._call("dc_model_set_truncation", int(on))
 
+    def set_chunk(self, rows: int):
+        """A single request runs in chunks of at most `rows` rows with carried state (Forward::set_chunk, forward.rs:504-510); 0 = whole."""
+        self._call("dc_model_set_chunk", rows)
+
+    def build_snapshot(self, prefix_ids, stream=None):
+        """Runs the constant prefix once and keeps the state after it (Forward::build_snapshot, forward.rs:645-673); later
+        single requests that begin with these ids skip them. An empty prefix drops the snapshot."""
+        ids = np.ascontiguousarray(prefix_ids, dtype=np.uint32)
+        self._call("dc_model_build_snapshot", _stream(stream), _u32p(ids) if len(ids) else None, len(ids))
+
+    @property
+    def last_route(self) -> str:
+        return ("full", "snapshot")[int(self.lib.dc_model_last_route(self.handle))]
+
     @property
     def resident_rows(self) -> int:
         """Rows the last `logits` call ran after truncation."""

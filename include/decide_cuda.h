@@ -408,6 +408,23 @@ int dc_model_set_truncation(dc_model* m, uint32_t on);
 /* Rows the last dc_model_prefill ran after truncation. */
 uint32_t dc_model_resident_rows(dc_model* m);
 
+/* Chunked prefill of ONE request (Forward::set_chunk, forward.rs:504-510, 919-942): with rows > 0 a
+ * batch of a single request runs in chunks of at most `rows` rows, chunk-major (all layers of a chunk,
+ * then the next chunk); Gated DeltaNet layers carry their 3 raw conv rows and their recurrent state
+ * from chunk to chunk, attention layers append each chunk's K/V rows to a cache of their own and attend
+ * over rows 0..=position. Results must not depend on the chunk size beyond fp32 rounding. rows = 0
+ * (default) runs requests whole. Batches of several requests always run whole. Allocates the carried
+ * state on first use (call it at set-up, not inside a request). Not available on a tensor-parallel shard. */
+int dc_model_set_chunk(dc_model* m, uint32_t rows);
+/* The prefix snapshot (Forward::build_snapshot, forward.rs:645-673, 237-247): runs the n prefix token ids
+ * (host memory) once and keeps every layer's state after them (per linear layer conv rows + recurrent
+ * state, per attention layer its K/V rows). A later single-request dc_model_prefill whose ids begin with
+ * that prefix, that is longer than it and whose answer rows all lie past it restores the state and runs
+ * only the remaining rows; any other request runs in full. n = 0 drops the snapshot. Synchronises. */
+int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_ids, uint32_t n);
+/* Route of the last dc_model_prefill: 0 = every row was run, 1 = it started from the prefix snapshot. */
+uint32_t dc_model_last_route(dc_model* m);
+
 /* Runs only the first `n` layers and skips the head when n < n_layers (0 restores all layers): the
  * residual stream after layer n-1 is then in buffer "x" (debug_layers, forward.rs:778-797). While a
  * limit is set, pruning and truncation are off: every row of the residual is computed. */

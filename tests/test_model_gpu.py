@@ -114,6 +114,45 @@ def test_pruning_and_truncation_do_not_change_the_logits(dev):
     eng.close()
 
 
+def test_chunk_size_and_snapshot_do_not_change_the_logits(dev):
+    """The reference's set_chunk invariance (forward.rs:504-510): one request run whole, in chunks of 64, 100 and 37 rows
+    (chunk boundaries inside and between delta-rule chunks, conv windows and attention tiles), and from a prefix snapshot
+    (forward.rs:645-673), gives the same logits to fp32 rounding; answers are given out of order. Then the gold."""
+    sd, eng = make(SMALL, dev, 41, max_rows=512, max_seqs=2, max_answers=16, max_cand=8)
+    one = synth_batch(SMALL, 1, 300, seed=42, n_answers=3, n_cand=8, max_cand=8)
+    one = Batch(one.ids, one.seq_start, np.array([295, 140, 268, 107], np.uint32), np.concatenate([one.cand, one.cand[:1]]), np.concatenate([one.ncand, one.ncand[:1]]))
+    whole = eng.logits(one)
+    assert eng.last_route == "full" and eng.resident_rows == 296
+    try:
+        for rows in (64, 100, 37):
+            eng.set_chunk(rows)
+            got = eng.logits(one)
+            d = np.abs(got - whole).max()
+            assert d < 2e-3, f"chunks of {rows} rows changed the logits by {d:.2e}"
+            eng.forward_resident(one)
+            dev.check_status()
+        eng.set_chunk(0)
+        eng.build_snapshot(one.ids[:107])
+        snap = eng.logits(one)
+        assert eng.last_route == "snapshot" and np.abs(snap - whole).max() < 2e-3
+        eng.set_chunk(50)                       # snapshot + chunks
+        both = eng.logits(one)
+        assert eng.last_route == "snapshot" and np.abs(both - whole).max() < 2e-3
+        other = synth_batch(SMALL, 1, 120, seed=43, n_answers=2, n_cand=8, max_cand=8)   # another prefix: full route
+        eng.logits(other)
+        assert eng.last_route == "full"
+        early = Batch(one.ids, one.seq_start, np.array([50, 295], np.uint32), one.cand[:2], one.ncand[:2])   # an answer inside the prefix
+        eng.logits(early)
+        assert eng.last_route == "full"
+    finally:
+        eng.set_chunk(0)
+        eng.build_snapshot([])
+    assert np.array_equal(eng.logits(one), whole)
+    want, _ = gold_synth.gold_batch_logits(gold_synth.build_model(SMALL, sd), one, 8)
+    check_parity(snap, want, one.ncand, "from the prefix snapshot")
+    eng.close()
+
+
 def test_engines_agree_on_the_whole_model(dev):
     """The same batch through the tcgen05 kernels (delta rule with the conv fused in, attention) and through
     the mma.sync kernels (separate conv): identical decisions, logits within a fraction of the gold tolerance."""
