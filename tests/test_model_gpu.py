@@ -224,39 +224,56 @@ def test_full_model_one_2307_token_request(dev):
 
 def test_bf16_engine_matches_its_cpu_emulation(dev):
     """bf16 as the 16-bit type misses the 0.02 logit bar over 36 layers, and that is the format, not a kernel:
-    the engine in bf16 mode reproduces the logits of the CPU forward that rounds the same tensors to bf16
-    (tests/golden/bf16_study.json, made by tests/golden/make_bf16_study.py), far more closely than either
-    matches the fp32 forward. The fp16 engine on the same request meets the bars."""
+    (1) after ONE layer the engine in bf16 mode sits on top of the CPU forward that rounds the same tensors to bf16
+    (the same rounding points give the same values), several times closer than either is to fp32;
+    (2) over all 36 layers its logit error against fp32 has the size the CPU emulation predicts
+    (tests/golden/bf16_study.json, made by tests/golden/make_bf16_study.py); the two bf16 results are not equal there,
+    because each rounding decision downstream hangs on fp32-vs-f64 differences and the errors decorrelate;
+    (3) the fp16 engine on the same request meets the bar."""
     import json
     from pathlib import Path
 
     from decide_b200.kernels import Act
+    from decide_b200.weights import fuse_layer
+    from oracle import cpu_forward
     from tests.golden.make_bf16_study import study_batch, study_dims
 
     study = json.loads((Path(__file__).parent / "golden" / "bf16_study.json").read_text())
     dims = study_dims()
-    batch = study_batch(dims, study["tokens"], study["seed"])
+    T = study["tokens"]
+    batch = study_batch(dims, T, study["seed"])
     fp32 = np.array(study["logits_fp32"], np.float32)
-    got = {}
+    got, x1 = {}, None
     for act in (Act.BF16, Act.F16):
         dev.set_activation_dtype(act)
         try:
-            sd, eng = make(dims, dev, study["seed"], max_rows=study["tokens"], max_seqs=1, max_answers=8, max_cand=16)
+            sd, eng = make(dims, dev, study["seed"], max_rows=T, max_seqs=1, max_answers=8, max_cand=16)
             got[act] = eng.logits(batch)
+            if act == Act.BF16:
+                eng.set_layer_limit(1)
+                eng.logits(batch)
+                x1 = eng.buffer("x", (T, dims.hidden))
             eng.close()
         finally:
             dev.set_activation_dtype(Act.F16)
-    emu = np.array(study["logits_bf16"], np.float32)
-    d_emu = np.abs(got[Act.BF16] - emu).max()
+    # (1) one layer: engine vs the rounding-matched CPU forward vs the unrounded one
+    one = Dims(**{**dims.__dict__, "n_layers": 1})
+    fused = [fuse_layer(sd, 0, one)]
+    args = (one, fused, sd["embed_tokens.weight"], sd["norm.weight"], batch.ids, [0], [batch.cand[0, :1]])
+    rounded, exact = [], []
+    cpu_forward.forward_logits(*args, round_to="bf16", layer_outputs=rounded)
+    cpu_forward.forward_logits(*args, layer_outputs=exact)
+    scale = np.abs(exact[0]).max()
+    to_emulation, to_fp32 = np.abs(x1 - rounded[0]).max() / scale, np.abs(x1 - exact[0]).max() / scale
+    # (2), (3) all layers
+    predicted = study["variants"]["bf16"]["max_abs_dlogit_vs_fp32"]
     d_fp32 = np.abs(got[Act.BF16] - fp32).max()
     d_f16 = np.abs(got[Act.F16] - fp32).max()
-    print(f"bf16 engine: max|dlogit| {d_fp32:.4f} vs fp32 (CPU emulation of bf16: {study['variants']['bf16']['max_abs_dlogit_vs_fp32']:.4f}), "
-          f"{d_emu:.4f} vs the emulation; fp16 engine: {d_f16:.4f} vs fp32")
-    # the same rounding points, but every rounding decision sits on an fp32-vs-f64 knife edge somewhere: the two bf16
-    # forwards agree to well within the distance of either from fp32, and the fp16 engine is inside the bar
-    assert d_emu < 0.5 * max(d_fp32, study["variants"]["bf16"]["max_abs_dlogit_vs_fp32"])
-    assert d_f16 <= check.MAX_DLOGIT
-    assert d_fp32 < 0.25, "bf16 error is far beyond what the format explains"
+    print(f"bf16 engine after one layer: {to_emulation:.2e} of the residual's range from its CPU emulation, {to_fp32:.2e} from fp32; "
+          f"36 layers: max|dlogit| {d_fp32:.4f} vs fp32 (the emulation predicts {predicted:.4f}); fp16 engine: {d_f16:.4f}")
+    assert to_emulation < 0.25 * to_fp32, "after one layer the bf16 engine should sit on its CPU emulation, far from fp32"
+    assert 0.4 * predicted < d_fp32 < 2.5 * predicted, "the bf16 engine's error is not the size the format predicts"
+    assert d_fp32 > check.MAX_DLOGIT >= d_f16
 
 
 def test_second_forward_allocates_and_encodes_nothing(dev):
