@@ -41,7 +41,7 @@ struct dc_ctx {
     uint32_t delta_split = 3;         // chunked delta rule: 3 = hi/lo split operands (near fp32), 1 = single bf16 pass
     uint32_t act_dtype = DC_ACT_F16;  // type of every 16-bit GEMM operand: activations and weight matrices
     float* gemm_part_ws = nullptr;   // partial accumulators of K-split tail tiles: sm_count x 128 x 256 fp32
-    int* gemm_part_cnt = nullptr;    // arrival counters of split tiles: sm_count x 4 row quadrants x 8 column chunks, zero between launches
+    int* gemm_part_cnt = nullptr;    // arrival counters of split tiles: sm_count x 4 row quadrants, zero between launches
     void* workspace = nullptr;       // scratch for the chunked delta rule and other multi-pass ops
     size_t workspace_bytes = 0;
     bool workspace_frozen = false;   // an op that needs more scratch than is reserved fails instead of allocating

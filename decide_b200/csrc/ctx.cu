@@ -131,8 +131,8 @@ dc_ctx* dc_open(int device, char* err, size_t err_len) {
     *ctx->status_host = 0;
     ctx->allocs += 2;
     const size_t ws = static_cast<size_t>(ctx->sm_count) * 128 * 256 * sizeof(float);
-    if ((e = cudaMalloc(&ctx->gemm_part_ws, ws)) != cudaSuccess || (e = cudaMalloc(&ctx->gemm_part_cnt, ctx->sm_count * 32 * sizeof(int))) != cudaSuccess ||
-        (e = cudaMemset(ctx->gemm_part_cnt, 0, ctx->sm_count * 32 * sizeof(int))) != cudaSuccess) {
+    if ((e = cudaMalloc(&ctx->gemm_part_ws, ws)) != cudaSuccess || (e = cudaMalloc(&ctx->gemm_part_cnt, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess ||
+        (e = cudaMemset(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int))) != cudaSuccess) {
         say("dc_open: cannot allocate the GEMM split workspace", cudaGetErrorString(e));
         dc_close(ctx);
         return nullptr;
@@ -225,7 +225,7 @@ int dc_check_status(dc_ctx* ctx, void* stream) {
     if (code != 0) {
         cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), s);
         // a split GEMM that gave up leaves arrival counters of its tail tiles non-zero: the next one must start from zero
-        cudaMemsetAsync(ctx->gemm_part_cnt, 0, ctx->sm_count * 32 * sizeof(int), s);
+        cudaMemsetAsync(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int), s);
         cudaStreamSynchronize(s);
         return dc_fail(ctx, DC_TIMEOUT, "a bounded device-side wait ran out (wait id %d); the results of this run are invalid", code);
     }

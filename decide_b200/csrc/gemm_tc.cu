@@ -39,7 +39,7 @@ struct GemmArgs {
     // is cut into `split` parts along K of `kb_per_part` k-blocks, so the last wave fills the SMs too.
     uint32_t full_tiles, split, kb_per_part;
     float* part_ws;   // [tail tile][part][128][BN] fp32 partial accumulators
-    int* part_cnt;    // [tail tile][4 row quadrants][8 column chunks] arrival counters, zero between launches
+    int* part_cnt;    // [tail tile][4 row quadrants] arrival counters, zero between launches
 };
 
 struct Unit {
@@ -98,12 +98,12 @@ __device__ __forceinline__ bool wait_quiet(uint64_t* bar, uint32_t parity) {
 }
 
 
-// Bounded wait until an arrival counter in global memory reads `want` (ordered accumulation of K-split parts).
-__device__ __forceinline__ bool wait_turn(const volatile int* cnt, int want, volatile uint32_t* abort_flag, int* status, int code) {
-    if (*cnt == want) return true;
+// Bounded wait until an arrival counter in global memory reaches `want` (all parts of a K-split tile have parked their sums).
+__device__ __forceinline__ bool wait_at_least(const volatile int* cnt, int want, volatile uint32_t* abort_flag, int* status, int code) {
+    if (*cnt >= want) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while (*cnt != want) {
+    while (*cnt < want) {
         if ((++spins & 63u) == 0u) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -354,92 +354,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[acc]);
-            } else if constexpr (EPI == DC_EPI_ADD_F32 || EPI == DC_EPI_STORE_F32) {
-                // One part of a K-split tile with an fp32 output: the parts accumulate straight into Y, IN PART ORDER, one 32-column
-                // chunk at a time. Part 0 runs the epilogue as given (store, or += residual); part p > 0 adds its accumulator on
-                // top of what part p - 1 left, chunk by chunk as that part finishes them (a counter per (tile, 32 rows, chunk)
-                // holds the number of parts done), so the parts' epilogues overlap like a pipeline instead of queueing up.
-                // ((y + p0) + p1) + ... is one fixed order of fp32 additions: the result does not depend on timing. No workspace.
-                // The wait cannot deadlock: all parts of the tail wave are resident at once (one unit per CTA, grid <= SMs) and
-                // part 0 waits for nobody; it is bounded all the same. A chunk's old values are requested one chunk ahead.
-                const uint32_t rt = w.tile - a.full_tiles;
-                int* cnt = a.part_cnt + (rt * 4u + q) * 8u;
-                const bool add = w.part > 0 || EPI == DC_EPI_ADD_F32;
-                const int sub = lane >> 3, l8 = lane & 7;
-                float* yf = static_cast<float*>(y) + 4 * l8;
-                const uint32_t n_chunks = min(static_cast<uint32_t>(BN / 32), (a.n - tn * BN + 31u) / 32u);
-                bool go = true;
-                auto my_turn = [&](uint32_t c) {   // part p may touch chunk c once p parts have finished it
-                    if (w.part == 0) return true;
-                    bool ok = true;
-                    if (lane == 0) ok = wait_turn(cnt + c, static_cast<int>(w.part), abort_flag, status, 5);
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    __threadfence();
-                    __syncwarp();
-                    return ok;
-                };
-                auto load_old = [&](uint32_t c, float4 (&old)[8]) {
-                    const uint32_t col0 = tn * BN + c * 32u;
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const size_t row = row0 + it * 4 + sub;
-                        old[it] = row < a.m ? __ldcg(reinterpret_cast<const float4*>(yf + row * a.ldy + col0)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                };
-                float4 old[8], next[8];
-#pragma unroll
-                for (int it = 0; it < 8; ++it) old[it] = next[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (add && n_chunks) {
-                    go = my_turn(0);
-                    if (go) load_old(0, old);
-                }
-#pragma unroll 1
-                for (uint32_t c = 0; go && c < n_chunks; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(taddr + c * 32u, r);
-                    if (add && c + 1 < n_chunks) {
-                        go = my_turn(c + 1);
-                        if (!go) break;
-                        load_old(c + 1, next);
-                    }
-                    tmem_ld_wait();
-                    float4* mine = reinterpret_cast<float4*>(st + lane * kEpiLd);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        mine[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                    __syncwarp();
-                    const uint32_t col0 = tn * BN + c * 32u;
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rr = it * 4 + sub;
-                        const size_t row = row0 + rr;
-                        float4 v = *reinterpret_cast<const float4*>(st + rr * kEpiLd + 4 * l8);
-                        v.x += old[it].x; v.y += old[it].y; v.z += old[it].z; v.w += old[it].w;
-                        if (row < a.m) *reinterpret_cast<float4*>(yf + row * a.ldy + col0) = v;
-                        old[it] = next[it];
-                    }
-                    __threadfence();
-                    __syncwarp();
-                    if (lane == 0) atomicExch(cnt + c, w.part + 1u == a.split ? 0 : static_cast<int>(w.part) + 1);   // the last part leaves zero behind
-                }
-                if (!go) break;
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[acc]);
             } else {
-                // One part of a K-split tile: park the raw accumulator in the workspace, laid out
-                // [part][32-column chunk][128 rows][32] so that every warp instruction moves 4 whole rows of
-                // a chunk (512 contiguous bytes). The warp that arrives last for these 32 rows adds the parts
-                // in part order (so the result does not depend on who was last) and runs the epilogue.
-                // Nobody waits for anybody.
+                // One part of a K-split tile. The P parts of a tile run at the same time on P SMs (one unit per CTA in the
+                // tail wave). Each parks its raw accumulator in the workspace, laid out [part][32-column chunk][128 rows][32] so
+                // that every warp instruction moves 4 whole rows of a chunk (512 contiguous bytes), and counts itself in. When
+                // all P have arrived, the parts SHARE the fix-up: part p sums chunks p, p + P, ... over all parts IN PART ORDER
+                // (so the result does not depend on timing) and runs the normal epilogue on them. The wait is for parts that are
+                // resident by construction (grid <= SMs), and bounded all the same. The counter goes P up on arrival, P up on
+                // leaving; whoever leaves last puts it back to zero.
                 const uint32_t rt = w.tile - a.full_tiles;
+                const uint32_t P = a.split;
                 const int sub = lane >> 3, l8 = lane & 7;
                 constexpr uint32_t kChunkFloats = BM * 32;                 // one chunk of all 128 rows
                 constexpr uint32_t kPartFloats = BM * BN;
-                float* mine = a.part_ws + static_cast<size_t>(rt * a.split + w.part) * kPartFloats + q * 32u * 32u;
+                const uint32_t n_chunks = min(static_cast<uint32_t>(BN / 32), (a.n - tn * BN + 31u) / 32u);
+                float* tile_ws = a.part_ws + static_cast<size_t>(rt * P) * kPartFloats + q * 32u * 32u;
+                float* mine = tile_ws + static_cast<size_t>(w.part) * kPartFloats;
 #pragma unroll 1
-                for (uint32_t c = 0; c < BN / 32; ++c) {
-                    if (tn * BN + c * 32u >= a.n) break;
+                for (uint32_t c = 0; c < n_chunks; ++c) {
                     uint32_t r[32];
                     tmem_ld_32x32(taddr + c * 32u, r);
                     tmem_ld_wait();
@@ -459,37 +391,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 tc_fence_before_sync();
                 __threadfence();
                 __syncwarp();
-                int prev = 0;
+                int* cnt = a.part_cnt + rt * 4u + q;
+                bool go = true;
                 if (lane == 0) {
-                    mbar_arrive(&acc_empty[acc]);
-                    prev = atomicAdd(&a.part_cnt[(rt * 4u + q) * 8u], 1);
+                    mbar_arrive(&acc_empty[acc]);        // the accumulator is free: everything else works from the workspace
+                    atomicAdd(cnt, 1);
+                    go = wait_at_least(cnt, static_cast<int>(P), abort_flag, status, 5);
                 }
-                prev = __shfl_sync(0xffffffffu, prev, 0);
-                if (prev == static_cast<int>(a.split) - 1) {
-                    __threadfence();
-                    const float* base = a.part_ws + static_cast<size_t>(rt * a.split) * kPartFloats + q * 32u * 32u;
+                go = __shfl_sync(0xffffffffu, go ? 1 : 0, 0) != 0;
+                if (!go) break;
+                __threadfence();
+                __syncwarp();
 #pragma unroll 1
-                    for (uint32_t c = 0; c < BN / 32; ++c) {
-                        const uint32_t col0 = tn * BN + c * 32u;
-                        if (col0 >= a.n) break;
-                        float4 sum[8];
+                for (uint32_t c = w.part; c < n_chunks; c += P) {
+                    const uint32_t col0 = tn * BN + c * 32u;
+                    float4 sum[8];
 #pragma unroll
-                        for (int it = 0; it < 8; ++it) sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int it = 0; it < 8; ++it) {
+                        sum[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if constexpr (EPI == DC_EPI_ADD_F32) {   // the residual is requested together with the first parts
+                            const size_t row = row0 + it * 4 + sub;
+                            if (row < a.m) sum[it] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(y) + row * a.ldy + col0 + 4 * l8));
+                        }
+                    }
+                    const float* src = tile_ws + c * kChunkFloats;
 #pragma unroll
-                        for (uint32_t pt = 0; pt < 4; ++pt) {
-                            if (pt < a.split) {
-                                const float* src = base + pt * kPartFloats + c * kChunkFloats;
+                    for (uint32_t pt = 0; pt < 4; pt += 2) {     // two parts' loads in flight together
+                        if (pt < P) {
+                            float4 v0[8], v1[8];
 #pragma unroll
-                                for (int it = 0; it < 8; ++it) {
-                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (it * 4 + sub) * 32 + 4 * l8));
-                                    sum[it].x += v.x;
-                                    sum[it].y += v.y;
-                                    sum[it].z += v.z;
-                                    sum[it].w += v.w;
-                                }
+                            for (int it = 0; it < 8; ++it) {
+                                v0[it] = __ldcg(reinterpret_cast<const float4*>(src + pt * kPartFloats + (it * 4 + sub) * 32 + 4 * l8));
+                                v1[it] = pt + 1 < P ? __ldcg(reinterpret_cast<const float4*>(src + (pt + 1) * kPartFloats + (it * 4 + sub) * 32 + 4 * l8))
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+#pragma unroll
+                            for (int it = 0; it < 8; ++it) {
+                                sum[it].x = (sum[it].x + v0[it].x) + v1[it].x;
+                                sum[it].y = (sum[it].y + v0[it].y) + v1[it].y;
+                                sum[it].z = (sum[it].z + v0[it].z) + v1[it].z;
+                                sum[it].w = (sum[it].w + v0[it].w) + v1[it].w;
                             }
                         }
-                        // back to one row per thread for the common epilogue
+                    }
+                    if constexpr (EPI == DC_EPI_ADD_F32 || EPI == DC_EPI_STORE_F32) {
+                        // fp32 outputs: the sums already sit in the layout the stores want (a warp instruction covers 4 whole rows)
+                        float* yf = static_cast<float*>(y);
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const size_t row = row0 + it * 4 + sub;
+                            if (row < a.m) *reinterpret_cast<float4*>(yf + row * a.ldy + col0 + 4 * l8) = sum[it];
+                        }
+                    } else {
+                        // 16-bit outputs: back to one row per thread for the common epilogue
 #pragma unroll
                         for (int it = 0; it < 8; ++it) *reinterpret_cast<float4*>(st + (it * 4 + sub) * kEpiLd + 4 * l8) = sum[it];
                         __syncwarp();
@@ -506,7 +460,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         __syncwarp();
                         epilogue_chunk<EPI, Act>(y, st, row0, a.m, col0, a.ldy, r, lane);
                     }
-                    if (lane == 0) atomicExch(&a.part_cnt[(rt * 4u + q) * 8u], 0);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    const int before = atomicAdd(cnt, 1);
+                    if (before == 2 * static_cast<int>(P) - 1) atomicExch(cnt, 0);
                 }
             }
         }
@@ -638,21 +596,19 @@ int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, ui
 // K into up to 4 parts so that wave fills the SMs as well. The tile width is the cheapest of 256, 224,
 // 192 and 128 under this model, calibrated on the B200: time = waves x (time of one tile); a narrower
 // tile takes tile_time() of a 256-wide one (less than proportionally less: its operand feed, not only
-// its MMAs, sets its pace). A split tile costs its share of the main loop plus its epilogues: with an
-// fp32 output the parts add into Y in part order, pipelined chunk by chunk, the first epilogue worth
-// ~kEpiF32 k-blocks of main loop and each further part ~kEpiF32Next; with a 16-bit output the parts meet in a workspace and the last one to arrive sums them,
-// worth ~45 k-blocks, so only long-K GEMMs split there.
+// its MMAs, sets its pace). A split tile costs its share of the main loop plus the fix-up: every part
+// parks its sums in the workspace and the parts share the summing, worth ~kFixup k-blocks of main loop.
 namespace {
 struct Plan {
     uint32_t bn, full_tiles, split, kb_per_part;
     double cost;
 };
-constexpr double kEpiF32 = 10.0, kEpiF32Next = 3.0, kFixup16 = 45.0;
+constexpr double kFixup = 14.0;   // k-blocks of main loop a split tile's park + shared fix-up is worth
 // measured on whole waves of the gate_up projection at 2,307 rows: one wave of 128 x BN tiles against one of 128 x 256
 double tile_time(uint32_t bn) { return bn == 256 ? 1.0 : bn == 224 ? 0.87 : bn == 192 ? 0.78 : 0.65; }
 
 Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uint32_t epi, uint32_t max_split = 4) {
-    const bool f32_out = epi == DC_EPI_ADD_F32 || epi == DC_EPI_STORE_F32;
+    (void)epi;
     const uint32_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
     const uint32_t k_blocks = (k + BK - 1) / BK;
     const uint32_t rest = tiles % sms;
@@ -660,7 +616,7 @@ Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uin
     auto tail_of = [&](uint32_t split) {
         const uint32_t per = (k_blocks + split - 1) / split;
         if (split == 1) return 1.0;
-        return static_cast<double>(per) / k_blocks + (f32_out ? kEpiF32 + (split - 1) * kEpiF32Next : kFixup16) / k_blocks;
+        return static_cast<double>(per) / k_blocks + kFixup / k_blocks;
     };
     if (rest > 0) {
         const uint32_t cap = sms / rest < max_split ? sms / rest : max_split;
