@@ -603,7 +603,8 @@ struct Plan {
     uint32_t bn, full_tiles, split, kb_per_part;
     double cost;
 };
-constexpr double kFixup = 14.0;   // k-blocks of main loop a split tile's park + shared fix-up is worth
+constexpr double kFixup = 14.0;   // k-blocks of main loop a split tile's park + shared fix-up is worth (~7 us)
+constexpr uint32_t kMinPartBlocks = 24;   // shorter parts did not pay on the B200: K = 2560 cut in four ran slower than whole tiles
 // measured on whole waves of the gate_up projection at 2,307 rows: one wave of 128 x BN tiles against one of 128 x 256
 double tile_time(uint32_t bn) { return bn == 256 ? 1.0 : bn == 224 ? 0.87 : bn == 192 ? 0.78 : 0.65; }
 
@@ -621,7 +622,7 @@ Plan plan_for(uint32_t bn, uint32_t m, uint32_t n, uint32_t k, uint32_t sms, uin
     if (rest > 0) {
         const uint32_t cap = sms / rest < max_split ? sms / rest : max_split;
         for (uint32_t split = 2; split <= cap; ++split)
-            if (k_blocks / split >= 8 && tail_of(split) < tail_of(p.split)) p.split = split;
+            if (k_blocks / split >= kMinPartBlocks && tail_of(split) < tail_of(p.split)) p.split = split;
     }
     p.kb_per_part = (k_blocks + p.split - 1) / p.split;
     const double tail = rest == 0 ? 0.0 : tail_of(p.split);
