@@ -240,7 +240,13 @@ def run_engine(args):
                 e1.record(stream)
                 torch.cuda.synchronize()
                 samples.append(e0.elapsed_time(e1))
-            latency[f"tokens_{toks}"] = {"p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)), "runs": len(samples)}
+            eng.profile()
+            eng.set_profiling(True)     # one more, profiled run: where a single request's time goes (events around every op add a little)
+            eng.logits(one)
+            per_op = {name: round(ms, 4) for name, ms, _ in eng.profile()}
+            eng.set_profiling(False)
+            latency[f"tokens_{toks}"] = {"p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)), "runs": len(samples),
+                                         "rows_computed": eng.resident_rows, "per_op_ms": per_op}
 
     # ---- strong scaling (N > 1): the same 64 requests on every N, sharded by request; results checked across ranks
     strong = None

@@ -28,6 +28,7 @@ constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
+constexpr uint32_t kGroupM = 16;                             // row tiles walked together (see tile_coords)
 constexpr int kEpiLd = 36;                                   // padded row of the per-warp epilogue staging tile
 constexpr uint32_t kEpiBytes = 4 * 32 * kEpiLd * 4;          // 4 epilogue warps x [32][36] fp32
 
@@ -685,7 +686,11 @@ int dc_gemm_tc(dc_ctx* ctx, cudaStream_t stream, const void* x, const void* w, v
     a.m_tiles = (m + BM - 1) / BM;
     a.n_tiles = (n + bn - 1) / bn;
     a.k_blocks = (k + BK - 1) / BK;
-    a.group_m = a.m_tiles < 16 ? a.m_tiles : 16;
+    // Row tiles per group: W is streamed from HBM once per group, and the group's X rows (group_m x 128 x K 16-bit values)
+    // have to stay in L2 beside the W stripes in flight. DECIDE_GEMM_GROUP_M overrides (a measuring aid).
+    static const uint32_t group_env = getenv("DECIDE_GEMM_GROUP_M") ? static_cast<uint32_t>(atoi(getenv("DECIDE_GEMM_GROUP_M"))) : 0u;
+    const uint32_t group_want = group_env ? group_env : kGroupM;
+    a.group_m = a.m_tiles < group_want ? a.m_tiles : group_want;
     a.full_tiles = pl.full_tiles;
     a.split = pl.split;
     a.kb_per_part = pl.kb_per_part;
