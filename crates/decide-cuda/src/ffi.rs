@@ -92,6 +92,8 @@ extern "C" {
     pub fn dc_model_activation_bytes(m: *mut DcModel) -> usize;
     pub fn dc_model_prefill(m: *mut DcModel, stream: *mut c_void, ids: *const u32, seq_start: *const u32, n_seq: u32, ans_rows: *const u32, cand: *const u32, ncand: *const u32, n_ans: u32, logits: *mut f32) -> i32;
     pub fn dc_model_forward_resident(m: *mut DcModel, stream: *mut c_void, seq_start: *const u32, n_seq: u32, n_ans: u32) -> i32;
+    pub fn dc_model_set_graphs(m: *mut DcModel, on: u32) -> i32;
+    pub fn dc_model_graph_count(m: *mut DcModel) -> usize;
     pub fn dc_model_set_pruning(m: *mut DcModel, on: u32) -> i32;
     pub fn dc_model_set_truncation(m: *mut DcModel, on: u32) -> i32;
     pub fn dc_model_resident_rows(m: *mut DcModel) -> u32;

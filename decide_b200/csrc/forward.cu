@@ -7,8 +7,11 @@
 // rule and attention take the per-request row offsets. Nothing is allocated, JIT-compiled or
 // tensor-map-encoded by a forward after the first one of a given shape.
 #include <algorithm>
+#include <array>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -48,6 +51,18 @@ struct dc_model {
         std::vector<void*> kc, vc;          // [layer] -> [max_rows, kv_dim] in the 16-bit type (null for linear layers)
         std::vector<float*> conv, state;    // [layer] -> [3, conv_dim], [nv, dv, dk] (null for attention layers)
     } carry, snap;
+    // CUDA graphs of the batched forward: one per (rows, requests, longest request, answer rows, switches), captured the first
+    // time that shape runs and replayed afterwards on the model's own stream (the caller's stream is joined by events;
+    // the legacy default stream cannot be captured). A 603-token forward is ~350 short kernels: replayed as a graph it is
+    // no longer bound by the host's enqueue rate.
+    bool use_graphs = true;
+    cudaStream_t graph_stream = nullptr;
+    cudaEvent_t graph_in = nullptr, graph_out = nullptr;
+    struct GraphEntry {
+        cudaGraphExec_t exec = nullptr;
+        uint64_t launches = 0;              // kernels in the graph, for the context's launch count
+    };
+    std::map<std::array<uint32_t, 6>, GraphEntry> graphs;
     uint32_t chunk_rows = 0;                // 0 = one request runs whole (no carry needed)
     std::vector<uint32_t> snap_ids;         // token ids of the captured prefix; empty = no snapshot
     uint32_t last_route = 0;                // 0 full, 1 from the prefix snapshot
@@ -230,6 +245,54 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
         RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows, m->xs, n_ans, H));
         RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
     }
+    return DC_OK;
+}
+
+// The batched forward, replayed from a CUDA graph when it can be: not while per-op profiling is on (events per op), not
+// on a tensor-parallel shard (the collective library's calls are left out of capture), not with a layer limit.
+int run_forward(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, uint32_t max_len, uint32_t n_ans) {
+    dc_ctx* c = m->ctx;
+    if (!m->use_graphs || m->profiling || c->tp_world > 1 || m->layer_limit != 0 || !m->graph_stream)
+        return forward_device(m, s, rows, n_seq, max_len, n_ans);
+    const std::array<uint32_t, 6> key = {rows, n_seq, max_len, n_ans, static_cast<uint32_t>(m->prune) | (c->act_dtype << 1) | (c->gemm_impl << 2) | (c->attn_impl << 3) |
+                                                                          (c->delta_impl << 4) | (c->attn_engine << 5) | (c->delta_engine << 6) | (c->delta_split << 7),
+                                         0u};
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        // First time this shape runs: one eager pass (it fills the tensor-map cache and is the result of this call), and a
+        // capture of the same enqueue sequence for the calls that follow.
+        int rc = forward_device(m, s, rows, n_seq, max_len, n_ans);
+        if (rc != DC_OK) return rc;
+        if (m->graphs.size() >= 64) return DC_OK;   // a bounded cache; further shapes simply run eagerly
+        const uint64_t before = c->launches;
+        if (cudaStreamBeginCapture(m->graph_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            return DC_OK;
+        }
+        rc = forward_device(m, m->graph_stream, rows, n_seq, max_len, n_ans);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(m->graph_stream, &graph);
+        dc_model::GraphEntry entry;
+        entry.launches = c->launches - before;
+        c->launches = before;                        // nothing ran during capture
+        if (rc == DC_OK && e == cudaSuccess && graph && cudaGraphInstantiate(&entry.exec, graph, 0) == cudaSuccess) {
+            cudaGraphUpload(entry.exec, m->graph_stream);   // device-side resources now, not at the first replay
+            cudaStreamSynchronize(m->graph_stream);
+            m->graphs.emplace(key, entry);
+        } else {
+            cudaGetLastError();
+        }
+        if (graph) cudaGraphDestroy(graph);
+        c->last_error.clear();
+        return DC_OK;
+    }
+    cudaError_t e = cudaEventRecord(m->graph_in, s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(m->graph_stream, m->graph_in, 0);
+    if (e == cudaSuccess) e = cudaGraphLaunch(it->second.exec, m->graph_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(m->graph_out, m->graph_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, m->graph_out, 0);
+    if (e != cudaSuccess) return dc_fail(c, DC_CUDA_ERROR, "forward: graph launch failed: %s", cudaGetErrorString(e));
+    c->launches += it->second.launches;
     return DC_OK;
 }
 
@@ -489,6 +552,12 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
         return nullptr;
     }
     ctx->allocs++;
+    if (cudaStreamCreateWithFlags(&m->graph_stream, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreateWithFlags(&m->graph_in, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->graph_out, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        m->graph_stream = nullptr;      // graphs are an optimisation: without the stream the forward runs eagerly
+    }
+    if (const char* g = getenv("DECIDE_GRAPHS")) m->use_graphs = !(g[0] == '0' && g[1] == 0);
     return m;
 }
 
@@ -497,6 +566,10 @@ void dc_model_destroy(dc_model* m) {
     cudaSetDevice(m->ctx->device);
     collect_profile(m);
     for (auto e : m->event_pool) cudaEventDestroy(e);
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.exec);
+    if (m->graph_in) cudaEventDestroy(m->graph_in);
+    if (m->graph_out) cudaEventDestroy(m->graph_out);
+    if (m->graph_stream) cudaStreamDestroy(m->graph_stream);
     if (m->arena) cudaFree(m->arena);
     if (m->carry.mem) cudaFree(m->carry.mem);
     if (m->snap.mem) cudaFree(m->snap.mem);
@@ -675,7 +748,7 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
         if (from_snapshot) rc = copy_carry(m, s, m->snap, m->carry, P);
         if (rc == DC_OK) rc = forward_single(m, s, chunks, n_ans);
     } else {
-        rc = forward_device(m, s, rows, n_seq, max_len, n_ans);
+        rc = run_forward(m, s, rows, n_seq, max_len, n_ans);
     }
     if (rc != DC_OK) return rc;
     if (n_ans) {
@@ -718,7 +791,7 @@ int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_sta
         }
         return forward_single(m, s, m->cur.chunks, n_ans);
     }
-    return forward_device(m, s, m->cur.rows, n_seq, m->cur.max_len, n_ans);
+    return run_forward(m, s, m->cur.rows, n_seq, m->cur.max_len, n_ans);
 }
 
 // Forward::set_chunk (forward.rs:504-510): a single request runs in chunks of at most `rows` rows, all layers of a chunk
@@ -764,6 +837,15 @@ int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_id
 
 // 0: the last dc_model_prefill ran every row; 1: it started from the prefix snapshot.
 uint32_t dc_model_last_route(dc_model* m) { return m ? m->last_route : 0; }
+
+// on = 0: every forward is enqueued kernel by kernel; on = 1 (default; DECIDE_GRAPHS=0 turns it off at creation): a batched
+// forward of a shape seen before is replayed from its CUDA graph.
+int dc_model_set_graphs(dc_model* m, uint32_t on) {
+    if (!m) return DC_INVALID_ARG;
+    m->use_graphs = on != 0;
+    return DC_OK;
+}
+size_t dc_model_graph_count(dc_model* m) { return m ? m->graphs.size() : 0; }
 
 int dc_model_set_pruning(dc_model* m, uint32_t on) {
     if (!m) return DC_INVALID_ARG;

@@ -103,6 +103,14 @@ class Engine:
         """Stop each request after its last answer row (forward.rs:830-831); on by default."""
         self._call("dc_model_set_truncation", int(on))
 
+    def set_graphs(self, on: bool):
+        """Replay batched forwards of a shape seen before from a CUDA graph (default on)."""
+        self._call("dc_model_set_graphs", int(on))
+
+    @property
+    def graph_count(self) -> int:
+        return int(self.lib.dc_model_graph_count(self.handle))
+
     def set_chunk(self, rows: int):
         """A single request runs in chunks of at most `rows` rows with carried state (Forward::set_chunk, forward.rs:504-510); 0 = whole."""
         self._call("dc_model_set_chunk", rows)

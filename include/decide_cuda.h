@@ -396,6 +396,16 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
  * and n_ans must be that batch's (DC_INVALID_ARG otherwise). */
 int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_start, uint32_t n_seq, uint32_t n_ans);
 
+/* CUDA graphs (on by default; DECIDE_GRAPHS=0 at creation or on = 0 turn them off): a batched forward of a
+ * shape (rows, requests, longest request, answer rows, switches) that has run before is replayed from a graph
+ * captured on its first run, on a stream the model owns that is joined to the caller's by events; the
+ * first run of a shape is enqueued kernel by kernel and also captures. A single request is a few hundred
+ * short kernels, which the host cannot enqueue as fast as the GPU runs them. Per-op profiling, a layer
+ * limit, tensor-parallel shards and the chunked / snapshot route always run eagerly. Results are the same
+ * bits either way. dc_model_graph_count: graphs held (at most 64; further shapes run eagerly). */
+int dc_model_set_graphs(dc_model* m, uint32_t on);
+size_t dc_model_graph_count(dc_model* m);
+
 /* Work skipping, both on by default as in the reference:
  *  - truncation (forward.rs:830-831): a request is run only up to its last answer row; rows after it
  *    cannot reach a logit. A request without answer rows runs whole.

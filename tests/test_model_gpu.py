@@ -281,6 +281,32 @@ def test_bf16_engine_matches_its_cpu_emulation(dev):
     assert d_fp32 > check.MAX_DLOGIT >= d_f16
 
 
+def test_graph_replay_equals_eager(dev):
+    """A forward replayed from its CUDA graph gives the bits of the eager forward; one graph per shape; another batch of
+    the same shape (other ids, other request lengths summing alike is NOT the same shape) reuses or adds as it should."""
+    sd, eng = make(SMALL, dev, 51, max_rows=512, max_seqs=4, max_answers=16, max_cand=8)
+    a = synth_batch(SMALL, 3, 100, seed=52, n_answers=2, n_cand=8, max_cand=8)
+    b = synth_batch(SMALL, 3, 100, seed=53, n_answers=2, n_cand=8, max_cand=8)     # same shape, other tokens
+    c = synth_batch(SMALL, 2, 150, seed=54, n_answers=2, n_cand=8, max_cand=8)     # another shape
+    eng.set_graphs(False)
+    eager = [eng.logits(x) for x in (a, b, c)]
+    assert eng.graph_count == 0
+    eng.set_graphs(True)
+    first = eng.logits(a)                    # eager run + capture
+    assert eng.graph_count == 1
+    launches = dev.launches
+    replay_a, replay_b = eng.logits(a), eng.logits(b)    # replays of one graph
+    assert eng.graph_count == 1 and dev.launches > launches      # replays count their kernels too
+    other = eng.logits(c)
+    again_c = eng.logits(c)
+    assert eng.graph_count == 2
+    eng.forward_resident(c)
+    dev.check_status()
+    for got, want in ((first, eager[0]), (replay_a, eager[0]), (replay_b, eager[1]), (other, eager[2]), (again_c, eager[2])):
+        assert np.array_equal(got, want)
+    eng.close()
+
+
 def test_second_forward_allocates_and_encodes_nothing(dev):
     """Nothing is allocated, compiled or tensor-map-encoded inside a request once its shape has been served
     (the reference checks the same for pipelines, engine.rs:168-172): across the second and third forward of a
