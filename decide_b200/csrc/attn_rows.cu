@@ -19,6 +19,7 @@ using namespace dc;
 constexpr int HD = 128;
 constexpr int TK = 256;          // cache rows per tile
 constexpr int kMaxGroup = 16;    // query heads per kv head
+constexpr int kPvUnroll = 16;    // V rows requested together in the P V loop
 constexpr float kMasked = -1e30f;
 
 template <typename Act>
@@ -76,12 +77,12 @@ attn_rows_kernel(const uint16_t* __restrict__ q, const uint16_t* __restrict__ kc
         const uint16_t* vbase = vc + ((base + j0) * nkv + kvh) * HD + 4 * lane;
         const size_t vstride = static_cast<size_t>(nkv) * HD;
         uint32_t j = 0;
-        for (; j + 4 <= cnt; j += 4) {
-            uint2 v[4];
+        for (; j + kPvUnroll <= cnt; j += kPvUnroll) {   // many V rows in flight per lane: the loop is bound by load latency
+            uint2 v[kPvUnroll];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint2*>(vbase + (j + u) * vstride);
+            for (int u = 0; u < kPvUnroll; ++u) v[u] = *reinterpret_cast<const uint2*>(vbase + (j + u) * vstride);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kPvUnroll; ++u) {
                 const float p = sc[j + u];
                 o0 += p * Act::lo(v[u].x); o1 += p * Act::hi(v[u].x); o2 += p * Act::lo(v[u].y); o3 += p * Act::hi(v[u].y);
             }
