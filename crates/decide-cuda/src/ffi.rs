@@ -56,6 +56,7 @@ extern "C" {
     pub fn dc_tmap_encode_count(ctx: *mut DcCtx) -> u64;
     pub fn dc_tmap_cache_size(ctx: *mut DcCtx) -> usize;
     pub fn dc_sm_count(ctx: *mut DcCtx) -> i32;
+    pub fn dc_source_hash() -> *const c_char;
     pub fn dc_convert_bf16_to_f16(ctx: *mut DcCtx, stream: *mut c_void, src: *const c_void, dst: *mut c_void, n: usize, report: *mut DcConvertReport) -> i32;
     pub fn dc_convert_bf16_to_f16_noalloc(stream: *mut c_void, src: *const c_void, dst: *mut c_void, n: usize, report: *mut DcConvertReport, err: *mut c_char, err_len: usize) -> i32;
     pub fn dc_gemm(ctx: *mut DcCtx, stream: *mut c_void, x: *const c_void, w: *const c_void, y: *mut c_void, m: u32, n: u32, k: u32, ldx: u32, ldw: u32, ldy: u32, epilogue: u32, swiglu_block: u32) -> i32;

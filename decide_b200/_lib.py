@@ -7,6 +7,7 @@ is no fallback: if the shared library is missing, `load()` raises.
 from __future__ import annotations
 
 import ctypes
+import os
 import re
 from pathlib import Path
 
@@ -67,5 +68,16 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here = the header declares a symbol the library lacks
         fn.restype = restype
         fn.argtypes = argtypes
+    # The stale-binary guard of the reference (crates/decide-metal/src/source_hash.rs, lib.rs:18-21): the library carries the
+    # hash of the sources it was built from and is refused when the sources beside it have changed since.
+    lib.dc_source_hash.restype = ctypes.c_char_p
+    built_from = lib.dc_source_hash().decode()
+    from . import build
+
+    if (PKG / "csrc").is_dir() and not os.environ.get("DECIDE_ALLOW_STALE_LIBRARY"):
+        now = build.source_hash()
+        if now != built_from:
+            raise RuntimeError(f"{LIB_PATH} was built from other sources (hash {built_from}, the sources hash to {now}): "
+                               "run `python -m decide_b200.build` (DECIDE_ALLOW_STALE_LIBRARY=1 overrides)")
     _lib = lib
     return lib

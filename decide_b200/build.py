@@ -28,6 +28,24 @@ NVCC_FLAGS = [
 ]
 
 
+def source_files() -> list[tuple[str, Path]]:
+    """The files the library is built from, as sorted (relative name, path): every csrc/*.cu and *.cuh and the public header."""
+    files = [(f"csrc/{p.name}", p) for p in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh"))] + [(f"include/{p.name}", p) for p in INCLUDE.glob("*.h")]
+    return sorted(files)
+
+
+def source_hash() -> str:
+    """Content hash of the kernel sources, the reference's stale-binary guard (crates/decide-metal/src/source_hash.rs:47-62):
+    FNV-1a 64 over `relative path NUL contents NUL` in sorted path order, as 16 hex digits. The library carries the hash of
+    the sources it was built from (dc_source_hash); decide_b200._lib refuses a library whose hash is not the sources'."""
+    h = 0xCBF29CE484222325
+    for rel, path in source_files():
+        for chunk in (rel.encode(), b"\0", path.read_bytes(), b"\0"):
+            for b in chunk:
+                h = ((h ^ b) * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+    return f"{h:016x}"
+
+
 def nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -58,6 +76,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         results = list(pool.map(lambda s: _compile(s, force, header_time), sources))
     objs = [o for o, _ in results]
+    # the stamp: a generated translation unit holding the hash of the sources above
+    digest = source_hash()
+    stamp_src, stamp_obj = OBJ / "source_hash_stamp.cu", OBJ / "source_hash_stamp.o"
+    text = f'extern "C" const char* dc_source_hash() {{ return "{digest}"; }}\n'
+    if not stamp_src.exists() or stamp_src.read_text() != text or not stamp_obj.exists():
+        stamp_src.write_text(text)
+        r = subprocess.run([nvcc(), "-O1", "-Xcompiler", "-fPIC", "-c", str(stamp_src), "-o", str(stamp_obj)], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for the source-hash stamp:\n{r.stdout}\n{r.stderr}")
+    objs.append(stamp_obj)
     if verbose:
         for _, log in results:
             if log:

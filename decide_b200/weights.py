@@ -171,7 +171,7 @@ def tp_shard_layer(lw: dict, layer: int, d: Dims, world: int, rank: int) -> dict
     The reference's precedent: the two-way split of each MLP between GPU and Neural Engine
     (crates/decide-engine/src/forward.rs:270-303; convert.rs's ANE split set)."""
     loc = d.tp_local(world)
-    rows = lambda t, lo, n: t[lo:lo + n]
+    rows = lambda t, lo, n: t[lo:lo + n].clone()   # a shard owns its memory: the engine converts matrices in place, and the whole may be freed
     out = {"in_norm": lw["in_norm"], "post_norm": lw["post_norm"]}
     if d.is_full_attention(layer):
         hd = d.head_dim
@@ -183,7 +183,7 @@ def tp_shard_layer(lw: dict, layer: int, d: Dims, world: int, rank: int) -> dict
         parts.append(rows(lw["w_in"], off + rank * loc.kv_dim, loc.kv_dim))
         parts.append(rows(lw["w_in"], off + d.kv_dim + rank * loc.kv_dim, loc.kv_dim))
         out["w_in"] = torch.cat(parts, dim=0).contiguous()
-        out["w_out"] = lw["w_out"][:, rank * loc.q_dim:(rank + 1) * loc.q_dim].contiguous()
+        out["w_out"] = lw["w_out"][:, rank * loc.q_dim:(rank + 1) * loc.q_dim].clone()
         out["q_norm"], out["k_norm"] = lw["q_norm"], lw["k_norm"]
         assert out["w_in"].shape[0] == loc.att_in_n and hd == loc.head_dim
     else:
@@ -197,11 +197,11 @@ def tp_shard_layer(lw: dict, layer: int, d: Dims, world: int, rank: int) -> dict
                                  rows(lw["w_in"], b0 + rank * loc.gdn_nv, loc.gdn_nv), gate_pad,
                                  rows(lw["w_in"], b0 + d.gate_cols + rank * loc.gdn_nv, loc.gdn_nv), gate_pad], dim=0).contiguous()
         out["conv_w"] = lw["conv_w"][conv_rows].contiguous()
-        out["a_log"] = rows(lw["a_log"], rank * loc.gdn_nv, loc.gdn_nv).contiguous()
-        out["dt_bias"] = rows(lw["dt_bias"], rank * loc.gdn_nv, loc.gdn_nv).contiguous()
+        out["a_log"] = rows(lw["a_log"], rank * loc.gdn_nv, loc.gdn_nv)
+        out["dt_bias"] = rows(lw["dt_bias"], rank * loc.gdn_nv, loc.gdn_nv)
         out["gnorm"] = lw["gnorm"]
-        out["w_out"] = lw["w_out"][:, rank * loc.value_dim:(rank + 1) * loc.value_dim].contiguous()
+        out["w_out"] = lw["w_out"][:, rank * loc.value_dim:(rank + 1) * loc.value_dim].clone()
         assert out["w_in"].shape[0] == loc.lin_in_n
-    out["w_gu"] = rows(lw["w_gu"], rank * 2 * loc.inter, 2 * loc.inter).contiguous()
-    out["w_down"] = lw["w_down"][:, rank * loc.inter:(rank + 1) * loc.inter].contiguous()
+    out["w_gu"] = rows(lw["w_gu"], rank * 2 * loc.inter, 2 * loc.inter)
+    out["w_down"] = lw["w_down"][:, rank * loc.inter:(rank + 1) * loc.inter].clone()
     return out

@@ -130,6 +130,10 @@ uint64_t dc_tmap_encode_count(dc_ctx* ctx);
 size_t dc_tmap_cache_size(dc_ctx* ctx);
 /* Number of SMs of the context's device. */
 int dc_sm_count(dc_ctx* ctx);
+/* Content hash (16 hex digits) of the kernel sources this library was built from: the stale-binary guard of
+ * the reference (crates/decide-metal/src/source_hash.rs:47-62; lib.rs:18-21). A host that ships the sources
+ * beside the library compares it with the hash of those sources before use, as the Python binding does. */
+const char* dc_source_hash(void);
 
 /* ---- weight conversion (bf16_to_f16 of the converter, crates/decide-engine/src/convert.rs:73-90) ----
  * dst[i] = fp16(src[i]) for n bf16 values, round to nearest even; dst may be src (in place). Adds to

@@ -67,3 +67,18 @@ def test_rust_ffi_is_generated_from_the_header():
     assert text == gen.render(), "run `python crates/decide-cuda/gen_ffi.py` after changing include/decide_cuda.h"
     declared = set(_lib.header_prototypes())
     assert all(f"pub fn {name}(" in text for name in declared) and len(declared) >= 50
+
+
+def test_stale_library_is_refused(monkeypatch):
+    """The stale-binary guard (the reference's source hash, crates/decide-metal/src/source_hash.rs): the library carries the
+    hash of the sources it was built from; when the sources beside it hash differently, loading fails until it is rebuilt."""
+    from decide_b200 import build
+
+    lib = _lib.load()
+    assert lib.dc_source_hash().decode() == build.source_hash() and len(build.source_hash()) == 16
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(build, "source_hash", lambda: "0" * 16)
+    with pytest.raises(RuntimeError, match="built from other sources"):
+        _lib.load()
+    monkeypatch.setenv("DECIDE_ALLOW_STALE_LIBRARY", "1")
+    assert _lib.load() is not None
