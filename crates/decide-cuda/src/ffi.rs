@@ -66,9 +66,12 @@ extern "C" {
     pub fn dc_gemm_plan_k(ctx: *mut DcCtx, m: u32, n: u32, k: u32, tail_split: *mut u32) -> u32;
     pub fn dc_rmsnorm(ctx: *mut DcCtx, stream: *mut c_void, x: *const f32, w: *const f32, y: *mut c_void, rowmap: *const u32, rows: u32, h: u32, ld_in: u32, ld_out: u32, eps: f32, add_one: u32) -> i32;
     pub fn dc_add_rmsnorm(ctx: *mut DcCtx, stream: *mut c_void, x: *mut f32, add: *const f32, w: *const f32, y: *mut c_void, rows: u32, h: u32, eps: f32, add_one: u32) -> i32;
+    pub fn dc_add16_rmsnorm(ctx: *mut DcCtx, stream: *mut c_void, x: *mut f32, add16: *const c_void, w: *const f32, y: *mut c_void, rows: u32, h: u32, eps: f32, add_one: u32) -> i32;
     pub fn dc_tp_unique_id(id128: *mut c_void, err: *mut c_char, err_len: usize) -> i32;
     pub fn dc_tp_init(ctx: *mut DcCtx, id128: *const c_void, world: u32, rank: u32) -> i32;
     pub fn dc_tp_all_reduce_f32(ctx: *mut DcCtx, stream: *mut c_void, buf: *mut f32, n: usize) -> i32;
+    pub fn dc_tp_all_reduce_16(ctx: *mut DcCtx, stream: *mut c_void, buf: *mut c_void, n: usize) -> i32;
+    pub fn dc_tp_set_exchange_16bit(ctx: *mut DcCtx, on: u32) -> i32;
     pub fn dc_tp_world(ctx: *mut DcCtx) -> u32;
     pub fn dc_tp_rank(ctx: *mut DcCtx) -> u32;
     pub fn dc_tp_destroy(ctx: *mut DcCtx);

@@ -49,6 +49,7 @@ struct dc_ctx {
     uint64_t tmap_encodes = 0;       // tensor maps encoded (cache misses)
     void* tp_comm = nullptr;         // NCCL communicator of the tensor-parallel group (dc_tp_init), or null
     uint32_t tp_world = 1, tp_rank = 0;
+    bool tp_exchange16 = false;      // partial sums cross the links in the 16-bit type (half the bytes) instead of fp32
 };
 
 int dc_fail(dc_ctx* ctx, int code, const char* fmt, ...);

@@ -156,10 +156,11 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
     // sums. They go to `xr`, are all-reduced over the group, and join the residual inside the next norm (`pending`).
     const bool tp = c->tp_world > 1;
     bool pending = false;
+    const bool x16 = c->tp_exchange16;   // the partial sums are stored, exchanged and added in the 16-bit type
     auto norm = [&](const float* wn) -> int {
         if (pending) {
             pending = false;
-            return dc_add_rmsnorm(c, st, m->x, m->xr, wn, m->h, rows, H, d.eps, 1);
+            return x16 ? dc_add16_rmsnorm(c, st, m->x, m->xr, wn, m->h, rows, H, d.eps, 1) : dc_add_rmsnorm(c, st, m->x, m->xr, wn, m->h, rows, H, d.eps, 1);
         }
         return dc_rmsnorm(c, st, m->x, wn, m->h, nullptr, rows, H, H, H, d.eps, 1);
     };
@@ -170,12 +171,12 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
         }
         {
             Prof _p(m, s, name);
-            const int rc = dc_gemm(c, st, a, wt, m->xr, rows, H, kk, kk, kk, H, DC_EPI_STORE_F32, d.swiglu_block);
+            const int rc = dc_gemm(c, st, a, wt, m->xr, rows, H, kk, kk, kk, H, x16 ? DC_EPI_STORE_BF16 : DC_EPI_STORE_F32, d.swiglu_block);
             if (rc != DC_OK) return rc;
         }
         Prof _p(m, s, "all_reduce");
         pending = true;
-        return dc_tp_all_reduce_f32(c, st, m->xr, static_cast<size_t>(rows) * H);
+        return x16 ? dc_tp_all_reduce_16(c, st, m->xr, static_cast<size_t>(rows) * H) : dc_tp_all_reduce_f32(c, st, m->xr, static_cast<size_t>(rows) * H);
     };
     const bool pruned = m->prune && !tp && m->layer_limit == 0 && n_ans > 0 && is_attention_layer(d, d.n_layers - 1);
     for (uint32_t l = 0; l < n_run; ++l) {
@@ -240,7 +241,8 @@ int forward_device(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, u
         RUN("gemm_gate_up", dc_gemm(c, st, m->h, w.w_gu, m->mlp, rows, 2 * d.inter, H, H, H, d.inter, DC_EPI_SWIGLU_BF16, d.swiglu_block));
         if (int rc = project_back("gemm_down", m->mlp, w.w_down, d.inter); rc != DC_OK) return rc;
     }
-    if (pending) RUN("add_partial", dc_add_rmsnorm(c, st, m->x, m->xr, nullptr, nullptr, rows, H, d.eps, 1));
+    if (pending)
+        RUN("add_partial", x16 ? dc_add16_rmsnorm(c, st, m->x, m->xr, nullptr, nullptr, rows, H, d.eps, 1) : dc_add_rmsnorm(c, st, m->x, m->xr, nullptr, nullptr, rows, H, d.eps, 1));
     if (n_ans && n_run == d.n_layers) {
         RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows, m->xs, n_ans, H));
         RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));

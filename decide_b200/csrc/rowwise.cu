@@ -77,38 +77,72 @@ rmsnorm_reg_kernel(const float* __restrict__ x, const float* __restrict__ w, uin
 
 // x[r] += add[r]; then (y != null) y[r] = x[r] * rsqrt(mean(x^2) + eps) * (w or 1 + w). The partial-sum add of a tensor-parallel
 // group (the all-reduced output of a row-split projection joins the residual; the reference's ane_add_partial,
-// kernels/ane.metal:10-18) fused with the RMSNorm that follows it.
-template <typename Act>
+// kernels/ane.metal:10-18) fused with the RMSNorm that follows it. `add` is fp32, or (ADD16) in the context's 16-bit type when
+// the group exchanges 16-bit partial sums. NV4 > 0: rows of exactly NV4 * 128 values stay in registers between the passes.
+template <typename Act, bool ADD16>
+__device__ __forceinline__ float4 load_add4(const void* add, size_t row, uint32_t h, uint32_t i) {
+    if constexpr (ADD16) {
+        const uint2 v = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(add) + row * h)[i];
+        return make_float4(Act::lo(v.x), Act::hi(v.x), Act::lo(v.y), Act::hi(v.y));
+    } else {
+        return reinterpret_cast<const float4*>(static_cast<const float*>(add) + row * h)[i];
+    }
+}
+
+template <typename Act, bool ADD16, int NV4>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, uint16_t* __restrict__ y, uint32_t rows,
+add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ add, const float* __restrict__ w, uint16_t* __restrict__ y, uint32_t rows,
                    uint32_t h, float eps, uint32_t add_one) {
     const uint32_t r = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     if (r >= rows) return;
     const int lane = threadIdx.x & 31;
     float4* xr = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * h);
-    const float4* ar = reinterpret_cast<const float4*>(add + static_cast<size_t>(r) * h);
-    const uint32_t nv = h >> 2;
-    float ss = 0.0f;
-    for (uint32_t i = lane; i < nv; i += 32) {
-        float4 v = xr[i];
-        const float4 a = ar[i];
-        v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-        xr[i] = v;
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
-    if (!y) return;
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / static_cast<float>(h) + eps);
-    const float one = add_one ? 1.0f : 0.0f;
     const float4* wr = reinterpret_cast<const float4*>(w);
     uint2* yr = reinterpret_cast<uint2*>(y + static_cast<size_t>(r) * h);
-    for (uint32_t i = lane; i < nv; i += 32) {
-        const float4 v = xr[i];   // this lane's own stores of the first pass
-        const float4 g = wr[i];
-        uint2 o;
-        o.x = Act::pack(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
-        o.y = Act::pack(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
-        yr[i] = o;
+    const float one = add_one ? 1.0f : 0.0f;
+    float ss = 0.0f;
+    if constexpr (NV4 > 0) {
+        float4 v[NV4];
+#pragma unroll
+        for (int i = 0; i < NV4; ++i) v[i] = xr[lane + 32 * i];
+#pragma unroll
+        for (int i = 0; i < NV4; ++i) {
+            const float4 a = load_add4<Act, ADD16>(add, r, h, lane + 32 * i);
+            v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
+            xr[lane + 32 * i] = v[i];
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+        if (!y) return;
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / static_cast<float>(NV4 * 128) + eps);
+#pragma unroll
+        for (int i = 0; i < NV4; ++i) {
+            const float4 g = wr[lane + 32 * i];
+            uint2 o;
+            o.x = Act::pack(v[i].x * inv * (one + g.x), v[i].y * inv * (one + g.y));
+            o.y = Act::pack(v[i].z * inv * (one + g.z), v[i].w * inv * (one + g.w));
+            yr[lane + 32 * i] = o;
+        }
+    } else {
+        const uint32_t nv = h >> 2;
+        for (uint32_t i = lane; i < nv; i += 32) {
+            float4 v = xr[i];
+            const float4 a = load_add4<Act, ADD16>(add, r, h, i);
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            xr[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        if (!y) return;
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / static_cast<float>(h) + eps);
+        for (uint32_t i = lane; i < nv; i += 32) {
+            const float4 v = xr[i];   // this lane's own stores of the first pass
+            const float4 g = wr[i];
+            uint2 o;
+            o.x = Act::pack(v.x * inv * (one + g.x), v.y * inv * (one + g.y));
+            o.y = Act::pack(v.z * inv * (one + g.z), v.w * inv * (one + g.w));
+            yr[i] = o;
+        }
     }
 }
 
@@ -353,18 +387,33 @@ int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* 
     return dc_check_launch(ctx, "rmsnorm");
 }
 
-int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const float* w, void* y, uint32_t rows, uint32_t h, float eps,
-                   uint32_t add_one) {
+static int add_rmsnorm_any(dc_ctx* ctx, void* stream, float* x, const void* add, bool add16, const float* w, void* y, uint32_t rows, uint32_t h, float eps,
+                           uint32_t add_one) {
     if (!ctx) return DC_INVALID_ARG;
     DC_REQUIRE(ctx, x && add && (!y || w), "add_rmsnorm: null operand");
     DC_REQUIRE(ctx, h % 4 == 0 && h > 0, "add_rmsnorm: H = %u must be a multiple of 4", h);
     DC_REQUIRE(ctx, aligned16(x) && aligned16(add) && (!y || (aligned16(w) && reinterpret_cast<uintptr_t>(y) % 8 == 0)), "add_rmsnorm: misaligned operand");
     if (rows == 0) return DC_OK;
-    if (ctx->act_dtype == DC_ACT_F16)
-        add_rmsnorm_kernel<ActF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(x, add, w, static_cast<uint16_t*>(y), rows, h, eps, add_one);
-    else
-        add_rmsnorm_kernel<ActBF16><<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(x, add, w, static_cast<uint16_t*>(y), rows, h, eps, add_one);
+    const bool f16 = ctx->act_dtype == DC_ACT_F16;
+    auto go = [&](auto kern) { kern<<<blocks_for(rows), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream)>>>(x, add, w, static_cast<uint16_t*>(y), rows, h, eps, add_one); };
+    if (h == 2560) {
+        if (add16) f16 ? go(add_rmsnorm_kernel<ActF16, true, 20>) : go(add_rmsnorm_kernel<ActBF16, true, 20>);
+        else f16 ? go(add_rmsnorm_kernel<ActF16, false, 20>) : go(add_rmsnorm_kernel<ActBF16, false, 20>);
+    } else {
+        if (add16) f16 ? go(add_rmsnorm_kernel<ActF16, true, 0>) : go(add_rmsnorm_kernel<ActBF16, true, 0>);
+        else f16 ? go(add_rmsnorm_kernel<ActF16, false, 0>) : go(add_rmsnorm_kernel<ActBF16, false, 0>);
+    }
     return dc_check_launch(ctx, "add_rmsnorm");
+}
+
+int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const float* w, void* y, uint32_t rows, uint32_t h, float eps,
+                   uint32_t add_one) {
+    return add_rmsnorm_any(ctx, stream, x, add, false, w, y, rows, h, eps, add_one);
+}
+
+int dc_add16_rmsnorm(dc_ctx* ctx, void* stream, float* x, const void* add16, const float* w, void* y, uint32_t rows, uint32_t h, float eps,
+                     uint32_t add_one) {
+    return add_rmsnorm_any(ctx, stream, x, add16, true, w, y, rows, h, eps, add_one);
 }
 
 int dc_embed(dc_ctx* ctx, void* stream, const uint32_t* ids, const void* table, float* out, uint32_t t, uint32_t h) {

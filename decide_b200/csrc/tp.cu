@@ -12,6 +12,7 @@
 // by the host (a file, a socket, torch.distributed: whatever launched the ranks).
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -23,7 +24,7 @@ struct NcclUniqueId {
     char internal[128];
 };
 typedef void* NcclComm;
-constexpr int kNcclFloat32 = 7;
+constexpr int kNcclFloat32 = 7, kNcclFloat16 = 6, kNcclBfloat16 = 9;
 constexpr int kNcclSum = 0;
 
 struct NcclApi {
@@ -108,6 +109,7 @@ int dc_tp_init(dc_ctx* ctx, const void* id128, uint32_t world, uint32_t rank) {
     ctx->tp_comm = comm;
     ctx->tp_world = world;
     ctx->tp_rank = rank;
+    if (const char* e = getenv("DECIDE_TP_EXCHANGE")) ctx->tp_exchange16 = strcmp(e, "16") == 0;
     return DC_OK;
 }
 
@@ -120,6 +122,24 @@ int dc_tp_all_reduce_f32(dc_ctx* ctx, void* stream, float* buf, size_t n) {
     const int rc = api->AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, ctx->tp_comm, static_cast<cudaStream_t>(stream));
     if (rc != 0) return dc_fail(ctx, DC_CUDA_ERROR, "ncclAllReduce: %s", api->GetErrorString(rc));
     ctx->launches++;
+    return DC_OK;
+}
+
+int dc_tp_all_reduce_16(dc_ctx* ctx, void* stream, void* buf, size_t n) {
+    if (!ctx) return DC_INVALID_ARG;
+    DC_REQUIRE(ctx, buf || n == 0, "dc_tp_all_reduce_16: null buffer");
+    if (ctx->tp_world <= 1 || n == 0) return DC_OK;
+    NcclApi* api = nccl_api(nullptr, 0);
+    if (!api || !ctx->tp_comm) return dc_fail(ctx, DC_INVALID_ARG, "dc_tp_all_reduce_16: no tensor-parallel group (dc_tp_init)");
+    const int rc = api->AllReduce(buf, buf, n, ctx->act_dtype == DC_ACT_F16 ? kNcclFloat16 : kNcclBfloat16, kNcclSum, ctx->tp_comm, static_cast<cudaStream_t>(stream));
+    if (rc != 0) return dc_fail(ctx, DC_CUDA_ERROR, "ncclAllReduce: %s", api->GetErrorString(rc));
+    ctx->launches++;
+    return DC_OK;
+}
+
+int dc_tp_set_exchange_16bit(dc_ctx* ctx, uint32_t on) {
+    if (!ctx) return DC_INVALID_ARG;
+    ctx->tp_exchange16 = on != 0;
     return DC_OK;
 }
 

@@ -266,6 +266,13 @@ class Norm(_Family):
         self.dev.call("dc_rmsnorm", _stream(stream), _ptr(x), _ptr(w), _ptr(y), _ptr(rowmap), rows, h, ld_in, ld_out, eps, int(add_one))
 
 
+    def add_rmsnorm(self, stream, x, add, w, y, rows, h, add_one: bool = True, eps: float = EPS):
+        """x[r] += add[r], then y[r] = rmsnorm(x[r]) (y None: only the add). `add` is fp32, or in the context's 16-bit type
+        (the partial sums of a tensor-parallel group; the reference's Ane::add_partial + rmsnorm, kernels/ane.rs:23)."""
+        name = "dc_add_rmsnorm" if add.dtype == torch.float32 else "dc_add16_rmsnorm"
+        self.dev.call(name, _stream(stream), _ptr(x), _ptr(add), _ptr(w), _ptr(y), rows, h, eps, int(add_one))
+
+
 class Embed(_Family):
     def embed(self, stream, ids, table, out, t, h):
         """out[t] = table[ids[t]] (bf16 → fp32) (kernels/embed.rs:16-22)."""

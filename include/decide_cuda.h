@@ -212,6 +212,9 @@ int dc_rmsnorm(dc_ctx* ctx, void* stream, const float* x, const float* w, void* 
  * projection join the residual), then, unless y is NULL, y[r] = rmsnorm(x[r]) as dc_rmsnorm writes it. */
 int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const float* w, void* y, uint32_t rows, uint32_t h,
                    float eps, uint32_t add_one);
+/* The same with `add16` in the context's 16-bit type (partial sums exchanged in 16 bits, dc_tp_set_exchange_16bit). */
+int dc_add16_rmsnorm(dc_ctx* ctx, void* stream, float* x, const void* add16, const float* w, void* y, uint32_t rows, uint32_t h,
+                     float eps, uint32_t add_one);
 
 /* ---- tensor-parallel group (no counterpart in the reference beyond its two-way GPU + Neural Engine MLP
  * split with a partial-sum add, forward.rs:270-303, 1286-1309) ----
@@ -227,6 +230,11 @@ int dc_add_rmsnorm(dc_ctx* ctx, void* stream, float* x, const float* add, const 
 int dc_tp_unique_id(void* id128, char* err, size_t err_len);
 int dc_tp_init(dc_ctx* ctx, const void* id128, uint32_t world, uint32_t rank);
 int dc_tp_all_reduce_f32(dc_ctx* ctx, void* stream, float* buf, size_t n);
+/* The exchange in the context's 16-bit type: n values of `buf` summed over the group in place (NCCL adds them in that
+ * type). dc_tp_set_exchange_16bit(ctx, 1), or DECIDE_TP_EXCHANGE=16 at dc_tp_init, makes a shard's forward store its
+ * partial sums in 16 bits, exchange half the bytes and widen them when they join the fp32 residual; default fp32. */
+int dc_tp_all_reduce_16(dc_ctx* ctx, void* stream, void* buf, size_t n);
+int dc_tp_set_exchange_16bit(dc_ctx* ctx, uint32_t on);
 uint32_t dc_tp_world(dc_ctx* ctx);
 uint32_t dc_tp_rank(dc_ctx* ctx);
 void dc_tp_destroy(dc_ctx* ctx);

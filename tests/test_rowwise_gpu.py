@@ -116,3 +116,25 @@ def test_convert_bf16_to_f16_with_report(k):
     assert rep.f16_flushed_to_zero == int(((want == 0) & (src.float() != 0)).sum())
     assert rep.f16_subnormal == int(((mag > 0) & (mag < 2 ** -14)).sum())
     assert rep.f16_overflow == 2 and rep.f16_flushed_to_zero >= 1 and rep.f16_subnormal >= 2
+
+
+@pytest.mark.parametrize("h", [2560, 512])
+@pytest.mark.parametrize("add16", [False, True])
+def test_add_rmsnorm(k, h, add16, act):
+    """The partial-sum add fused with the RMSNorm that follows (a tensor-parallel shard's norm): x += add in fp32, bit for bit;
+    then the norm of the sum. fp32 and 16-bit partial sums, the register-resident form (H = 2560) and the generic one."""
+    rows = 37
+    x = randn(81, rows, h)
+    add = randn(82, rows, h, std=0.5)
+    add_dev = add.to(act) if add16 else add
+    w = randn(83, h, std=0.02)
+    xd = x.cuda()
+    y = torch.empty(rows, h, dtype=act, device="cuda")
+    k.norm.add_rmsnorm(None, xd, add_dev.cuda(), w.cuda(), y, rows, h)
+    want_x = np32(x) + np32(add_dev.float())
+    assert np.array_equal(np32(xd), want_x)
+    want = cpu_ref.rmsnorm(want_x, np32(w), h, True)
+    assert_close(np32(y), want, atol=1e-3 if act == torch.float16 else 8e-3, rtol=half_ulp(act), what="add_rmsnorm")
+    x2 = x.cuda()
+    k.norm.add_rmsnorm(None, x2, add_dev.cuda(), None, None, rows, h)      # only the add
+    assert np.array_equal(np32(x2), want_x)
