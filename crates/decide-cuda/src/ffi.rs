@@ -104,6 +104,12 @@ extern "C" {
     pub fn dc_model_set_chunk(m: *mut DcModel, rows: u32) -> i32;
     pub fn dc_model_build_snapshot(m: *mut DcModel, stream: *mut c_void, prefix_ids: *const u32, n: u32) -> i32;
     pub fn dc_model_last_route(m: *mut DcModel) -> u32;
+    pub fn dc_model_last_start(m: *mut DcModel) -> u32;
+    pub fn dc_model_set_state_cache(m: *mut DcModel, entries: u32) -> i32;
+    pub fn dc_model_forget_states(m: *mut DcModel);
+    pub fn dc_model_state_cache_capacity(m: *mut DcModel) -> u32;
+    pub fn dc_model_cached_states(m: *mut DcModel, lens: *mut u32, cap: u32) -> u32;
+    pub fn dc_model_set_state_marker(m: *mut DcModel, ids: *const u32, n: u32) -> i32;
     pub fn dc_model_set_layer_limit(m: *mut DcModel, n: u32) -> i32;
     pub fn dc_model_buffer(m: *mut DcModel, name: *const c_char) -> *mut c_void;
     pub fn dc_model_read_buffer(m: *mut DcModel, name: *const c_char, dst: *mut c_void, bytes: usize) -> i32;

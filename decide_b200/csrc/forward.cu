@@ -48,6 +48,7 @@ struct dc_model {
     // Per Gated DeltaNet layer the 3 raw conv rows and the recurrent state, per attention layer its own K/V cache.
     struct Carry {
         char* mem = nullptr;
+        uint32_t kv_rows = 0;               // rows each K/V cache holds
         std::vector<void*> kc, vc;          // [layer] -> [max_rows, kv_dim] in the 16-bit type (null for linear layers)
         std::vector<float*> conv, state;    // [layer] -> [3, conv_dim], [nv, dv, dk] (null for attention layers)
     } carry, snap;
@@ -65,16 +66,31 @@ struct dc_model {
     std::map<std::array<uint32_t, 6>, GraphEntry> graphs;
     uint32_t chunk_rows = 0;                // 0 = one request runs whole (no carry needed)
     std::vector<uint32_t> snap_ids;         // token ids of the captured prefix; empty = no snapshot
-    uint32_t last_route = 0;                // 0 full, 1 from the prefix snapshot
+    uint32_t last_route = 0;                // 0 full, 1 from the prefix snapshot, 2 from a cached state
+    uint32_t last_start = 0;                // first row the last prefill computed
+    // The state cache (forward.rs:704-731, 845-905): on the snapshot route a request whose ids contain the marker leaves
+    // the state after the marker here; a later request that starts with exactly those ids runs from the end of them.
+    struct StateEntry {
+        Carry c;
+        std::vector<uint32_t> ids;          // the ids the state was captured from (prefix, state, marker)
+        uint64_t id = 0;                    // never reused: tells a replay whether its entry is still here
+    };
+    std::vector<StateEntry> states;         // most recently used first
+    std::vector<Carry> free_states;         // buffers of forgotten entries, kept for the next captures
+    uint32_t state_capacity = 2;            // DEFAULT_STATE_ENTRIES (forward.rs:75)
+    std::vector<uint32_t> state_marker{550, 39087, 10485, 198};   // STATE_MARKER (forward.rs:70)
+    uint64_t next_state_id = 1;
     struct Chunk {
         uint32_t c0, c1, a0, na;            // rows [c0, c1) of the request; its answers are sorted slots [a0, a0 + na)
+        bool capture = false;               // the request's state ends with this chunk: keep the carried state after it
     };
     // the batch the last dc_model_prefill left on the device, as it was laid out after truncation
     struct Resident {
         std::vector<uint32_t> given_seq_start;   // what the caller passed
         uint32_t rows = 0, n_seq = 0, max_len = 0, n_ans = 0, given_rows = 0;
         bool single = false;                     // ran through forward_single (chunks / snapshot)
-        uint32_t row0 = 0;                       // first row computed (the snapshot's length, or 0)
+        uint32_t row0 = 0;                       // first row computed (the snapshot's or the cached state's length, or 0)
+        uint64_t state_id = 0;                   // the cached state it started from (0: the snapshot, when row0 > 0)
         std::vector<Chunk> chunks;
     } cur;
     // pinned host staging for the host-buffer entry point
@@ -298,19 +314,28 @@ int run_forward(dc_model* m, cudaStream_t s, uint32_t rows, uint32_t n_seq, uint
     return DC_OK;
 }
 
-bool ensure_carry(dc_model* m, dc_model::Carry& c) {
-    if (c.mem) return true;
+// Device memory of one carried state; `kv_rows` = rows each K/V cache can hold (0: the model's row capacity). A Carry
+// that is too small is released and made again.
+bool ensure_carry(dc_model* m, dc_model::Carry& c, uint32_t kv_rows = 0) {
+    if (kv_rows == 0) kv_rows = m->max_rows;
+    if (c.mem && c.kv_rows >= kv_rows) return true;
+    cudaSetDevice(m->ctx->device);
+    if (c.mem) {
+        cudaFree(c.mem);   // waits for the work that uses it
+        c.mem = nullptr;
+    }
     const dc_dims& d = m->d;
-    const size_t kv = align_up(static_cast<size_t>(m->max_rows) * m->kv_dim * 2, 1024), cv = align_up(static_cast<size_t>(3) * m->conv_dim * 4, 1024),
+    const size_t kv = align_up(static_cast<size_t>(kv_rows) * m->kv_dim * 2, 1024), cv = align_up(static_cast<size_t>(3) * m->conv_dim * 4, 1024),
                  st = align_up(static_cast<size_t>(d.gdn_nv) * d.gdn_dv * d.gdn_dk * 4, 1024);
     size_t total = 0;
     for (uint32_t l = 0; l < d.n_layers; ++l) total += is_attention_layer(d, l) ? 2 * kv : cv + st;
-    cudaSetDevice(m->ctx->device);
     if (cudaMalloc(&c.mem, total) != cudaSuccess) {
         cudaGetLastError();
         c.mem = nullptr;
+        c.kv_rows = 0;
         return false;
     }
+    c.kv_rows = kv_rows;
     m->ctx->allocs++;
     c.kc.assign(d.n_layers, nullptr);
     c.vc.assign(d.n_layers, nullptr);
@@ -350,11 +375,23 @@ int copy_carry(dc_model* m, cudaStream_t s, const dc_model::Carry& from, dc_mode
     return DC_OK;
 }
 
+// Where a request's state ends (state_boundary, forward.rs:1503-1512): one past the first occurrence of `marker` in
+// ids[prefix, limit), `limit` being the first answer row; 0 when there is none. Correctness never rests on it: an entry
+// serves only ids that start with exactly the ids it was captured from.
+uint32_t state_boundary(const uint32_t* ids, uint32_t prefix, const std::vector<uint32_t>& marker, uint32_t limit) {
+    const uint32_t n = static_cast<uint32_t>(marker.size());
+    if (n == 0 || limit < prefix + n) return 0;
+    for (uint32_t i = prefix; i + n <= limit; ++i)
+        if (std::equal(marker.begin(), marker.end(), ids + i)) return i + n;
+    return 0;
+}
+
 // ONE request, chunk by chunk (encode_chunk over chunks(start, end), forward.rs:919-942, 1129-1142): all layers of a chunk,
 // then the next chunk. Linear layers carry their conv rows and recurrent state from chunk to chunk; attention layers append
 // the chunk's K/V rows to their own cache and attend over rows 0..=position. `row0 > 0` continues from state already in
-// `carry` (the restored prefix snapshot). The ids and absolute positions of the whole request are on the device.
-int forward_single(dc_model* m, cudaStream_t s, const std::vector<dc_model::Chunk>& chunks, uint32_t n_ans) {
+// `carry` (the restored prefix snapshot or cached state). After a chunk marked `capture` the carried state is copied to
+// `capture` (the reference snapshots inside the chunk, forward.rs:869-873; here the chunk ends at the state's boundary). The ids and absolute positions of the whole request are on the device.
+int forward_single(dc_model* m, cudaStream_t s, const std::vector<dc_model::Chunk>& chunks, uint32_t n_ans, dc_model::Carry* capture = nullptr) {
     dc_ctx* c = m->ctx;
     const dc_dims& d = m->d;
     const uint32_t H = d.hidden;
@@ -409,6 +446,8 @@ int forward_single(dc_model* m, cudaStream_t s, const std::vector<dc_model::Chun
         }
         if (ch.na && n_run == d.n_layers)   // this chunk's answer rows (chunk-relative, sorted) into their slots
             RUN("gather_rows", dc_gather_rows_f32(c, st, m->x, m->ans_rows + ch.a0, m->xs + static_cast<size_t>(ch.a0) * H, ch.na, H));
+        if (ch.capture && capture)          // rows 0 .. c1 of every K/V cache and every linear layer's state are final now
+            RUN("state_capture", copy_carry(m, s, m->carry, *capture, ch.c1));
     }
     if (n_ans && n_run == d.n_layers)
         RUN("final_head", dc_final_head(c, st, m->xs, m->final_norm, m->embed, m->cand, m->ncand, m->logits, n_ans, H, m->max_cand, d.eps));
@@ -575,6 +614,8 @@ void dc_model_destroy(dc_model* m) {
     if (m->arena) cudaFree(m->arena);
     if (m->carry.mem) cudaFree(m->carry.mem);
     if (m->snap.mem) cudaFree(m->snap.mem);
+    for (auto& e : m->states) cudaFree(e.c.mem);
+    for (auto& c : m->free_states) cudaFree(c.mem);
     if (m->host) cudaFreeHost(m->host);
     delete m;
 }
@@ -700,17 +741,38 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
     // every answer row past them.
     const uint32_t P = static_cast<uint32_t>(m->snap_ids.size());
     bool from_snapshot = n_seq == 1 && P > 0 && rows > P && m->layer_limit == 0 && std::equal(m->snap_ids.begin(), m->snap_ids.end(), h_ids);
-    for (uint32_t i = 0; from_snapshot && i < n_ans; ++i) from_snapshot = h_ans[i] >= P;
+    uint32_t first_row = rows;
+    for (uint32_t i = 0; i < n_ans; ++i) first_row = std::min(first_row, h_ans[i]);
+    from_snapshot = from_snapshot && first_row >= P;
+    // On the snapshot route: a follow-up runs from the longest cached state its ids start with (Plan::Hit); a request with
+    // a new state captures it at the boundary the marker gives (Plan::Capture), forward.rs:708-729.
+    int hit = -1;
+    uint32_t boundary = 0;
+    if (from_snapshot && n_ans > 0) {
+        for (size_t i = 0; i < m->states.size(); ++i) {
+            const auto& e = m->states[i];
+            if (e.ids.size() <= first_row && std::equal(e.ids.begin(), e.ids.end(), h_ids) &&
+                (hit < 0 || e.ids.size() > m->states[hit].ids.size()))
+                hit = static_cast<int>(i);
+        }
+        if (hit < 0 && m->state_capacity > 0) boundary = state_boundary(h_ids, P, m->state_marker, first_row);
+    }
+    const uint32_t row0 = hit >= 0 ? static_cast<uint32_t>(m->states[hit].ids.size()) : from_snapshot ? P : 0u;
     const bool single = n_seq == 1 && (m->chunk_rows > 0 || from_snapshot);
     std::vector<uint32_t> order(n_ans);          // sorted slot -> the caller's answer index
     std::vector<dc_model::Chunk> chunks;
     if (single) {
         for (uint32_t i = 0; i < n_ans; ++i) order[i] = i;
         std::stable_sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) { return h_ans[x] < h_ans[y]; });
-        const uint32_t row0 = from_snapshot ? P : 0u, step = m->chunk_rows ? m->chunk_rows : rows - row0;
+        const uint32_t step = m->chunk_rows ? m->chunk_rows : rows - row0;
         uint32_t slot = 0;
-        for (uint32_t c0 = row0; c0 < rows; c0 += step) {
+        for (uint32_t c0 = row0; c0 < rows;) {
             dc_model::Chunk ch{c0, std::min(rows, c0 + step), slot, 0};
+            if (boundary > c0 && boundary <= ch.c1) {   // the state ends inside this chunk: end the chunk there
+                ch.c1 = boundary;
+                ch.capture = true;
+            }
+            c0 = ch.c1;
             while (slot < n_ans && h_ans[order[slot]] < ch.c1) ++slot;
             ch.na = slot - ch.a0;
             chunks.push_back(ch);
@@ -725,9 +787,11 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
         }
         memcpy(h_ans, rel.data(), static_cast<size_t>(n_ans) * 4);
     }
-    m->last_route = from_snapshot ? 1u : 0u;
+    m->last_route = hit >= 0 ? 2u : from_snapshot ? 1u : 0u;
+    m->last_start = row0;
     m->cur.single = single;
-    m->cur.row0 = from_snapshot ? P : 0u;
+    m->cur.row0 = row0;
+    m->cur.state_id = hit >= 0 ? m->states[hit].id : 0;
     m->cur.chunks = chunks;
     m->cur.given_seq_start.assign(seq_start, seq_start + n_seq + 1);
     m->cur.rows = rows;
@@ -746,19 +810,41 @@ int dc_model_prefill(dc_model* m, void* stream, const uint32_t* ids, const uint3
     if (e == cudaSuccess && n_ans) e = cudaMemcpyAsync(m->cand, h_cand, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyHostToDevice, s);
     if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: host-to-device copy failed: %s", cudaGetErrorString(e));
 
+    dc_model::StateEntry fresh;   // Plan::Capture: new buffers, a forgotten entry's, or the least recently used entry's
+    if (boundary) {
+        if (!m->free_states.empty()) {
+            fresh.c = m->free_states.back();
+            m->free_states.pop_back();
+        } else if (m->states.size() >= m->state_capacity) {
+            fresh.c = m->states.back().c;
+            m->states.pop_back();
+        }
+        if (!ensure_carry(m, fresh.c, boundary)) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: cannot allocate a state-cache entry of %u rows", boundary);
+        fresh.ids.assign(h_ids, h_ids + boundary);
+        fresh.id = m->next_state_id++;
+    }
     if (single) {
-        if (from_snapshot) rc = copy_carry(m, s, m->snap, m->carry, P);
-        if (rc == DC_OK) rc = forward_single(m, s, chunks, n_ans);
+        if (hit >= 0) rc = copy_carry(m, s, m->states[hit].c, m->carry, row0);
+        else if (from_snapshot) rc = copy_carry(m, s, m->snap, m->carry, P);
+        if (rc == DC_OK) rc = forward_single(m, s, chunks, n_ans, boundary ? &fresh.c : nullptr);
     } else {
         rc = run_forward(m, s, rows, n_seq, max_len, n_ans);
     }
-    if (rc != DC_OK) return rc;
-    if (n_ans) {
+    if (rc == DC_OK && n_ans) {
         e = cudaMemcpyAsync(h_logits, m->logits, static_cast<size_t>(n_ans) * m->max_cand * 4, cudaMemcpyDeviceToHost, s);
-        if (e != cudaSuccess) return dc_fail(ctx, DC_CUDA_ERROR, "prefill: device-to-host copy failed: %s", cudaGetErrorString(e));
+        if (e != cudaSuccess) rc = dc_fail(ctx, DC_CUDA_ERROR, "prefill: device-to-host copy failed: %s", cudaGetErrorString(e));
     }
-    rc = dc_check_status(ctx, s);  // synchronises
-    if (rc != DC_OK) return rc;
+    if (rc == DC_OK) rc = dc_check_status(ctx, s);  // synchronises
+    if (rc != DC_OK) {
+        if (fresh.c.mem) m->free_states.push_back(fresh.c);   // its contents are unknown; its buffers serve the next capture
+        return rc;
+    }
+    if (boundary) {                       // the new state is the most recently used
+        m->cur.state_id = 0;              // a replay of this request starts from the snapshot again
+        m->states.insert(m->states.begin(), std::move(fresh));
+    } else if (hit > 0) {
+        std::rotate(m->states.begin(), m->states.begin() + hit, m->states.begin() + hit + 1);
+    }
     if (n_ans) {
         if (single) {   // back from sorted slots to the caller's order
             for (uint32_t a = 0; a < n_ans; ++a)
@@ -788,7 +874,14 @@ int dc_model_forward_resident(dc_model* m, void* stream, const uint32_t* seq_sta
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (m->cur.single) {
         if (m->cur.row0) {
-            const int rc = copy_carry(m, s, m->snap, m->carry, m->cur.row0);
+            const dc_model::Carry* from = &m->snap;
+            if (m->cur.state_id) {
+                from = nullptr;
+                for (const auto& e : m->states)
+                    if (e.id == m->cur.state_id) from = &e.c;
+                DC_REQUIRE(ctx, from, "forward_resident: the cached state the last dc_model_prefill started from is no longer held");
+            }
+            const int rc = copy_carry(m, s, *from, m->carry, m->cur.row0);
             if (rc != DC_OK) return rc;
         }
         return forward_single(m, s, m->cur.chunks, n_ans);
@@ -811,6 +904,7 @@ int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_id
     if (!m) return DC_INVALID_ARG;
     dc_ctx* ctx = m->ctx;
     m->snap_ids.clear();
+    dc_model_forget_states(m);
     if (n == 0) return DC_OK;
     DC_REQUIRE(ctx, prefix_ids && n < m->max_rows, "build_snapshot: %u prefix rows (capacity %u)", n, m->max_rows);
     for (uint32_t i = 0; i < n; ++i) DC_REQUIRE(ctx, prefix_ids[i] < m->d.vocab, "build_snapshot: token id %u out of the vocabulary", prefix_ids[i]);
@@ -837,8 +931,54 @@ int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_id
     return DC_OK;
 }
 
-// 0: the last dc_model_prefill ran every row; 1: it started from the prefix snapshot.
+// 0: the last dc_model_prefill ran every row; 1: it started from the prefix snapshot; 2: from a cached state (Route,
+// forward.rs:196-206). dc_model_last_start: the first row it computed (last_start, forward.rs:686-692).
 uint32_t dc_model_last_route(dc_model* m) { return m ? m->last_route : 0; }
+uint32_t dc_model_last_start(dc_model* m) { return m ? m->last_start : 0; }
+
+// Forward::set_state_cache (forward.rs:735-744): hold up to `entries` states (at most DC_MAX_STATE_ENTRIES; 0 = off).
+// Shrinking evicts the least recently used entries and releases their memory.
+int dc_model_set_state_cache(dc_model* m, uint32_t entries) {
+    if (!m) return DC_INVALID_ARG;
+    DC_REQUIRE(m->ctx, entries <= DC_MAX_STATE_ENTRIES, "a state cache of %u entries; at most %u", entries, DC_MAX_STATE_ENTRIES);
+    cudaSetDevice(m->ctx->device);
+    m->state_capacity = entries;
+    while (m->states.size() > entries) {
+        cudaFree(m->states.back().c.mem);
+        m->states.pop_back();
+    }
+    while (m->states.size() + m->free_states.size() > entries) {
+        cudaFree(m->free_states.back().mem);
+        m->free_states.pop_back();
+    }
+    return DC_OK;
+}
+
+// Forward::forget_states (forward.rs:746-752): every cached state is forgotten; the buffers serve the next captures.
+void dc_model_forget_states(dc_model* m) {
+    if (!m) return;
+    for (auto& e : m->states) m->free_states.push_back(e.c);
+    m->states.clear();
+}
+
+uint32_t dc_model_state_cache_capacity(dc_model* m) { return m ? m->state_capacity : 0; }
+
+// Forward::cached_states (forward.rs:759-763): the length in tokens of each cached state, most recently used first. Writes
+// at most `cap` lengths and returns how many states are held.
+uint32_t dc_model_cached_states(dc_model* m, uint32_t* lens, uint32_t cap) {
+    if (!m) return 0;
+    for (size_t i = 0; i < m->states.size() && i < cap && lens; ++i) lens[i] = static_cast<uint32_t>(m->states[i].ids.size());
+    return static_cast<uint32_t>(m->states.size());
+}
+
+// Forward::set_state_marker (forward.rs:765-772): the token ids that end a request's state. Empties the cache.
+int dc_model_set_state_marker(dc_model* m, const uint32_t* ids, uint32_t n) {
+    if (!m) return DC_INVALID_ARG;
+    DC_REQUIRE(m->ctx, ids && n > 0, "an empty state marker");
+    m->state_marker.assign(ids, ids + n);
+    dc_model_forget_states(m);
+    return DC_OK;
+}
 
 // on = 0: every forward is enqueued kernel by kernel; on = 1 (default; DECIDE_GRAPHS=0 turns it off at creation): a batched
 // forward of a shape seen before is replayed from its CUDA graph.

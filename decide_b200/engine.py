@@ -123,7 +123,37 @@ class Engine:
 
     @property
     def last_route(self) -> str:
-        return ("full", "snapshot")[int(self.lib.dc_model_last_route(self.handle))]
+        """How the last `logits` call ran its request (Route, forward.rs:196-206)."""
+        return ("full", "snapshot", "state_cache")[int(self.lib.dc_model_last_route(self.handle))]
+
+    @property
+    def last_start(self) -> int:
+        """The first row the last `logits` call computed (Forward::last_start, forward.rs:686-692)."""
+        return int(self.lib.dc_model_last_start(self.handle))
+
+    def set_state_cache(self, entries: int):
+        """Hold up to `entries` (at most 4) states for follow-up questions; 0 turns the cache off
+        (Forward::set_state_cache, forward.rs:735-744)."""
+        self._call("dc_model_set_state_cache", entries)
+
+    def forget_states(self):
+        """Forget every cached state, keeping the buffers (Forward::forget_states, forward.rs:746-752)."""
+        self.lib.dc_model_forget_states(self.handle)
+
+    @property
+    def state_cache_capacity(self) -> int:
+        return int(self.lib.dc_model_state_cache_capacity(self.handle))
+
+    def cached_states(self) -> list[int]:
+        """Length in tokens of each cached state, most recently used first (Forward::cached_states, forward.rs:759-763)."""
+        lens = np.zeros(4, dtype=np.uint32)
+        n = int(self.lib.dc_model_cached_states(self.handle, _u32p(lens), 4))
+        return [int(v) for v in lens[:n]]
+
+    def set_state_marker(self, marker_ids):
+        """The token ids that end a request's state; empties the cache (Forward::set_state_marker, forward.rs:765-772)."""
+        ids = np.ascontiguousarray(marker_ids, dtype=np.uint32)
+        self._call("dc_model_set_state_marker", _u32p(ids) if len(ids) else None, len(ids))
 
     @property
     def resident_rows(self) -> int:

@@ -444,8 +444,28 @@ int dc_model_set_chunk(dc_model* m, uint32_t rows);
  * that prefix, that is longer than it and whose answer rows all lie past it restores the state and runs
  * only the remaining rows; any other request runs in full. n = 0 drops the snapshot. Synchronises. */
 int dc_model_build_snapshot(dc_model* m, void* stream, const uint32_t* prefix_ids, uint32_t n);
-/* Route of the last dc_model_prefill: 0 = every row was run, 1 = it started from the prefix snapshot. */
+/* Route of the last dc_model_prefill (Route, forward.rs:196-206): 0 = every row was run, 1 = it started
+ * from the prefix snapshot, 2 = it started from a cached state. dc_model_last_start: the first row it
+ * computed (Forward::last_start, forward.rs:686-692). */
 uint32_t dc_model_last_route(dc_model* m);
+uint32_t dc_model_last_start(dc_model* m);
+
+/* The state cache for follow-up questions (forward.rs:704-731, 845-905). On the snapshot route, a
+ * request whose ids hold the state marker between the prefix and its first answer row leaves the state
+ * after the marker (every layer's conv rows, recurrent state and K/V rows up to there) in the cache,
+ * evicting the least recently used entry when `entries` are held. A later request that starts with
+ * exactly the ids an entry was captured from, and whose answer rows lie at or past their end, restores
+ * that state and runs only the rows after it (route 2); among several such entries the longest wins.
+ * Capacity 2 and the marker {550, 39087, 10485, 198} at creation (DEFAULT_STATE_ENTRIES, STATE_MARKER,
+ * forward.rs:70-75). An entry's memory (each linear layer's state + K/V rows of the state's length) is
+ * allocated when a state is first captured into it: that request allocates, later ones reuse it.
+ * Results must not depend on the cache beyond fp32 rounding. */
+#define DC_MAX_STATE_ENTRIES 4u
+int dc_model_set_state_cache(dc_model* m, uint32_t entries);               /* Forward::set_state_cache, forward.rs:735; 0 = off */
+void dc_model_forget_states(dc_model* m);                                   /* Forward::forget_states, forward.rs:749 */
+uint32_t dc_model_state_cache_capacity(dc_model* m);                        /* forward.rs:755 */
+uint32_t dc_model_cached_states(dc_model* m, uint32_t* lens, uint32_t cap); /* Forward::cached_states, forward.rs:761; returns the count */
+int dc_model_set_state_marker(dc_model* m, const uint32_t* ids, uint32_t n); /* Forward::set_state_marker, forward.rs:767; empties the cache */
 
 /* Runs only the first `n` layers and skips the head when n < n_layers (0 restores all layers): the
  * residual stream after layer n-1 is then in buffer "x" (debug_layers, forward.rs:778-797). While a

@@ -153,6 +153,93 @@ def test_chunk_size_and_snapshot_do_not_change_the_logits(dev):
     eng.close()
 
 
+def test_state_cache_serves_follow_up_questions(dev):
+    """The reference's state cache (forward.rs:704-731, 845-905): on the snapshot route a request whose ids hold the marker
+    leaves the state after it in the cache; a follow-up that starts with the same ids runs only the rows after the state
+    (route "state_cache") and gets the logits a cold run gives, to fp32 rounding. Least recently used entries are evicted;
+    the longest matching entry wins; an answer row inside the state, a changed state token or an emptied cache run cold."""
+    sd, eng = make(SMALL, dev, 51, max_rows=512, max_seqs=2, max_answers=16, max_cand=8)
+    marker = np.array([991, 992, 993], np.uint32)
+    P = 64
+
+    def request(seed, state_len, tail_len, answers, marker_at_end=True):
+        """prefix (shared) | state tokens | marker | `tail_len` question tokens; answer rows counted from the end."""
+        rs = np.random.RandomState(seed)
+        prefix = np.random.RandomState(7).randint(0, 900, P)
+        state = np.random.RandomState(seed // 10).randint(0, 900, state_len)      # requests of one decade share a state
+        tail = rs.randint(0, 900, tail_len)
+        ids = np.concatenate([prefix, state, marker if marker_at_end else [], tail]).astype(np.uint32)
+        rows = np.array([len(ids) - a for a in answers], np.uint32)
+        cand = np.stack([rs.choice(900, 8, replace=False) for _ in answers]).astype(np.uint32)
+        return Batch(ids, np.array([0, len(ids)], np.uint32), rows, cand, np.full(len(answers), 8, np.uint32))
+
+    first, follow = request(100, 150, 40, (30, 12, 3)), request(101, 150, 55, (4, 20))
+    boundary = P + 150 + 3
+    eng.set_state_cache(0)
+    eng.build_snapshot(first.ids[:P])
+    cold_first, cold_follow = eng.logits(first), eng.logits(follow)
+    assert eng.last_route == "snapshot" and eng.last_start == P and eng.cached_states() == []
+    try:
+        eng.set_state_marker(marker)
+        eng.set_state_cache(2)
+        assert eng.state_cache_capacity == 2
+        got = eng.logits(first)                                     # captures the state
+        assert eng.last_route == "snapshot" and eng.cached_states() == [boundary]
+        assert np.abs(got - cold_first).max() < 2e-3
+        eng.forward_resident(first)                                 # a replay does not capture again
+        dev.check_status()
+        assert eng.cached_states() == [boundary]
+        got = eng.logits(follow)                                    # the follow-up
+        assert eng.last_route == "state_cache" and eng.last_start == boundary and eng.resident_rows == follow.rows - 3
+        d = np.abs(got - cold_follow).max()
+        assert d < 2e-3, f"the follow-up's logits differ from the cold run's by {d:.2e}"
+        eng.forward_resident(follow)
+        dev.check_status()
+        eng.set_chunk(32)                                           # a follow-up in chunks
+        assert np.abs(eng.logits(follow) - cold_follow).max() < 2e-3 and eng.last_route == "state_cache"
+        got = eng.logits(first)                                     # the first request again is a follow-up of itself
+        assert eng.last_route == "state_cache" and np.abs(got - cold_first).max() < 2e-3
+        eng.set_chunk(0)
+        # two more states: capacity 2 evicts the least recently used one
+        second, third = request(200, 90, 30, (5,)), request(300, 120, 30, (5,))
+        eng.logits(second)
+        assert eng.cached_states() == [P + 90 + 3, boundary]
+        eng.logits(follow)                                          # touches the first state: most recently used again
+        assert eng.cached_states() == [boundary, P + 90 + 3]
+        eng.logits(third)
+        assert eng.cached_states() == [P + 120 + 3, boundary] and eng.last_route == "snapshot"
+        eng.logits(request(201, 90, 30, (5,)))                      # the evicted state: cold again, captured again
+        assert eng.last_route == "snapshot" and eng.cached_states() == [P + 90 + 3, P + 120 + 3]
+        # an answer row inside the cached state: no hit, and no boundary before the answer either
+        eng.logits(follow)
+        early = Batch(follow.ids, follow.seq_start, np.array([P + 20, follow.rows - 1], np.uint32), follow.cand, follow.ncand)
+        eng.logits(early)
+        assert eng.last_route == "snapshot" and eng.last_start == P
+        # a changed state token: not a follow-up
+        changed = Batch(follow.ids.copy(), follow.seq_start, follow.ans_rows, follow.cand, follow.ncand)
+        changed.ids[P + 10] ^= 1
+        eng.logits(changed)
+        assert eng.last_route == "snapshot"
+        # no marker: nothing is captured
+        n = len(eng.cached_states())
+        eng.forget_states()
+        assert eng.cached_states() == []
+        eng.logits(request(400, 80, 30, (5,), marker_at_end=False))
+        assert eng.last_route == "snapshot" and eng.cached_states() == [] and n == 2
+        eng.logits(follow)                                          # forgotten: cold, captured into a kept buffer
+        assert eng.last_route == "snapshot" and eng.cached_states() == [boundary]
+        with pytest.raises(Exception, match="at most 4"):
+            eng.set_state_cache(5)
+        eng.set_state_cache(0)                                      # off: entries dropped, nothing captured
+        assert eng.cached_states() == []
+        got = eng.logits(follow)
+        assert eng.last_route == "snapshot" and np.array_equal(got, cold_follow)
+    finally:
+        eng.set_chunk(0)
+        eng.build_snapshot([])
+    eng.close()
+
+
 def test_engines_agree_on_the_whole_model(dev):
     """The same batch through the tcgen05 kernels (delta rule with the conv fused in, attention) and through
     the mma.sync kernels (separate conv): identical decisions, logits within a fraction of the gold tolerance."""
