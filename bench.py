@@ -249,6 +249,49 @@ def run_engine(args):
             latency[f"tokens_{toks}"] = {"p50_ms": float(np.percentile(samples, 50)), "p95_ms": float(np.percentile(samples, 95)), "runs": len(samples),
                                          "rows_computed": eng.resident_rows, "per_op_ms": per_op}
 
+        # follow-up questions about one state (the reference's follow-up demo, crates/decide-cli/src/race.rs:707-733, and
+        # `decide bench`, bench.rs:224): a 2,491-token request cold from a 300-token prefix snapshot (the state cache
+        # forgotten before every call, the new state captured inside it), then other questions about the same state, which
+        # run only the 184 rows after it
+        from decide_b200.synth import Batch
+        rs = np.random.RandomState(11)
+        marker = np.array([550, 39087, 10485, 198], np.uint32)        # the engine's default state marker
+        prefix, state = rs.randint(0, dims.vocab, 300), rs.randint(0, dims.vocab, 2491 - 300 - 4 - 184)
+
+        def ask(seed):
+            q = np.random.RandomState(seed)
+            ids = np.concatenate([prefix, state, marker, q.randint(0, dims.vocab, 184)]).astype(np.uint32)
+            ans = np.array([len(ids) - o for o in (52, 33, 7)], np.uint32)
+            cand = np.zeros((3, CANDS), np.uint32)
+            for i in range(3):
+                cand[i] = q.choice(dims.vocab, CANDS, replace=False)
+            return Batch(ids, np.array([0, len(ids)], np.uint32), ans, cand, np.full(3, CANDS, np.uint32))
+
+        def timed(req, forget):
+            out = []
+            for i in range(13):
+                if forget:
+                    eng.forget_states()
+                e0.record(stream)
+                got = eng.logits(req)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                if i >= 3:
+                    out.append(e0.elapsed_time(e1))
+            return got, {"p50_ms": float(np.percentile(out, 50)), "p95_ms": float(np.percentile(out, 95)), "runs": len(out),
+                         "route": eng.last_route, "rows_computed": eng.resident_rows - eng.last_start}
+
+        eng.build_snapshot(prefix)
+        first, second = ask(1), ask(2)
+        _, cold = timed(first, forget=True)
+        cold_second, _ = timed(second, forget=True)
+        eng.forget_states()
+        eng.logits(first)                                   # leaves the state in the cache
+        warm_second, follow = timed(second, forget=False)
+        follow["max_abs_dlogit_vs_cold"] = float(np.abs(warm_second - cold_second).max())
+        latency["follow_up"] = {"cold": cold, "follow_up": follow, "speedup_p50": cold["p50_ms"] / follow["p50_ms"]}
+        eng.build_snapshot([])
+
     # ---- strong scaling (N > 1): the same 64 requests on every N, sharded by request; results checked across ranks
     strong = None
     if world > 1:
