@@ -84,6 +84,7 @@ extern "C" {
     pub fn dc_kv_norm_rope(ctx: *mut DcCtx, stream: *mut c_void, pkv: *const f32, kw: *const f32, inv_freq: *const f32, kc: *mut c_void, vc: *mut c_void, rows: u32, ldkv: u32, kcol: u32, vcol: u32, pos0: u32, pos: *const u32, cache_rows: u32, nkv: u32, hd: u32, rot: u32, eps: f32) -> i32;
     pub fn dc_attention(ctx: *mut DcCtx, stream: *mut c_void, q: *const c_void, kc: *const c_void, vc: *const c_void, gate: *const f32, qpos: *const u32, y: *mut c_void, rows: u32, ldg: u32, nq: u32, nkv: u32, hd: u32, seq_start: *const u32, n_seq: u32, max_len: u32) -> i32;
     pub fn dc_attention_rows(ctx: *mut DcCtx, stream: *mut c_void, q: *const c_void, kc: *const c_void, vc: *const c_void, gate: *const f32, qpos: *const u32, kv_start: *const u32, y: *mut c_void, rows: u32, ldg: u32, nq: u32, nkv: u32, hd: u32) -> i32;
+    pub fn dc_attention_rows_scratch_bytes(ctx: *mut DcCtx, rows: u32, nq: u32, nkv: u32) -> usize;
     pub fn dc_conv_silu_l2(ctx: *mut DcCtx, stream: *mut c_void, p: *const f32, prev: *const f32, w: *const f32, q: *mut f32, k: *mut f32, v: *mut f32, t: u32, ldp: u32, nk: u32, nv: u32, dk: u32, dv: u32, seq_start: *const u32, n_seq: u32, max_len: u32) -> i32;
     pub fn dc_conv_state_update(ctx: *mut DcCtx, stream: *mut c_void, p: *const f32, prev_in: *const f32, prev_out: *mut f32, t: u32, ldp: u32, conv_dim: u32) -> i32;
     pub fn dc_gated_delta(ctx: *mut DcCtx, stream: *mut c_void, q: *const f32, k: *const f32, v: *const f32, a: *const f32, b: *const f32, a_log: *const f32, dt_bias: *const f32, state_in: *const f32, state_out: *mut f32, o: *mut f32, t: u32, ldab: u32, write_state: u32, nk: u32, nv: u32, dk: u32, dv: u32, seq_start: *const u32, n_seq: u32, max_len: u32) -> i32;

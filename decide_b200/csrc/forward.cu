@@ -572,8 +572,10 @@ dc_model* dc_model_create(dc_ctx* ctx, const dc_dims* dims, const dc_layer_weigh
     // scratch of the chunked delta rule and of the attention's transposed V for the largest batch, so that no forward
     // allocates; every kernel variant opted in to its shared memory now (Gemm::warm_up's role, gemm.rs:89-107)
     void* ws = nullptr;
-    if (dc_get_workspace(ctx, std::max(dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv), dc_attention_tc_scratch_bytes(max_rows, max_seqs, d.nkv)),
-                         "dc_model_create", &ws) != DC_OK ||
+    size_t ws_bytes = std::max(dc_gated_delta_scratch_bytes(max_rows, max_seqs, d.gdn_nv), dc_attention_tc_scratch_bytes(max_rows, max_seqs, d.nkv));
+    for (uint32_t r = 1; r <= m->max_answers; ++r)   // the answer rows' attention slices the keys more finely the fewer rows there are
+        ws_bytes = std::max(ws_bytes, dc_attention_rows_scratch_bytes(ctx, r, d.nq, d.nkv));
+    if (dc_get_workspace(ctx, ws_bytes, "dc_model_create", &ws) != DC_OK ||
         dc_warm_up(ctx) != DC_OK) {
         cudaFree(m->arena);
         delete m;

@@ -297,10 +297,14 @@ int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void* kc, const
  * forward.rs:1176-1178: a few query rows at given positions over the whole cache) ----
  * As dc_attention without seq_start, plus kv_start (u32 [rows], NULL = all 0): query row r attends
  * cache rows kv_start[r] .. kv_start[r] + qpos[r], i.e. the cache rows of its own request in a
- * packed batch. Built for few rows: one CTA per (row, kv head), fp32 throughout. nq / nkv <= 16. */
+ * packed batch. Built for few rows: one CTA per (row, kv head, slice of the keys), fp32 throughout;
+ * when rows * nkv would leave most SMs idle each row's keys are cut into slices whose partial sums go
+ * through the context workspace (dc_attention_rows_scratch_bytes: reserve it before freezing the
+ * workspace) and are joined in slice order. nq / nkv <= 16. */
 int dc_attention_rows(dc_ctx* ctx, void* stream, const void* q, const void* kc, const void* vc, const float* gate,
                       const uint32_t* qpos, const uint32_t* kv_start, void* y, uint32_t rows, uint32_t ldg, uint32_t nq,
                       uint32_t nkv, uint32_t hd);
+size_t dc_attention_rows_scratch_bytes(dc_ctx* ctx, uint32_t rows, uint32_t nq, uint32_t nkv);
 
 /* ---- Conv::conv_silu_l2 (kernels/conv.rs:21-36; spec cpu_ref.rs:55-81) ----
  * Depthwise causal conv (kernel 4) + SiLU over the qkv columns 0..(2nk+nv)*128 of `t` rows of p (fp32,

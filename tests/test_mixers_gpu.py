@@ -113,17 +113,20 @@ def test_attention_scattered_query_positions(k):
     assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
 
 
+@pytest.mark.parametrize("repeat", [1, 20], ids=["few-rows-sliced-keys", "many-rows"])
 @pytest.mark.parametrize("gated", [True, False])
-def test_attention_rows_over_packed_caches(k, gated, act):
+def test_attention_rows_over_packed_caches(k, gated, act, repeat):
     """The pruned last layer's attention: a few answer rows of several requests, each attending the cache rows of its own
-    request up to its position (1 key, a tile boundary, more than two tiles of 256), 4 query heads per kv head."""
+    request up to its position (1 key, a tile boundary, more than two tiles of 256), 4 query heads per kv head. With few rows
+    the kernel cuts each row's keys into slices and joins them (9 rows x 2 kv heads: 17 slices, most of them empty for the
+    short rows); with many rows (180 x 2 CTAs) every row is one slice."""
     nq, nkv, hd = 8, 2, 128
     lens = [603, 1, 257, 700]
     starts = np.concatenate([[0], np.cumsum(lens)])
     total = int(starts[-1])
     kc = randn(61, total, nkv, hd).to(act)
     vc = randn(62, total, nkv, hd).to(act)
-    picks = [(0, 602), (0, 0), (0, 255), (0, 256), (1, 0), (2, 256), (3, 699), (3, 511), (3, 512)]   # (request, position)
+    picks = [(0, 602), (0, 0), (0, 255), (0, 256), (1, 0), (2, 256), (3, 699), (3, 511), (3, 512)] * repeat   # (request, position)
     rows = len(picks)
     q = randn(63, rows, nq, hd).to(act)
     gate = randn(64, rows, nq * hd + 16) if gated else None
