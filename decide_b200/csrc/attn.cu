@@ -20,6 +20,7 @@ constexpr int BQ = 64;   // query rows per CTA
 constexpr int BKV = 64;  // cache rows per tile
 constexpr int kThreads = 128;
 constexpr float kMasked = -1e30f;
+constexpr uint32_t kTcMinChunkRows = 64;   // a chunk of at least this many rows over a longer cache runs on the tcgen05 kernel
 
 // element (row, col) of a [rows][128] bf16 tile: 16-byte chunks XOR-swizzled by the row
 __device__ __forceinline__ uint32_t tile_off(int row, int col) {
@@ -353,8 +354,10 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
     DC_REQUIRE(ctx, nkv >= 1 && nq % nkv == 0, "attention: %u query heads over %u kv heads", nq, nkv);
     DC_REQUIRE(ctx, !gate || (ldg >= nq * hd && ldg % 4 == 0 && aligned16(gate)), "attention: ldg = %u must cover the gate columns, be a multiple of 4, gate 16-byte aligned", ldg);
     DC_REQUIRE(ctx, aligned16(q) && aligned16(kc) && aligned16(vc) && reinterpret_cast<uintptr_t>(y) % 8 == 0, "attention: q, kc, vc must be 16-byte aligned");
+    uint32_t kv_len = 0;   // without seq_start: max_len, if given, is the number of cache rows in use (every position is below it)
     if (!seq_start) {
         n_seq = 1;
+        kv_len = max_len;
         max_len = rows;
     }
     DC_REQUIRE(ctx, n_seq >= 1 && n_seq <= 65535 && nq <= 65535, "attention: %u sequences", n_seq);
@@ -366,8 +369,10 @@ extern "C" int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void
                                                  gate, qpos, static_cast<uint16_t*>(y), rows, ldg, nq, nkv, scale, seq_start, n_seq);
         return dc_check_launch(ctx, "attention (baseline)");
     }
-    if (seq_start && ctx->attn_engine == DC_ENGINE_TCGEN05)
-        return dc_attention_tc(ctx, s, q, kc, vc, gate, qpos, y, rows, ldg, nq, nkv, seq_start, n_seq, max_len);
+    // The tcgen05 kernel takes packed batches, and a chunk of one sequence that continues a longer cache when the caller says
+    // how long the cache is (a short chunk stays on the mma.sync kernel: transposing V for it would cost more than it saves).
+    if (ctx->attn_engine == DC_ENGINE_TCGEN05 && (seq_start || (kv_len >= rows && rows >= kTcMinChunkRows)))
+        return dc_attention_tc(ctx, s, q, kc, vc, gate, qpos, y, rows, ldg, nq, nkv, seq_start, n_seq, max_len, kv_len);
     constexpr size_t smem = kFastSmem;
     auto fast = ctx->act_dtype == DC_ACT_F16 ? attn_fast_kernel<ActF16> : attn_fast_kernel<ActBF16>;
     {

@@ -68,12 +68,13 @@ __host__ __device__ __forceinline__ uint32_t vt_col(uint32_t row_lo, uint32_t se
 // vt[(head * 128 + d) * ldt + vt_col(seq) + t] = vc[(row_lo + t) * nkv * 128 + head * 128 + d]; columns from the end of a
 // sequence to the start of the next one are zero-filled.
 __global__ void __launch_bounds__(256) v_transpose_kernel(const uint16_t* __restrict__ vc, uint16_t* __restrict__ vt, uint32_t rows, uint32_t nkv,
-                                                          uint32_t ldt, const uint32_t* __restrict__ seq_start, uint32_t n_seq) {
+                                                          uint32_t ldt, const uint32_t* __restrict__ seq_start, uint32_t n_seq, uint32_t kv_len) {
     __shared__ uint16_t tile[64][HD + 8];
     const uint32_t seq = blockIdx.z, head = blockIdx.y, t0 = blockIdx.x * 64;
-    const uint32_t row_lo = seq_start[seq], len = seq_start[seq + 1] - row_lo;
+    // without seq_start: one sequence whose cache is rows 0 .. kv_len
+    const uint32_t row_lo = seq_start ? seq_start[seq] : 0u, len = seq_start ? seq_start[seq + 1] - row_lo : kv_len;
     const uint32_t col0 = vt_col(row_lo, seq);
-    const uint32_t col_end = seq + 1 < n_seq ? vt_col(seq_start[seq + 1], seq + 1) : ldt;   // first column of the next sequence
+    const uint32_t col_end = seq_start && seq + 1 < n_seq ? vt_col(seq_start[seq + 1], seq + 1) : ldt;   // first column of the next sequence
     if (col0 + t0 >= col_end) return;
     for (int e = threadIdx.x; e < 64 * 16; e += 256) {
         const int r = e >> 4, c8 = (e & 15) * 8;
@@ -97,9 +98,11 @@ template <typename Act>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t ldg, uint32_t nq, uint32_t nkv,
-               float scale_log2, const uint32_t* __restrict__ seq_start, int* __restrict__ status) {
+               float scale_log2, const uint32_t* __restrict__ seq_start, uint32_t q_len, int* __restrict__ status) {
     const uint32_t seq = blockIdx.z, head = blockIdx.y;
-    const uint32_t row_lo = seq_start[seq], len = seq_start[seq + 1] - row_lo;
+    // without seq_start: q_len query rows of one sequence (a chunk that continues a longer cache; the cache starts at row 0
+    // and each query row's position says how far it attends)
+    const uint32_t row_lo = seq_start ? seq_start[seq] : 0u, len = seq_start ? seq_start[seq + 1] - row_lo : q_len;
     // query tiles are handed out last-first: the tiles with the most cache rows to visit start first
     const uint32_t r0 = (gridDim.x - 1 - blockIdx.x) * TQ;
     if (r0 >= len) return;
@@ -448,19 +451,22 @@ int dc_attention_tc_warm(dc_ctx* ctx) {
 }
 
 int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,
-                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len) {
+                    uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len, uint32_t kv_len) {
+    // Packed batch (seq_start): query rows and cache rows are packed alike, `rows` of each. One sequence without seq_start:
+    // `rows` query rows (a chunk) over cache rows 0 .. kv_len.
     const bool f16 = ctx->act_dtype == DC_ACT_F16;
-    const uint32_t ldt = ((rows + 7u) & ~7u) + 8u * n_seq;
+    const uint32_t kv_rows = seq_start ? rows : kv_len, kv_max = seq_start ? max_len : kv_len;
+    const uint32_t ldt = ((kv_rows + 7u) & ~7u) + 8u * n_seq;
     void* ws = nullptr;
-    int rc = dc_get_workspace(ctx, dc_attention_tc_scratch_bytes(rows, n_seq, nkv), "attention", &ws);
+    int rc = dc_get_workspace(ctx, dc_attention_tc_scratch_bytes(kv_rows, n_seq, nkv), "attention", &ws);
     if (rc != DC_OK) return rc;
     uint16_t* vt = static_cast<uint16_t*>(ws);
     CUtensorMap tq, tk, tv;
     rc = dc_make_tmap(ctx, q, rows, nq * HD, nq * HD, TQ, f16, &tq);
-    if (rc == DC_OK) rc = dc_make_tmap(ctx, kc, rows, nkv * HD, nkv * HD, TKV, f16, &tk);
+    if (rc == DC_OK) rc = dc_make_tmap(ctx, kc, kv_rows, nkv * HD, nkv * HD, TKV, f16, &tk);   // rows past the end read as zeros
     if (rc == DC_OK) rc = dc_make_tmap(ctx, vt, nkv * HD, ldt, ldt, HD, f16, &tv);
     if (rc != DC_OK) return rc;
-    v_transpose_kernel<<<dim3((max_len + 16 + 63) / 64, nkv, n_seq), 256, 0, s>>>(static_cast<const uint16_t*>(vc), vt, rows, nkv, ldt, seq_start, n_seq);
+    v_transpose_kernel<<<dim3((kv_max + 16 + 63) / 64, nkv, n_seq), 256, 0, s>>>(static_cast<const uint16_t*>(vc), vt, kv_rows, nkv, ldt, seq_start, n_seq, kv_len);
     rc = dc_check_launch(ctx, "attention (V transpose)");
     if (rc != DC_OK) return rc;
     rc = dc_attention_tc_warm(ctx);
@@ -468,6 +474,6 @@ int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, 
     const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
     const dim3 grid((max_len + TQ - 1) / TQ, nq, n_seq);
     auto kern = f16 ? attn_tc_kernel<ActF16> : attn_tc_kernel<ActBF16>;
-    kern<<<grid, kThreads, Smem::kBytes, s>>>(tq, tk, tv, gate, qpos, static_cast<uint16_t*>(y), ldg, nq, nkv, scale_log2, seq_start, ctx->status_dev);
+    kern<<<grid, kThreads, Smem::kBytes, s>>>(tq, tk, tv, gate, qpos, static_cast<uint16_t*>(y), ldg, nq, nkv, scale_log2, seq_start, rows, ctx->status_dev);
     return dc_check_launch(ctx, "attention (tcgen05)");
 }

@@ -436,7 +436,7 @@ int forward_single(dc_model* m, cudaStream_t s, const std::vector<dc_model::Chun
                 RUN("kv_norm_rope", dc_kv_norm_rope(c, st, m->p, w.k_norm, m->inv_freq, m->carry.kc[l], m->carry.vc[l], n, ld, kcol, kcol + m->kv_dim, ch.c0, nullptr,
                                                     m->max_rows, d.nkv, d.head_dim, d.rot_dim, d.eps));
                 RUN("attention", dc_attention(c, st, m->qo, m->carry.kc[l], m->carry.vc[l], d.attn_gate ? m->p + m->q_dim : nullptr, m->pos + ch.c0, m->g, n, ld,
-                                              d.nq, d.nkv, d.head_dim, nullptr, 1, 0));
+                                              d.nq, d.nkv, d.head_dim, nullptr, 1, ch.c1));   // cache rows 0 .. c1 are in use
                 out_k = m->q_dim;
             }
             RUN("gemm_out", dc_gemm(c, st, m->g, w.w_out, m->x, n, H, out_k, out_k, out_k, H, DC_EPI_ADD_F32, d.swiglu_block));

@@ -286,9 +286,12 @@ int dc_kv_norm_rope(dc_ctx* ctx, void* stream, const float* pkv, const float* kw
  * 0..=qpos[r] of the bf16 K/V caches [..,nkv,hd]; scale hd^-1/2; fp32 online softmax. `gate` (fp32,
  * row stride ldg, already offset to the gate's first column; NULL = no gate) multiplies the output by
  * sigmoid(gate). Writes bf16 y [rows, nq*hd]. hd must be 128.
- * seq_start == NULL: one sequence. Otherwise seq_start is u32 [n_seq+1] row offsets of packed
- * sequences (q rows and cache rows packed alike, qpos relative to the sequence) and max_len the
- * longest sequence. */
+ * seq_start == NULL: one sequence; max_len, if not 0, is the number of cache rows in use (every
+ * qpos[r] < max_len, the cache holds at least that many rows): a chunk of 64 or more rows that
+ * continues a longer cache then runs on the tcgen05 kernel (rows past max_len are never read), with
+ * max_len = 0 it runs on the mma.sync kernel. Otherwise seq_start is u32 [n_seq+1] row offsets of
+ * packed sequences (q rows and cache rows packed alike, qpos relative to the sequence) and max_len
+ * the longest sequence. */
 int dc_attention(dc_ctx* ctx, void* stream, const void* q, const void* kc, const void* vc, const float* gate,
                  const uint32_t* qpos, void* y, uint32_t rows, uint32_t ldg, uint32_t nq, uint32_t nkv, uint32_t hd,
                  const uint32_t* seq_start, uint32_t n_seq, uint32_t max_len);

@@ -113,6 +113,25 @@ def test_attention_scattered_query_positions(k):
     assert_close(np32(y), want, atol=6e-3, rtol=2 ** -7, what="attention scattered")
 
 
+@pytest.mark.parametrize("rows,c0,gated", [(100, 400, True), (64, 0, False), (300, 1000, True), (129, 127, False), (63, 200, True)])
+def test_attention_chunk_continuing_a_cache(k, rows, c0, gated, act):
+    """A chunk of one request: rows at positions c0 .. c0 + rows over cache rows 0 .. c0 + rows (chunked prefill, the
+    snapshot and state-cache routes, forward.rs:919-942). With the cache length given, a chunk of 64 rows or more runs on
+    the tcgen05 kernel (63 rows: the mma.sync kernel). The cache buffers are longer than the rows in use and hold NaN
+    past them: nothing there may be read."""
+    nq, nkv, hd = 8, 2, 128
+    kv_len = c0 + rows
+    qpos = c0 + np.arange(rows)
+    q, kc, vc, gate, qpos, want = _attn_case(70 + rows, rows, nq, nkv, hd, gated, qpos=qpos, npos=kv_len, act=act)
+    pad = torch.full((77, nkv, hd), float("nan"), dtype=act)
+    y = torch.full((rows + 1, nq * hd), 5.0, dtype=act, device="cuda")
+    k.attn.attention(None, q.cuda(), torch.cat([kc, pad]).cuda(), torch.cat([vc, pad]).cuda(), gate.cuda() if gated else None, _u32(qpos), y, rows,
+                     gate.shape[1] if gated else 0, nq, nkv, hd, max_len=kv_len)
+    k.dev.check_status()
+    assert_close(np32(y[:rows]), want, atol=6e-3 if act == torch.bfloat16 else 1e-3, rtol=2 * half_ulp(act), what=f"attention chunk rows={rows} c0={c0}")
+    assert (np32(y[rows]) == 5.0).all()
+
+
 @pytest.mark.parametrize("repeat", [1, 20], ids=["few-rows-sliced-keys", "many-rows"])
 @pytest.mark.parametrize("gated", [True, False])
 def test_attention_rows_over_packed_caches(k, gated, act, repeat):
