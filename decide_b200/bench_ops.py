@@ -3,6 +3,7 @@
     python -m decide_b200.bench_ops gemm --m 38592 --n 19456 --k 2560 --epi swiglu
     python -m decide_b200.bench_ops rmsnorm --rows 38592
     python -m decide_b200.bench_ops delta --seqs 64 --tokens 603
+    python -m decide_b200.bench_ops request --tokens 603   # ONE request through the whole 36-layer engine
     python -m decide_b200.bench_ops all            # every hot-path kernel at the benchmark's shapes
 
 Prints one JSON line per case: microseconds per launch, the algorithmic work (FLOPs for GEMM and
@@ -274,9 +275,29 @@ def config_case(k: Kernels, cfg: int, iters: int, warmup: int, gated: bool = Tru
     return {"config": cfg, "what": what, "rows": m, "us": us, "flops": flops, "tflops": flops / us / 1e6}
 
 
+def request(dev: Device, tokens: int, iters: int, warmup: int) -> dict:
+    """One request of `tokens` token ids through the full synthetic 36-layer model, host ids in, host logits out (the
+    single-request latency of the benchmark; DECIDE_GRAPHS=0 enqueues kernel by kernel, which a launch list wants)."""
+    from .engine import Engine
+    from .synth import synth_batch, synth_fused_on_device
+    from .weights import BASELINE_DIMS as dims
+
+    cuda = torch.device("cuda", 0)
+    fused, embed, final_norm = synth_fused_on_device(dims, 1, cuda)
+    eng = Engine(dims, dev=dev, max_rows=max(4096, tokens), max_seqs=1, max_answers=8, max_cand=16, fused_layers=fused, embed=embed, final_norm=final_norm)
+    one = synth_batch(dims, 1, tokens, seed=7, n_answers=6 if tokens < 1000 else 3, n_cand=16, max_cand=16)
+    l0 = dev.launches
+    eng.logits(one)
+    per_forward = dev.launches - l0
+    us = _time(lambda: eng.logits(one), iters, warmup)
+    out = {"op": "request", "tokens": tokens, "rows_run": eng.resident_rows, "us": us, "launches_per_forward": per_forward, "graphs": eng.graph_count}
+    eng.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["gemm", "gemms", "rowwise", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "all"])
+    ap.add_argument("op", choices=["gemm", "gemms", "rowwise", "rmsnorm", "gnorm", "conv", "delta", "conv_delta", "rope", "attention", "request", "all"])
     ap.add_argument("--m", type=int, default=38592)
     ap.add_argument("--n", type=int, default=19456)
     ap.add_argument("--k", type=int, default=2560)
@@ -314,6 +335,8 @@ def main():
         out.append(rope(k, a.rows, 32, 8, True, a.iters, a.warmup))
     elif a.op == "attention":
         out.append(attention(k, a.seqs, a.tokens, 32, 8, True, a.iters, a.warmup))
+    elif a.op == "request":
+        out.append(request(dev, a.tokens, a.iters, a.warmup))
     else:
         for m in (603, 2307, 38592):
             for (n, kk, epi) in PROJECTIONS:
