@@ -19,8 +19,19 @@ impl Attn {
                                             rows as u32, ldq as u32, d.nq as u32, d.nkv as u32, d.head_dim as u32) }
         } else {
             unsafe { ffi::dc_attention(self.dev.ctx, st.raw(), ptr(q), ptr(kc), ptr(vc), gate, ptr(qpos) as *const u32, ptr_mut(y), rows as u32, ldq as u32,
-                                       d.nq as u32, d.nkv as u32, d.head_dim as u32, std::ptr::null(), 1, rows as u32) }
+                                       d.nq as u32, d.nkv as u32, d.head_dim as u32, std::ptr::null(), 1, 0) }   // 0: cache length not given (see attention_in_cache)
         };
+        self.dev.check(rc, "attention");
+    }
+
+    /// The same for a chunk of one request whose cache holds `cache_rows` rows in use (positions below it): `Forward` knows
+    /// `pos0 + rows` (forward.rs:1236-1246); with it a chunk of 64 rows or more runs on the tcgen05 kernel.
+    #[allow(clippy::too_many_arguments)]
+    pub fn attention_in_cache(&self, st: &Stream, q: Arg, kc: Arg, vc: Arg, pq: Arg, qpos: Arg, y: Arg, rows: usize, ldq: usize, cache_rows: usize) {
+        let d = &self.d;
+        let gate = if d.attn_gate { (pq.0.ptr + pq.1 + (d.nq * d.head_dim * 4) as u64) as *const f32 } else { std::ptr::null() };
+        let rc = unsafe { ffi::dc_attention(self.dev.ctx, st.raw(), ptr(q), ptr(kc), ptr(vc), gate, ptr(qpos) as *const u32, ptr_mut(y), rows as u32, ldq as u32,
+                                            d.nq as u32, d.nkv as u32, d.head_dim as u32, std::ptr::null(), 1, cache_rows as u32) };
         self.dev.check(rc, "attention");
     }
 }
