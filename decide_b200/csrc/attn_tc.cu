@@ -36,6 +36,7 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0, kColO = 128;
 constexpr float kMasked = -1e30f;
 constexpr float kRescaleStep = 8.0f;   // log2 units
+constexpr int kStatusPositionPastCache = DC_STATUS_POSITION_PAST_CACHE;
 
 struct Smem {
     static constexpr size_t kAtom = 128 * 128;          // [128 rows][64 x 16 bit]
@@ -98,7 +99,7 @@ template <typename Act>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                const float* __restrict__ gate, const uint32_t* __restrict__ qpos, uint16_t* __restrict__ y, uint32_t ldg, uint32_t nq, uint32_t nkv,
-               float scale_log2, const uint32_t* __restrict__ seq_start, uint32_t q_len, int* __restrict__ status) {
+               float scale_log2, const uint32_t* __restrict__ seq_start, uint32_t q_len, uint32_t kv_len, int* __restrict__ status) {
     const uint32_t seq = blockIdx.z, head = blockIdx.y;
     // without seq_start: q_len query rows of one sequence (a chunk that continues a longer cache; the cache starts at row 0
     // and each query row's position says how far it attends)
@@ -170,6 +171,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     __syncthreads();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t n_tiles = static_cast<uint32_t>(*qp_max + TKV) / TKV;   // cache rows 0..=max qpos; 0 only if no row is valid
+    // One sequence with the cache length given: a position at or past it breaks the caller's promise (the maps end there,
+    // so nothing out of bounds is read, but the result would miss keys): reported through the status word.
+    if (!seq_start && tid == 0 && *qp_max >= static_cast<int>(kv_len)) atomicCAS(status, 0, kStatusPositionPastCache);
 
     if (warp == 8) {
         // ------------------------------------------------------------------ issuer (one thread)
@@ -474,6 +478,6 @@ int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, 
     const float scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HD));
     const dim3 grid((max_len + TQ - 1) / TQ, nq, n_seq);
     auto kern = f16 ? attn_tc_kernel<ActF16> : attn_tc_kernel<ActBF16>;
-    kern<<<grid, kThreads, Smem::kBytes, s>>>(tq, tk, tv, gate, qpos, static_cast<uint16_t*>(y), ldg, nq, nkv, scale_log2, seq_start, rows, ctx->status_dev);
+    kern<<<grid, kThreads, Smem::kBytes, s>>>(tq, tk, tv, gate, qpos, static_cast<uint16_t*>(y), ldg, nq, nkv, scale_log2, seq_start, rows, kv_len, ctx->status_dev);
     return dc_check_launch(ctx, "attention (tcgen05)");
 }

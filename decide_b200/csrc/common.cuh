@@ -67,6 +67,8 @@ int dc_delta_chunk_warm(dc_ctx* ctx);
 // Cached 2-D tensor map over a 16-bit row-major matrix [rows][cols] (row stride ld elements): boxes of
 // box_rows x 64 elements, 128-byte swizzle, zero fill outside the matrix.
 int dc_make_tmap(dc_ctx* ctx, const void* base, uint32_t rows, uint32_t cols, uint32_t ld, uint32_t box_rows, bool f16, CUtensorMap* out);
+// Status-word value that is not a wait id: a query position at or past the cache length the caller gave (dc_attention).
+#define DC_STATUS_POSITION_PAST_CACHE 70
 // tcgen05 attention for packed prefill batches, or (seq_start null) `rows` query rows of one sequence over cache rows
 // 0 .. kv_len (attn_tc.cu), and the scratch it takes from the workspace.
 int dc_attention_tc(dc_ctx* ctx, cudaStream_t s, const void* q, const void* kc, const void* vc, const float* gate, const uint32_t* qpos, void* y,

@@ -227,6 +227,8 @@ int dc_check_status(dc_ctx* ctx, void* stream) {
         // a split GEMM that gave up leaves arrival counters of its tail tiles non-zero: the next one must start from zero
         cudaMemsetAsync(ctx->gemm_part_cnt, 0, ctx->sm_count * 4 * sizeof(int), s);
         cudaStreamSynchronize(s);
+        if (code == DC_STATUS_POSITION_PAST_CACHE)
+            return dc_fail(ctx, DC_INVALID_ARG, "attention: a query row's position lies at or past the cache length given as max_len; the results of this run are invalid");
         return dc_fail(ctx, DC_TIMEOUT, "a bounded device-side wait ran out (wait id %d); the results of this run are invalid", code);
     }
     return DC_OK;

@@ -95,12 +95,15 @@ int dc_set_delta_split(dc_ctx* ctx, uint32_t split);
  *  DC_FAMILY_DELTA: the serial kernel of the chunked delta rule with split 3 (split 1 always runs on
  *    mma.sync); tcgen05 keeps the accumulators in tensor memory, one CTA per (sequence, head); mma.sync
  *    also splits the value columns over CTAs. Same results to ~1e-6.
- *  DC_FAMILY_ATTN: tcgen05 serves packed batches (seq_start given); calls without seq_start always run on
- *    mma.sync. Same contract; results differ by fp32 rounding order only.
+ *  DC_FAMILY_ATTN: tcgen05 serves packed batches (seq_start given) and chunks of one sequence whose cache
+ *    length is given (dc_attention); other calls without seq_start run on mma.sync. Same contract;
+ *    results differ by fp32 rounding order only.
  *  DC_FAMILY_GEMM has one engine (tcgen05). */
 int dc_set_engine(dc_ctx* ctx, uint32_t family, uint32_t engine);
 /* Synchronises `stream`, then reports DC_TIMEOUT if a kernel's bounded wait ran out since the
- * last check (the analogue of the command-buffer status check, forward.rs:1022-1042). */
+ * last check (the analogue of the command-buffer status check, forward.rs:1022-1042), or
+ * DC_INVALID_ARG if a kernel found a contract violation only it can see (dc_attention: a position at
+ * or past the cache length given). */
 int dc_check_status(dc_ctx* ctx, void* stream);
 /* Self-test of that path (no counterpart in the reference): enqueues one tiny kernel whose only
  * wait is on an mbarrier that nothing ever arrives at. The wait gives up at the library's limit
@@ -288,7 +291,8 @@ int dc_kv_norm_rope(dc_ctx* ctx, void* stream, const float* pkv, const float* kw
  * sigmoid(gate). Writes bf16 y [rows, nq*hd]. hd must be 128.
  * seq_start == NULL: one sequence; max_len, if not 0, is the number of cache rows in use (every
  * qpos[r] < max_len, the cache holds at least that many rows): a chunk of 64 or more rows that
- * continues a longer cache then runs on the tcgen05 kernel (rows past max_len are never read), with
+ * continues a longer cache then runs on the tcgen05 kernel (rows past max_len are never read; a
+ * position at or past max_len is reported by the next dc_check_status as DC_INVALID_ARG), with
  * max_len = 0 it runs on the mma.sync kernel. Otherwise seq_start is u32 [n_seq+1] row offsets of
  * packed sequences (q rows and cache rows packed alike, qpos relative to the sequence) and max_len
  * the longest sequence. */

@@ -132,6 +132,20 @@ def test_attention_chunk_continuing_a_cache(k, rows, c0, gated, act):
     assert (np32(y[rows]) == 5.0).all()
 
 
+def test_attention_reports_a_position_past_the_given_cache_length(k):
+    """A caller that gives the cache length promises every position is below it; the kernel reads nothing past the length
+    and the next status check reports the broken promise as an argument error, not as a result."""
+    from decide_b200.kernels import KernelError
+
+    nq, nkv, hd, rows = 8, 2, 128, 64
+    q, kc, vc, _, _, _ = _attn_case(90, rows, nq, nkv, hd, False, qpos=np.arange(rows), npos=200, act=k.dev.act_torch)
+    y = torch.empty(rows, nq * hd, dtype=k.dev.act_torch, device="cuda")
+    k.attn.attention(None, q.cuda(), kc.cuda(), vc.cuda(), None, _u32(100 + np.arange(rows)), y, rows, 0, nq, nkv, hd, max_len=150)
+    with pytest.raises(KernelError, match="at or past the cache length"):
+        k.dev.check_status()
+    k.dev.check_status()   # the context stays usable
+
+
 @pytest.mark.parametrize("repeat", [1, 20], ids=["few-rows-sliced-keys", "many-rows"])
 @pytest.mark.parametrize("gated", [True, False])
 def test_attention_rows_over_packed_caches(k, gated, act, repeat):
