@@ -68,3 +68,47 @@ def test_decide_cold_then_follow_up(dev, tmp_path):
     finally:
         eng.build_snapshot([])
     eng.close()
+
+
+def test_decide_check_against_gold_files_of_the_cpu_forward(dev, tmp_path):
+    """`decide check` end to end (decide_b200/gold_check.py, crates/decide-cli/src/check.rs): gold files written from the
+    fp32 CPU forward on the same synthetic weights (the layout reference/gold.py writes), then every request through the
+    GPU engine: prompts and response envelopes identical, decisions and calibrated probabilities within the criteria."""
+    from decide_b200 import gold_check, respond
+    from decide_b200.decision import fields_of
+
+    byte_level_tokenizer_file(tmp_path / "tokenizer.json")
+    tok = prompt.Tokenizer.from_file(tmp_path / "tokenizer.json")
+    sd, eng = make(SMALL, dev, 62, max_rows=2048, max_seqs=1, max_answers=16, max_cand=8)
+    model = gold_synth.build_model(SMALL, sd)
+    requests = {"core/first": {"state": STATE, "questions": FIRST}, "core/second": {"state": STATE, "questions": SECOND},
+                "extra/other": {"state": {"note": "late parcel"}, "questions": SECOND}}
+    for name, req in requests.items():
+        text = json.dumps(req)
+        p = tok.prepare(text)
+        cand = np.zeros((len(p.positions), 8), np.uint32)
+        for i, c in enumerate(p.candidates):
+            cand[i, :len(c)] = c
+        batch = Batch(np.asarray(p.ids, np.uint32), np.array([0, len(p.ids)], np.uint32), np.asarray(p.positions, np.uint32), cand,
+                      np.array([len(c) for c in p.candidates], np.uint32))
+        want, sec = gold_synth.gold_batch_logits(model, batch, 8)
+        logits = [[float(x) for x in want[i, :len(c)]] for i, c in enumerate(p.candidates)]
+        gold = {"name": name, "mode": "fp32", "input_ids": p.ids, "positions": p.positions, "fields": p.compiled.fields,
+                "candidate_ids": dict(zip(p.compiled.fields, p.candidates)), "logits": dict(zip(p.compiled.fields, logits)),
+                "response": respond.respond(fields_of(p), logits, len(p.ids), 1e3 * sec, backend="hf"), "seconds": sec}
+        for root, obj in (("gold", gold), ("requests", req)):
+            path = tmp_path / root / f"{name}.json"
+            path.parent.mkdir(parents=True, exist_ok=True)
+            path.write_text(json.dumps(obj))
+    de = DecisionEngine(eng, tok)
+    try:
+        ok, lines = gold_check.check(de.decide, tmp_path / "gold", tmp_path / "requests")
+    finally:
+        eng.build_snapshot([])
+    text = "\n".join(lines)
+    print(text)
+    assert ok, text
+    assert "summary: 3 requests, 6 fields: PASS" in text and "prompts identical to the gold's (ids, logit rows, fields, candidates): 3/3" in text
+    routes = [l.split()[2] for l in lines[4:7]]
+    assert routes == ["snapshot", "state_cache", "snapshot"]
+    eng.close()
