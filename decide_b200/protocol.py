@@ -187,6 +187,37 @@ def bench_report(eng, requests: list, iters: int = 20, warmup: int = 3, gpu: int
     return report, lines
 
 
+def measure_request(de, name: str, text: str, iters: int = 20, warmup: int = 3, primer: str | None = None) -> dict:
+    """One request JSON through `DecisionEngine.decide`, timed as the reference's bench does (bench.rs:209-290): cold
+    (`primer` None: the state cache is emptied before every run, outside the timed region) or as a follow-up (`primer`: that
+    request runs once, untimed, to cache its state, and every run of `text` finds it). Spans per run: tokenize, forward
+    (ids to logits on the host), head, end to end."""
+    follow_up = primer is not None
+
+    def reset():
+        if not follow_up:
+            de.engine.forget_states()
+
+    if follow_up:
+        de.decide(primer)
+    reset()
+    first = de.decide(text)   # the first warm-up run also records what the request is
+    for _ in range(1, warmup):
+        reset()
+        de.decide(text)
+    spans = {"tokenize": [], "forward": [], "head": [], "e2e": []}
+    for _ in range(iters):
+        reset()
+        t0 = time.perf_counter()
+        d = de.decide(text)
+        spans["e2e"].append((time.perf_counter() - t0) * 1e3)
+        for k in ("tokenize", "forward", "head"):
+            spans[k].append(d.timings[f"{k}_ms"])
+    return {"name": name, "kind": "follow-up" if follow_up else "cold", "tokens": len(first.prepared.ids), "rows": first.rows, "route": first.route,
+            "decisions": {f: a["decision"] for f, a in first.response["answers"].items()},
+            **{f"{k}_ms": stats(v) for k, v in spans.items()}}
+
+
 def check_table(rows: list) -> tuple[bool, list]:
     """`decide check`'s table and summary (check.rs:270-343). rows = [{"name", "tokens", "rows", "got", "want", "ncand", "forward_ms"}]
     with got / want logits [n, max_cand]. Returns (pass, lines)."""

@@ -67,3 +67,32 @@ def test_check_table_rules():
     flipped[0, :2] = [4.992, 4.998]
     ok, lines = P.check_table([dict(good, name="tie", got=flipped, want=tie)])
     assert ok and any("flips below the 0.05 gold margin (allowed): tie:" in l for l in lines)
+
+
+def test_measure_request_cold_and_follow_up():
+    """bench.rs:209-290: a cold measurement empties the state cache before every run; a follow-up runs its primer once
+    and never forgets."""
+    from types import SimpleNamespace
+
+    from decide_b200 import protocol
+
+    calls = []
+
+    class FakeEngine:
+        def forget_states(self):
+            calls.append("forget")
+
+    class FakeDecisionEngine:
+        engine = FakeEngine()
+
+        def decide(self, text):
+            calls.append(text)
+            return SimpleNamespace(prepared=SimpleNamespace(ids=[0] * 40), rows=17, route="snapshot" if text == "primer" else "state_cache",
+                                   response={"answers": {"team": {"decision": "billing"}}}, timings={"tokenize_ms": 0.1, "forward_ms": 2.0, "head_ms": 0.05})
+
+    cold = protocol.measure_request(FakeDecisionEngine(), "card", "req", iters=4, warmup=3)
+    assert calls == ["forget", "req"] * 7 and cold["kind"] == "cold" and cold["forward_ms"]["p50"] == 2.0 and len(cold["e2e_ms"]["samples"]) == 4
+    assert cold["decisions"] == {"team": "billing"} and cold["tokens"] == 40 and cold["rows"] == 17
+    calls.clear()
+    warm = protocol.measure_request(FakeDecisionEngine(), "card", "req", iters=4, warmup=3, primer="primer")
+    assert calls == ["primer"] + ["req"] * 7 and warm["kind"] == "follow-up" and warm["route"] == "state_cache"
