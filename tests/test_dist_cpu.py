@@ -131,3 +131,53 @@ def test_tp_local_dims_and_shapes():
         assert torch.equal(torch.cat([p["w_down"] for p in parts], dim=1), whole["w_down"])
         assert torch.equal(torch.cat([p["w_gu"] for p in parts], dim=0), whole["w_gu"])
         assert torch.equal(torch.cat([p["w_out"] for p in parts], dim=1), whole["w_out"])
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_tp_shards_reproduce_the_whole_model_at_4_and_8_ranks(world):
+    """The same partition arithmetic at the wider splits (one head of every kind per rank at 8), the ranks emulated as
+    threads of one process whose all-reduce meets at a barrier: sums in rank order, so every rank sees the same bits."""
+    import threading
+
+    from decide_b200.synth import synth_batch, synth_state_dict
+    from decide_b200.weights import Dims, fuse_layer, tp_shard_layer
+    from oracle import cpu_forward
+
+    d = Dims(hidden=64, n_layers=4, nq=8, nkv=8, head_dim=128, rot_dim=32, gdn_nk=8, gdn_nv=8, inter=256, vocab=50)
+    sd = synth_state_dict(d, seed=7)
+    batch = synth_batch(d, 1, 19, seed=8, n_answers=2, n_cand=4, max_cand=4)
+    positions = [int(r) for r in batch.ans_rows]
+    cands = [batch.cand[i, :4] for i in range(2)]
+    fused = [fuse_layer(sd, l, d) for l in range(d.n_layers)]
+    want = cpu_forward.forward_logits(d, fused, sd["embed_tokens.weight"], sd["norm.weight"], batch.ids, positions, cands)
+    barrier, parts, got, errors = threading.Barrier(world), [None] * world, [None] * world, []
+
+    def rank_main(rank):
+        def all_reduce(a):
+            parts[rank] = np.array(a, dtype=np.float64 if a.dtype == np.float64 else a.dtype)
+            barrier.wait(timeout=120)
+            total = parts[0].copy()
+            for r in range(1, world):
+                total = total + parts[r]
+            barrier.wait(timeout=120)   # nobody overwrites its part before everybody has summed
+            return total
+
+        try:
+            local = [tp_shard_layer(fused[l], l, d, world, rank) for l in range(d.n_layers)]
+            got[rank] = cpu_forward.forward_logits(d.tp_local(world), local, sd["embed_tokens.weight"], sd["norm.weight"], batch.ids, positions, cands,
+                                                   all_reduce=all_reduce)
+        except Exception as e:   # a rank that fails must not leave the others at the barrier
+            errors.append((rank, repr(e)))
+            barrier.abort()
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=300)
+    assert not errors, errors
+    scale = max(np.abs(w).max() for w in want)
+    for rank in range(world):
+        err = max(np.abs(g - w).max() for g, w in zip(got[rank], want))
+        assert err < 1e-4 * max(scale, 1.0), f"rank {rank} of {world}: sharded forward differs from the whole model by {err:.3e}"
+        assert all(np.array_equal(a, b) for a, b in zip(got[rank], got[0]))
